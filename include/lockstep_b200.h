@@ -1,0 +1,97 @@
+/* lockstep_b200 -- C ABI of the B200 (sm_100a) MXFP4 hot path.
+ *
+ * Drop-in boundary for lockstep's data-parallel hot path: MXFP4 quantize /
+ * pack / unpack / dequantize, the packed (dual-batch) MXFP4 GEMM and the
+ * FP4-compressed gradient all-reduce.  Plain pointers and sizes only; every
+ * pointer is a DEVICE pointer unless its comment says "host".  Kernels are
+ * enqueued on the CUDA stream passed as `stream` (a cudaStream_t cast to
+ * void*, NULL = default stream) and the call returns without synchronising
+ * unless stated otherwise.
+ *
+ * Return value: 0 on success, a negative LS_E* code otherwise;
+ * ls_last_error() gives the message of the calling thread's last failure.
+ * Nothing in this library computes on the CPU: without a CUDA device of
+ * compute capability 10.x every compute entry point returns LS_EARCH.
+ *
+ * "Replaces" comments cite the lockstep source (path:line within that
+ * project) whose behaviour the entry point reproduces.
+ */
+#ifndef LOCKSTEP_B200_H
+#define LOCKSTEP_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LS_OK        0
+#define LS_EINVAL   -1   /* bad argument (shape, block size, null pointer)   */
+#define LS_EALIGN   -2   /* pointer or size not aligned as documented        */
+#define LS_ECUDA    -3   /* a CUDA runtime/driver call failed                */
+#define LS_ETIMEOUT -4   /* a bounded device-side wait ran out               */
+#define LS_EARCH    -5   /* no sm_100 device                                 */
+#define LS_ESTATE   -6   /* handle used in the wrong state                   */
+
+/* element types of floating-point buffers */
+#define LS_F32  0
+#define LS_BF16 1
+
+/* rounding of a value exactly halfway between two E2M1 grid points */
+#define LS_ROUND_REF 0   /* keep the smaller magnitude: lockstep fp4.py:43-54 */
+#define LS_ROUND_RNE 1   /* OCP MX ties-to-even (no lockstep counterpart)     */
+
+int ls_version(void);
+const char *ls_last_error(void);
+
+/* Number of bytes of the tensor-core scale-factor ("SF") buffer for a
+ * [rows, K] operand quantized in blocks of 32: 512 bytes per 128 rows x 128
+ * columns, rows rounded up to 128.  K must be a multiple of 128. */
+int64_t ls_sf_bytes(int64_t rows, int64_t K);
+
+/* Fused MXFP4 quantizer along the last dimension.
+ * Replaces fp4.py:57-72 (quantize_mxfp4), :43-54 (_round_to_e2m1) and,
+ * through `packed`, :91-94 (pack_fp4).
+ *   x        [rows, K] row-major, LS_F32 or LS_BF16; 16-byte aligned
+ *   block    32 or 16; K % block == 0
+ * Outputs, each may be NULL (at least one must not be):
+ *   codes    [rows, K] one E2M1 code per byte (bit 3 = sign)
+ *   packed   [rows, K/2] two codes per byte, even index in the low nibble
+ *   scale    [rows, K/block] fp32 power of two 2^E
+ *   e8m0     [rows, K/block] biased exponent E+127 (0xFF for a NaN block)
+ *   sf       e8m0 bytes in the tcgen05 scale-factor layout (ls_sf_bytes);
+ *            needs block == 32 and K % 128 == 0 */
+int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int block,
+                      int rounding, uint8_t *codes, uint8_t *packed, float *scale,
+                      uint8_t *e8m0, uint8_t *sf, void *stream);
+
+/* Replaces fp4.py:43-54 (_round_to_e2m1) on values already divided by their
+ * scale: q fp32 [n] -> codes [n]. */
+int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *codes, void *stream);
+
+/* Replaces fp4.py:91-94 (pack_fp4).  n_codes even; 16-byte aligned buffers. */
+int ls_pack_fp4(const uint8_t *codes, uint8_t *packed, int64_t n_codes, void *stream);
+
+/* Replaces fp4.py:97-99 (unpack_fp4). */
+int ls_unpack_fp4(const uint8_t *packed, uint8_t *codes, int64_t n_bytes, void *stream);
+
+/* Replaces fp4.py:75-78 (dequantize_mxfp4): out = value[code] * scale.
+ *   q        codes [rows, K] (is_packed = 0) or packed bytes [rows, K/2] (1)
+ *   scale    fp32 [rows, K/block], or NULL when e8m0 is given
+ *   e8m0     exponent bytes [rows, K/block], or NULL
+ *   out      [rows, K], LS_F32 or LS_BF16 */
+int ls_dequantize_mxfp4(const uint8_t *q, int is_packed, const float *scale,
+                        const uint8_t *e8m0, int64_t rows, int64_t K, int block,
+                        void *out, int out_dtype, void *stream);
+
+/* fp32 power-of-two scales [rows, K/32] -> scale-factor layout bytes.
+ * Serves callers of mxfp4_gemm.py:161 that hold fp32 scales.  `bad` (device
+ * int32, may be NULL) is incremented for every scale that is not a power of
+ * two in [2^-127, 2^127]. */
+int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint8_t *sf, int32_t *bad,
+                    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LOCKSTEP_B200_H */

@@ -1,0 +1,433 @@
+// MXFP4 codec kernels: fused quantize (+pack, +E8M0, +tensor-core scale
+// layout), pack, unpack, dequantize.  All are HBM-bound streaming kernels:
+// 128-bit coalesced loads and stores, block maxima by warp shuffles, grids of
+// a few CTAs per SM looping over the tensor.
+#include "common.cuh"
+
+namespace ls {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;          // 16-byte loads in flight per thread
+
+struct QuantOut {
+    uint8_t *codes, *packed, *e8m0, *sf;
+    float *scale;
+    uint32_t kblocks;               // blocks per row (K / BLOCK)
+    uint32_t ktiles;                // K / 128 (scale-factor tiles per row)
+};
+
+// Stores the results of one 8-element group.  `g8` = index of the group,
+// `lane_in_block` = position of the group inside its quantization block.
+template <int BLOCK>
+__device__ __forceinline__ void store_group(const QuantOut &o, int64_t g8, uint32_t pk,
+                                            uint32_t e8, bool leader)
+{
+    if (o.packed) reinterpret_cast<uint32_t *>(o.packed)[g8] = pk;
+    if (o.codes) {
+        uint2 c;
+        c.x = (pk & 0xFu) | ((pk & 0xF0u) << 4) | ((pk & 0xF00u) << 8) | ((pk & 0xF000u) << 12);
+        uint32_t h = pk >> 16;
+        c.y = (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
+        reinterpret_cast<uint2 *>(o.codes)[g8] = c;
+    }
+    if (leader) {
+        int64_t blk = g8 / (BLOCK / 8);
+        if (o.scale) o.scale[blk] = __uint_as_float(scale_bits(e8));
+        if (o.e8m0) o.e8m0[blk] = uint8_t(e8);
+        if (o.sf) {
+            uint32_t row = uint32_t(blk / o.kblocks);
+            uint32_t kb = uint32_t(blk - int64_t(row) * o.kblocks);
+            o.sf[sf_offset(row, kb, o.ktiles)] = uint8_t(e8);
+        }
+    }
+}
+
+// Generic rounding of 8 values already divided by the scale.
+template <bool RNE>
+__device__ __forceinline__ uint32_t codes8(const float (&q)[8])
+{
+    uint32_t pk = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) pk |= e2m1_code<RNE>(q[i]) << (4 * i);
+    return pk;
+}
+
+// ---- bf16 input -------------------------------------------------------------
+// One thread owns 8 consecutive elements (one 16-byte load); BLOCK/8 adjacent
+// lanes share a quantization block.  The codes come from the hardware
+// E2M1 converter (round-to-nearest-even).  For the reference rule (halfway
+// keeps the smaller magnitude) the divisor carries a factor (1 - 2^-12): a
+// bf16 value has 8 significant bits, the factor 12, so the product is exact
+// in fp32, lies strictly below every halfway point the value sat on, and
+// never crosses one it did not.
+template <int BLOCK, bool RNE>
+__global__ void __launch_bounds__(kThreads)
+quantize_bf16_kernel(const uint4 *__restrict__ x, int64_t n8, QuantOut o)
+{
+    constexpr int LPB = BLOCK / 8;
+    const int64_t stride = int64_t(gridDim.x) * kThreads * kUnroll;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads * kUnroll; base < n8; base += stride) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            int64_t g8 = base + u * kThreads + threadIdx.x;
+            v[u] = g8 < n8 ? ld_stream(x + g8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; u++) {
+            int64_t g8 = base + u * kThreads + threadIdx.x;
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            // |x| maxima on packed bf16 pairs, NaN-propagating
+            __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
+#pragma unroll
+            for (int i = 1; i < 4; i++)
+                m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+            uint32_t mb = *reinterpret_cast<uint32_t *>(&m);
+#pragma unroll
+            for (int off = 1; off < LPB; off <<= 1) {
+                uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, mb, off);
+                __nv_bfloat162 mm = __hmax2_nan(*reinterpret_cast<__nv_bfloat162 *>(&mb),
+                                                *reinterpret_cast<__nv_bfloat162 *>(&other));
+                mb = *reinterpret_cast<uint32_t *>(&mm);
+            }
+            uint32_t amax = max(mb & 0xFFFF0000u, mb << 16);      // as fp32 bits
+            uint32_t e8 = block_e8m0(amax);
+            float q[8];
+            uint32_t pk;
+            if (e8 <= 252u) {
+                uint32_t mul = RNE ? inv_scale_bits(e8) : (((253u - e8) << 23) | 0x7FF000u);
+                float c = __uint_as_float(mul);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    q[2 * i] = __uint_as_float(w[i] << 16) * c;
+                    q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
+                }
+                pk = cvt_e2m1x8(q);
+            } else {                                   // infinite or NaN block maximum
+                float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    q[2 * i] = __uint_as_float(w[i] << 16) * c;
+                    q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
+                }
+                pk = codes8<RNE>(q);
+            }
+            if (g8 < n8) store_group<BLOCK>(o, g8, pk, e8, (threadIdx.x & (LPB - 1)) == 0);
+        }
+    }
+}
+
+// ---- fp32 input -------------------------------------------------------------
+// One thread owns 8 consecutive elements (two adjacent 16-byte loads).
+// Integer rounding on the bit pattern; exact for every fp32 input.
+template <int BLOCK, bool RNE>
+__global__ void __launch_bounds__(kThreads)
+quantize_f32_kernel(const uint4 *__restrict__ x, int64_t n8, QuantOut o)
+{
+    constexpr int LPB = BLOCK / 8;
+    constexpr int U = kUnroll / 2;
+    const int64_t stride = int64_t(gridDim.x) * kThreads * U;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads * U; base < n8; base += stride) {
+        uint4 v[U][2];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int64_t g8 = base + u * kThreads + threadIdx.x;
+            bool ok = g8 < n8;
+            v[u][0] = ok ? ld_stream(x + 2 * g8) : make_uint4(0, 0, 0, 0);
+            v[u][1] = ok ? ld_stream(x + 2 * g8 + 1) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int64_t g8 = base + u * kThreads + threadIdx.x;
+            const uint32_t w[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w,
+                                   v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) amax = max(amax, w[i] & 0x7FFFFFFFu);
+#pragma unroll
+            for (int off = 1; off < LPB; off <<= 1)
+                amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+            uint32_t e8 = block_e8m0(amax);
+            float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+            float q[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) q[i] = __uint_as_float(w[i]) * c;
+            uint32_t pk = codes8<RNE>(q);
+            if (g8 < n8) store_group<BLOCK>(o, g8, pk, e8, (threadIdx.x & (LPB - 1)) == 0);
+        }
+    }
+}
+
+// ---- pack / unpack ----------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+pack_kernel(const uint4 *__restrict__ codes, uint2 *__restrict__ packed, int64_t n16,
+            const uint8_t *codes_tail, uint8_t *packed_tail, int tail_bytes)
+{
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n16; i += stride) {
+        uint4 c = ld_stream(codes + i);
+        auto squeeze = [](uint32_t a) {      // 4 code bytes -> 16 bits
+            uint32_t t = a | (a >> 4);       // byte0|byte1<<4 in bits 0-7, byte2|byte3<<4 in 16-23
+            return (t & 0xFFu) | ((t >> 8) & 0xFF00u);
+        };
+        uint2 p;
+        p.x = squeeze(c.x & 0x0F0F0F0Fu) | (squeeze(c.y & 0x0F0F0F0Fu) << 16);
+        p.y = squeeze(c.z & 0x0F0F0F0Fu) | (squeeze(c.w & 0x0F0F0F0Fu) << 16);
+        packed[i] = p;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < tail_bytes)
+        packed_tail[threadIdx.x] = uint8_t((codes_tail[2 * threadIdx.x] & 0xF) |
+                                           (codes_tail[2 * threadIdx.x + 1] << 4));
+}
+
+__device__ __forceinline__ uint32_t spread4(uint32_t h)   // 16 bits -> 4 code bytes
+{
+    return (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
+}
+
+__global__ void __launch_bounds__(kThreads)
+unpack_kernel(const uint2 *__restrict__ packed, uint4 *__restrict__ codes, int64_t n8,
+              const uint8_t *packed_tail, uint8_t *codes_tail, int tail_bytes)
+{
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n8; i += stride) {
+        uint2 p = packed[i];
+        uint4 c;
+        c.x = spread4(p.x & 0xFFFFu);
+        c.y = spread4(p.x >> 16);
+        c.z = spread4(p.y & 0xFFFFu);
+        c.w = spread4(p.y >> 16);
+        codes[i] = c;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < tail_bytes) {
+        uint8_t b = packed_tail[threadIdx.x];
+        codes_tail[2 * threadIdx.x] = b & 0xF;
+        codes_tail[2 * threadIdx.x + 1] = b >> 4;
+    }
+}
+
+// ---- dequantize ---------------------------------------------------------------
+// One thread produces 8 outputs from 8 codes (8 bytes, or 4 packed bytes).
+template <bool PACKED, bool OUT_BF16>
+__global__ void __launch_bounds__(kThreads)
+dequantize_kernel(const uint8_t *__restrict__ q, const float *__restrict__ scale,
+                  const uint8_t *__restrict__ e8m0, int64_t n8, int block, void *__restrict__ out)
+{
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    for (int64_t g8 = int64_t(blockIdx.x) * kThreads + threadIdx.x; g8 < n8; g8 += stride) {
+        uint32_t pk;
+        if (PACKED) {
+            pk = reinterpret_cast<const uint32_t *>(q)[g8];
+        } else {
+            uint2 c = reinterpret_cast<const uint2 *>(q)[g8];
+            auto squeeze = [](uint32_t a) {
+                a &= 0x0F0F0F0Fu;
+                uint32_t t = a | (a >> 4);
+                return (t & 0xFFu) | ((t >> 8) & 0xFF00u);
+            };
+            pk = squeeze(c.x) | (squeeze(c.y) << 16);
+        }
+        int64_t blk = g8 * 8 / block;
+        float s = scale ? scale[blk] : __uint_as_float(scale_bits(e8m0[blk]));
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) f[i] = e2m1_value((pk >> (4 * i)) & 0xFu) * s;
+        if (OUT_BF16) {
+            uint4 r;
+            uint32_t *rw = &r.x;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                rw[i] = *reinterpret_cast<uint32_t *>(&h);
+            }
+            reinterpret_cast<uint4 *>(out)[g8] = r;
+        } else {
+            float4 *o4 = reinterpret_cast<float4 *>(out) + 2 * g8;
+            o4[0] = make_float4(f[0], f[1], f[2], f[3]);
+            o4[1] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+scales_to_sf_kernel(const float *__restrict__ scale, int64_t nblocks, uint32_t kblocks,
+                    uint8_t *__restrict__ sf, int32_t *bad)
+{
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    for (int64_t b = int64_t(blockIdx.x) * kThreads + threadIdx.x; b < nblocks; b += stride) {
+        uint32_t u = __float_as_uint(scale[b]);
+        uint32_t e = (u >> 23) & 0xFFu;
+        bool ok = (u & 0x807FFFFFu) == 0u && e >= 1u && e <= 254u;
+        if (u == 0x00400000u) { ok = true; e = 0u; }          // 2^-127
+        if (!ok) {
+            if (bad) atomicAdd(bad, 1);
+            e = 255u;
+        }
+        uint32_t row = uint32_t(b / kblocks);
+        uint32_t kb = uint32_t(b - int64_t(row) * kblocks);
+        sf[sf_offset(row, kb, kblocks / 4)] = uint8_t(e);
+    }
+}
+
+template <bool RNE>
+__global__ void __launch_bounds__(kThreads)
+round_e2m1_kernel(const float *__restrict__ q, int64_t n, uint8_t *__restrict__ codes)
+{
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride)
+        codes[i] = uint8_t(e2m1_code<RNE>(q[i]));
+}
+
+int grid_for(int64_t work_items, int per_cta)
+{
+    int64_t want = (work_items + per_cta - 1) / per_cta;
+    int64_t cap = int64_t(sm_count()) * 8;             // 8 CTAs of 256 threads fill an SM
+    return int(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+}  // namespace
+}  // namespace ls
+
+using namespace ls;
+
+extern "C" int64_t ls_sf_bytes(int64_t rows, int64_t K)
+{
+    if (rows < 0 || K < 0 || K % 128 != 0) return -1;
+    return ((rows + 127) / 128) * (K / 128) * 512;
+}
+
+extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int block,
+                                 int rounding, uint8_t *codes, uint8_t *packed, float *scale,
+                                 uint8_t *e8m0, uint8_t *sf, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (block != 32 && block != 16) return fail(LS_EINVAL, "block must be 32 or 16, got %d", block);
+    if (rows < 0 || K < 0 || K % block != 0)
+        return fail(LS_EINVAL, "K=%lld must be a multiple of block=%d", (long long)K, block);
+    if (x_dtype != LS_F32 && x_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported dtype %d", x_dtype);
+    if (rounding != LS_ROUND_REF && rounding != LS_ROUND_RNE) return fail(LS_EINVAL, "bad rounding %d", rounding);
+    if (rows * K == 0) return LS_OK;
+    if (!codes && !packed && !scale && !e8m0 && !sf) return fail(LS_EINVAL, "no output requested");
+    if (sf && (block != 32 || K % 128 != 0))
+        return fail(LS_EINVAL, "scale-factor layout needs block 32 and K %% 128 == 0 (K=%lld)", (long long)K);
+    int64_t n = rows * K;
+    if (n == 0) return LS_OK;
+    if (!x) return fail(LS_EINVAL, "x is null");
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7) || (reinterpret_cast<uintptr_t>(packed) & 3))
+        return fail(LS_EALIGN, "x must be 16-byte, codes 8-byte, packed 4-byte aligned");
+    if (n / block >= (int64_t(1) << 32)) return fail(LS_EINVAL, "too many blocks");
+    QuantOut o{codes, packed, e8m0, sf, scale, uint32_t(K / block), uint32_t(K / 128)};
+    int64_t n8 = n / 8;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint4 *xp = static_cast<const uint4 *>(x);
+    bool rne = rounding == LS_ROUND_RNE;
+    if (x_dtype == LS_BF16) {
+        int grid = grid_for(n8, kThreads * kUnroll);
+        if (block == 32) {
+            if (rne) quantize_bf16_kernel<32, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            else quantize_bf16_kernel<32, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+        } else {
+            if (rne) quantize_bf16_kernel<16, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            else quantize_bf16_kernel<16, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+        }
+    } else {
+        int grid = grid_for(n8, kThreads * kUnroll / 2);
+        if (block == 32) {
+            if (rne) quantize_f32_kernel<32, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            else quantize_f32_kernel<32, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+        } else {
+            if (rne) quantize_f32_kernel<16, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            else quantize_f32_kernel<16, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+        }
+    }
+    LS_LAUNCH_CHECK("quantize_mxfp4");
+    return LS_OK;
+}
+
+extern "C" int ls_pack_fp4(const uint8_t *codes, uint8_t *packed, int64_t n_codes, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (n_codes < 0 || (n_codes & 1)) return fail(LS_EINVAL, "n_codes must be even");
+    if (n_codes == 0) return LS_OK;
+    if (!codes || !packed) return fail(LS_EINVAL, "null pointer");
+    if (!aligned16(codes) || (reinterpret_cast<uintptr_t>(packed) & 7)) return fail(LS_EALIGN, "codes 16-byte, packed 8-byte aligned");
+    int64_t n16 = n_codes / 16;
+    int tail = int((n_codes - n16 * 16) / 2);
+    pack_kernel<<<grid_for(n16, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4 *>(codes), reinterpret_cast<uint2 *>(packed), n16,
+        codes + n16 * 16, packed + n16 * 8, tail);
+    LS_LAUNCH_CHECK("pack_fp4");
+    return LS_OK;
+}
+
+extern "C" int ls_unpack_fp4(const uint8_t *packed, uint8_t *codes, int64_t n_bytes, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (n_bytes < 0) return fail(LS_EINVAL, "negative size");
+    if (n_bytes == 0) return LS_OK;
+    if (!codes || !packed) return fail(LS_EINVAL, "null pointer");
+    if (!aligned16(codes) || (reinterpret_cast<uintptr_t>(packed) & 7)) return fail(LS_EALIGN, "codes 16-byte, packed 8-byte aligned");
+    int64_t n8 = n_bytes / 8;
+    int tail = int(n_bytes - n8 * 8);
+    unpack_kernel<<<grid_for(n8, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint2 *>(packed), reinterpret_cast<uint4 *>(codes), n8,
+        packed + n8 * 8, codes + n8 * 16, tail);
+    LS_LAUNCH_CHECK("unpack_fp4");
+    return LS_OK;
+}
+
+extern "C" int ls_dequantize_mxfp4(const uint8_t *q, int is_packed, const float *scale,
+                                   const uint8_t *e8m0, int64_t rows, int64_t K, int block,
+                                   void *out, int out_dtype, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (block != 32 && block != 16) return fail(LS_EINVAL, "block must be 32 or 16, got %d", block);
+    if (rows < 0 || K < 0 || K % block != 0) return fail(LS_EINVAL, "K must be a multiple of block");
+    if (out_dtype != LS_F32 && out_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported dtype %d", out_dtype);
+    if (!scale == !e8m0) return fail(LS_EINVAL, "give exactly one of scale and e8m0");
+    int64_t n = rows * K;
+    if (n == 0) return LS_OK;
+    if (!q || !out) return fail(LS_EINVAL, "null pointer");
+    if (!aligned16(out) || (reinterpret_cast<uintptr_t>(q) & (is_packed ? 3 : 7))) return fail(LS_EALIGN, "misaligned buffer");
+    int64_t n8 = n / 8;
+    int grid = grid_for(n8, kThreads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (is_packed) {
+        if (out_dtype == LS_BF16) dequantize_kernel<true, true><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
+        else dequantize_kernel<true, false><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
+    } else {
+        if (out_dtype == LS_BF16) dequantize_kernel<false, true><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
+        else dequantize_kernel<false, false><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
+    }
+    LS_LAUNCH_CHECK("dequantize_mxfp4");
+    return LS_OK;
+}
+
+extern "C" int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint8_t *sf, int32_t *bad,
+                               void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (rows < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K must be a multiple of 128");
+    int64_t nblocks = rows * (K / 32);
+    if (nblocks == 0) return LS_OK;
+    if (!scale || !sf) return fail(LS_EINVAL, "null pointer");
+    scales_to_sf_kernel<<<grid_for(nblocks, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        scale, nblocks, uint32_t(K / 32), sf, bad);
+    LS_LAUNCH_CHECK("scales_to_sf");
+    return LS_OK;
+}
+
+extern "C" int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *codes, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (n < 0) return fail(LS_EINVAL, "negative size");
+    if (n == 0) return LS_OK;
+    if (!q || !codes) return fail(LS_EINVAL, "null pointer");
+    int grid = grid_for(n, kThreads);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rounding == LS_ROUND_RNE) round_e2m1_kernel<true><<<grid, kThreads, 0, st>>>(q, n, codes);
+    else round_e2m1_kernel<false><<<grid, kThreads, 0, st>>>(q, n, codes);
+    LS_LAUNCH_CHECK("round_e2m1");
+    return LS_OK;
+}
