@@ -91,6 +91,30 @@ int ls_dequantize_mxfp4(const uint8_t *q, int is_packed, const float *scale,
 int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint8_t *sf, int32_t *bad,
                     void *stream);
 
+/* Packed MXFP4 GEMM  C[M,N] = A[M,K] * W[N,K]^T  with fp32 accumulation.
+ * Replaces mxfp4_gemm.py:161-174 (mxfp4_gemm_packed) and the kernel behind it
+ * (:116-158); same math as the reference's dequantize + F.linear path
+ * (fp4_linear.py:40).
+ *   a_pk   [M, K/2] packed E2M1, K-contiguous          bt_pk  [N, K/2] likewise
+ *   sfa    scale bytes of A in the scale-factor layout  sfb    likewise for W
+ *   c      [M, N] row-major, LS_BF16 (round to nearest even) or LS_F32
+ * K % 128 == 0; M and N are free.  All buffers 16-byte aligned. */
+int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                  void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
+
+/* Dual-batch form: two activation batches against one weight stream, one
+ * launch, two outputs.  Replaces dual_gemm.py:244-255 (dual_separate) for the
+ * shared-weight case b1 is b2 (train_step.py:52-53) on MXFP4 operands. */
+int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
+                       const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
+                       void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
+
+/* Synchronises the device's error word to the host: returns LS_ETIMEOUT (and
+ * clears the word) if any GEMM kernel since the last call abandoned a bounded
+ * wait, LS_OK otherwise.  `status_host` (host int, may be NULL) receives the
+ * raw word.  Blocks until prior work on the default stream is done. */
+int ls_gemm_status(int *status_host);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,386 @@
+// Block-scaled MXFP4 GEMM on the 5th-generation tensor cores:
+//   C[b][M,N] = A[b][M,K] * W[N,K]^T,  b = 0 (single) or 0,1 (dual batch, one W)
+// A and W are packed E2M1 (two codes per byte, K-contiguous) with one UE8M0
+// scale per 32 elements, held in the 128-row x 4-block tile layout that
+// tcgen05.cp moves into tensor memory.  Accumulation is fp32 in tensor memory;
+// the epilogue rounds to bf16 (nearest even) or writes fp32.
+//
+// One persistent CTA per SM, three roles:
+//   warp 0      TMA producer: operand tiles (128-byte swizzle) and scale tiles
+//               into a ring of shared-memory stages
+//   warp 1      MMA issuer: scale tiles shared -> tensor memory, then four
+//               K=64 MMAs per stage; commits free the stage / publish the tile
+//   warps 2-5   epilogue: tensor memory -> registers -> global
+// Two accumulator buffers alternate between tiles.  With 256-column tiles they
+// overlap by 32 columns (2 x 256 + scales would not fit in 512 columns): the
+// epilogue drains the shared columns first and only then lets the next tile's
+// MMAs start.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace ls {
+namespace {
+
+constexpr int BM = 128;            // rows of A per tile (= tensor-memory lanes)
+constexpr int BKB = 128;           // bytes of K per stage row = 256 E2M1 = one swizzle row
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+
+template <int BN>
+struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int A_BYTES = BM * BKB;
+    static constexpr int B_BYTES = BN * BKB;
+    static constexpr int SFA_BYTES = 1024;                 // 128 rows x 8 k-blocks
+    static constexpr int SFB_BYTES = (BN / 128) * 1024;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int OVL = BN == 256 ? 32 : 0;        // columns shared by the two accumulators
+    static constexpr int ACC1 = BN - OVL;                 // first column of the second accumulator
+    static constexpr int SFA_COL = 2 * BN - OVL;          // 8 columns
+    static constexpr int SFB_COL = SFA_COL + 8;           // BN / 16 columns
+    static_assert(SFB_COL + BN / 16 <= kTmemCols, "tensor memory overflow");
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+    const uint8_t *sfa[2];
+    const uint8_t *sfb;
+    void *c[2];
+    int M, N, K;
+    int nbatch;
+    int out_bf16;
+    int *err;                      // device int, set non-zero when a wait ran out
+};
+
+__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, int row, int col0,
+                                            const uint32_t (&r)[32])
+{
+    if (row >= p.M || col0 >= p.N) return;
+    if (p.out_bf16) {
+        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(cbase) + int64_t(row) * p.N + col0;
+        if (col0 + 32 <= p.N && (p.N & 7) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; v++) {
+                uint4 o;
+                uint32_t *ow = &o.x;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2 * j]),
+                                                             __uint_as_float(r[8 * v + 2 * j + 1]));
+                    ow[j] = *reinterpret_cast<uint32_t *>(&h);
+                }
+                reinterpret_cast<uint4 *>(dst)[v] = o;
+            }
+        } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        }
+    } else {
+        float *dst = static_cast<float *>(cbase) + int64_t(row) * p.N + col0;
+        if (col0 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int v = 0; v < 8; v++)
+                reinterpret_cast<uint4 *>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __uint_as_float(r[j]);
+        }
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+                  const __grid_constant__ CUtensorMap tm_b, const GemmParams p)
+{
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * C::STAGES);
+    const uint32_t acc_free_bar = acc_full_bar + 8u;
+    const uint32_t tmem_slot = acc_free_bar + 8u;
+    uint8_t *gen_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_p = reinterpret_cast<volatile uint32_t *>(gen_base + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 2));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot_p + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles * p.nbatch;
+    const int k_tiles = (p.K / 2 + BKB - 1) / BKB;
+    const int k_atoms = p.K / 128;                    // scale tiles (4 k-blocks each) per row tile
+    const int n_atoms = (p.N + 127) / 128;            // 128-row scale tiles of W
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(acc_full_bar, 1);
+        ptx::mbar_init(acc_free_bar, 4);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(tmem_slot, kTmemCols);
+        ptx::tmem_relinquish<1>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_p;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (ptx::elect_one()) {
+            ptx::prefetch_tmap(&tm_a0);
+            ptx::prefetch_tmap(&tm_a1);
+            ptx::prefetch_tmap(&tm_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int b = t % p.nbatch, rest = t / p.nbatch;
+                const int mt = rest % m_tiles, nt = rest / m_tiles;
+                const CUtensorMap *tma = b ? &tm_a1 : &tm_a0;
+                const uint8_t *sfa = p.sfa[b] + int64_t(mt) * k_atoms * 512;
+                for (int kt = 0; kt < k_tiles; kt++, it++) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag))) break;
+                    const int atoms = min(2, k_atoms - 2 * kt);           // scale tiles in this stage
+                    const uint32_t sf_bytes = 512u * atoms;
+                    const uint32_t st = smem_base + s * C::STAGE_BYTES;
+                    // scale tiles of W rows past N do not exist; their products are never stored
+                    const int b_atoms = min(BN / 128, n_atoms - nt * (BN / 128));
+                    ptx::mbar_expect_tx(full_bar(s), C::A_BYTES + C::B_BYTES + sf_bytes * (1 + b_atoms));
+                    ptx::tma_load_2d(st, tma, kt * BKB, mt * BM, full_bar(s));
+                    ptx::tma_load_2d(st + C::A_BYTES, &tm_b, kt * BKB, nt * BN, full_bar(s));
+                    ptx::bulk_load(st + C::A_BYTES + C::B_BYTES, sfa + int64_t(kt) * 1024, sf_bytes, full_bar(s));
+                    for (int r = 0; r < b_atoms; r++)
+                        ptx::bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + r * 1024,
+                                       p.sfb + (int64_t(nt * (BN / 128) + r) * k_atoms + 2 * kt) * 512,
+                                       sf_bytes, full_bar(s));
+                }
+            }
+            // do not leave while the MMA side may still arrive on this CTA's barriers
+            for (int i = 0; i < C::STAGES && ok; i++, it++)
+                ok = ptx::mbar_wait(empty_bar(it % C::STAGES), ((it / C::STAGES) & 1) ^ 1, abort_flag);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_mxf4(BM, BN);
+            uint32_t it = 0;
+            int lt = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
+                if (lt > 0 && !(ok = ptx::mbar_wait(acc_free_bar, (lt - 1) & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0);
+                for (int kt = 0; kt < k_tiles; kt++, it++) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
+                    ptx::tc_fence_after();
+                    const int atoms = min(2, k_atoms - 2 * kt);
+                    const uint32_t st = smem_base + s * C::STAGE_BYTES;
+                    const uint32_t sfa_s = st + C::A_BYTES + C::B_BYTES, sfb_s = sfa_s + C::SFA_BYTES;
+                    for (int j = 0; j < atoms; j++) {
+                        ptx::tmem_cp_sf<1>(tmem_base + C::SFA_COL + 4 * j, ptx::desc_sf(sfa_s + 512 * j));
+#pragma unroll
+                        for (int r = 0; r < BN / 128; r++)
+                            ptx::tmem_cp_sf<1>(tmem_base + C::SFB_COL + (BN / 32) * j + 4 * r,
+                                               ptx::desc_sf(sfb_s + 1024 * r + 512 * j));
+                    }
+                    const uint64_t adesc = ptx::desc_sw128(st), bdesc = ptx::desc_sw128(st + C::A_BYTES);
+                    for (int kb = 0; kb < 2 * atoms; kb++) {
+                        const uint32_t id = (kb & 1) * 2u;                 // byte of the scale column
+                        ptx::mma_mxf4<1>(acc, adesc + 2 * kb, bdesc + 2 * kb,
+                                         idesc | (id << 29) | (id << 4),
+                                         tmem_base + C::SFA_COL + 4 * (kb >> 1) + (id << 30),
+                                         tmem_base + C::SFB_COL + (BN / 32) * (kb >> 1) + (id << 30),
+                                         (kt | kb) ? 1u : 0u);
+                    }
+                    ptx::tc_commit(empty_bar(s));
+                }
+                if (ok) ptx::tc_commit(acc_full_bar);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int q = warp & 3;                        // tensor-memory lane quarter of this warp
+        int lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
+            const int b = t % p.nbatch, rest = t / p.nbatch;
+            const int mt = rest % m_tiles, nt = rest / m_tiles;
+            if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
+            ptx::tc_fence_after();
+            const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
+            const int row = mt * BM + 32 * q + lane;
+            constexpr int CH = BN / 32;
+            // first chunk: the columns shared with the other accumulator
+            const int first = (C::OVL && !(lt & 1)) ? CH - 1 : 0;
+            for (int i = 0; i < CH; i++) {
+                const int c = (first + i) % CH;
+                uint32_t r[32];
+                ptx::tmem_ld32(acc + 32 * c, r);
+                ptx::tmem_ld_wait();
+                if (i == 0) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_free_bar);
+                }
+                store_chunk(p, p.c[b], row, nt * BN + 32 * c, r);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // give copies and MMAs still in flight time to land before memory is released
+        for (int i = 0; i < 4096; i++) __nanosleep(256);
+        if (threadIdx.x == 0) atomicExch(p.err, 1);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---- host ---------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn()
+{
+    static EncodeFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+// [rows, kbytes] bytes, K-contiguous; box = 128 bytes x box_rows, 128-byte swizzle
+int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kbytes, int box_rows)
+{
+    EncodeFn fn = encode_fn();
+    if (!fn) return fail(LS_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {cuuint64_t(kbytes), cuuint64_t(rows)};
+    cuuint64_t strides[1] = {cuuint64_t(kbytes)};
+    cuuint32_t box[2] = {cuuint32_t(BKB), cuuint32_t(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LS_ECUDA, "cuTensorMapEncodeTiled failed with %d", int(r));
+    return LS_OK;
+}
+
+int *error_word()
+{
+    // one device int per device, allocated on first use and kept for the process
+    static int *words[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(words[dev], 0, sizeof(int));
+    }
+    return words[dev];
+}
+
+template <int BN>
+int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
+           cudaStream_t st)
+{
+    using C = Cfg<BN>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    LS_CUDA(cudaGetDevice(&dev));
+    if (!attr_set[dev]) {
+        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        attr_set[dev] = true;
+    }
+    int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.nbatch;
+    int grid = tiles < sm_count() ? tiles : sm_count();
+    mxfp4_gemm_kernel<BN><<<grid, kGemmThreads, C::SMEM, st>>>(ta0, ta1, tb, p);
+    LS_LAUNCH_CHECK("mxfp4_gemm");
+    return LS_OK;
+}
+
+int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
+                const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
+                int64_t N, int64_t K, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (M < 0 || N < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a multiple of 128", (long long)K);
+    if (out_dtype != LS_F32 && out_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported output dtype %d", out_dtype);
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(LS_EINVAL, "dimension too large");
+    if (M == 0 || N == 0) return LS_OK;
+    if (K == 0) return fail(LS_EINVAL, "K must be positive");
+    const void *ptrs[] = {a0, w, sfa0, sfb, c0};
+    for (const void *q : ptrs)
+        if (!q) return fail(LS_EINVAL, "null pointer");
+    if (nbatch == 2 && (!a1 || !sfa1 || !c1)) return fail(LS_EINVAL, "null pointer (second batch)");
+    if (!aligned16(a0) || !aligned16(w) || !aligned16(sfa0) || !aligned16(sfb) || !aligned16(c0) ||
+        (nbatch == 2 && (!aligned16(a1) || !aligned16(sfa1) || !aligned16(c1))))
+        return fail(LS_EALIGN, "GEMM operands, scale buffers and outputs must be 16-byte aligned");
+    int *err = error_word();
+    if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
+    const int bn = 256;
+    CUtensorMap ta0, ta1, tb;
+    if (int rc = make_operand_map(&ta0, a0, M, K / 2, BM)) return rc;
+    if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, BM)) return rc;
+    if (int rc = make_operand_map(&tb, w, N, K / 2, bn)) return rc;
+    GemmParams p{};
+    p.sfa[0] = sfa0;
+    p.sfa[1] = nbatch == 2 ? sfa1 : sfa0;
+    p.sfb = sfb;
+    p.c[0] = c0;
+    p.c[1] = nbatch == 2 ? c1 : c0;
+    p.M = int(M), p.N = int(N), p.K = int(K);
+    p.nbatch = nbatch;
+    p.out_bf16 = out_dtype == LS_BF16;
+    p.err = err;
+    return launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace ls
+
+using namespace ls;
+
+extern "C" int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                             void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
+{
+    return gemm_common(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream);
+}
+
+extern "C" int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
+                                  const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
+                                  void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
+{
+    return gemm_common(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream);
+}
+
+extern "C" int ls_gemm_status(int *status_host)
+{
+    if (int rc = check_device()) return rc;
+    int *err = error_word();
+    if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
+    int v = 0;
+    LS_CUDA(cudaMemcpy(&v, err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v) LS_CUDA(cudaMemset(err, 0, sizeof(int)));
+    if (status_host) *status_host = v;
+    return v ? fail(LS_ETIMEOUT, "a GEMM kernel gave up waiting on a barrier") : LS_OK;
+}

@@ -1,0 +1,83 @@
+"""MXFP4 linear layer with the API of lockstep's fp4_linear.py.
+
+Forward: quantize activations and weights along K to MXFP4 and multiply on the
+block-scaled tensor cores (the reference does the same through Triton on an
+H100 and through dequantize + F.linear elsewhere, fp4_linear.py:33-40; the
+results agree with that second path within the GEMM tolerance).
+
+Backward, two modes:
+  "ste"    the reference's: straight-through matmuls in the incoming grad's
+           dtype, dX = gy @ w, dW = gy.T @ x (fp4_linear.py:42-45)
+  "mxfp4"  (extension) both backward GEMMs in MXFP4 too: dX contracts over the
+           output features, so gy and w.T are quantized along that axis; dW
+           contracts over tokens, so gy.T and x.T are quantized along tokens.
+
+There is no CPU path: on a device without block-scaled tensor cores the
+forward raises.
+"""
+
+import functools
+
+import torch
+import torch.nn as nn
+
+from . import fp4, mxfp4_gemm
+
+
+@functools.cache
+def kernel():
+    """The tcgen05 MXFP4 GEMM on an sm_100 device, else None (fp4_linear.py:16-25)."""
+    if not torch.cuda.is_available() or torch.cuda.get_device_capability()[0] != 10:
+        return None
+    return mxfp4_gemm.mxfp4_gemm_packed
+
+
+def path():
+    return "tcgen05-mxfp4" if kernel() else "unavailable"
+
+
+def _gemm(a, b_t, out_dtype):
+    """a [M, K] @ b_t [N, K].T with both operands quantized along K."""
+    k = kernel()
+    if k is None:
+        raise RuntimeError("MXFP4Linear needs an sm_100 GPU (there is no CPU or fake-quant fallback)")
+    pa, sa = fp4.quantize_mxfp4_packed(a)
+    pb, sb = fp4.quantize_mxfp4_packed(b_t)
+    return k(pa, pb, sa, sb, out_dtype=out_dtype)
+
+
+class _MXFP4Matmul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, backward_mode="ste"):
+        ctx.save_for_backward(x, w)
+        ctx.backward_mode = backward_mode
+        return _gemm(x, w, x.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        if ctx.backward_mode == "ste":
+            return (gy @ w.to(gy.dtype)).to(x.dtype), (gy.t() @ x.to(gy.dtype)).to(w.dtype), None
+        gy = gy.contiguous()
+        gx = _gemm(gy, w.t().contiguous(), x.dtype)                           # [T, K], contract over N
+        gw = _gemm(gy.t().contiguous(), x.t().contiguous(), torch.float32)    # [N, K], contract over T
+        return gx, gw.to(w.dtype), None
+
+
+class MXFP4Linear(nn.Linear):
+    """nn.Linear whose forward GEMM runs in MXFP4 (bias unsupported)."""
+
+    def __init__(self, fan_in, fan_out, bias=False, backward="ste"):
+        assert not bias, "MXFP4Linear has no bias"
+        assert backward in ("ste", "mxfp4")
+        super().__init__(fan_in, fan_out, bias=False)
+        self.backward_mode = backward
+
+    def forward(self, x):
+        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+        with torch.autocast("cuda", enabled=False):
+            y = _MXFP4Matmul.apply(x.reshape(-1, x.shape[-1]).to(dt), self.weight, self.backward_mode)
+        return y.view(*x.shape[:-1], -1)
+
+
+FP4Linear = MXFP4Linear

@@ -1,0 +1,84 @@
+"""Packed MXFP4 GEMM with the API of lockstep's mxfp4_gemm.py, on tcgen05.
+
+`mxfp4_gemm_packed` and `mxfp4_gemm_fp8` keep the reference signatures
+(mxfp4_gemm.py:74-87, :161-174).  The reference emulates the block-scaled
+product on Hopper FP8 tensor cores through Triton; here one hand-written
+sm_100a kernel feeds packed E2M1 operands and UE8M0 block scales straight to
+`tcgen05.mma.kind::mxf4.block_scale`, accumulating in tensor memory.
+
+Scales may be given as the reference does (fp32 powers of two, [rows, K//32])
+or, to skip a conversion pass, as the uint8 scale-factor buffer that
+`fp4.quantize_mxfp4_packed` produces.
+"""
+
+import torch
+
+from . import _lib, fp4
+from ._lib import check, lib, need_cuda, ptr, stream
+
+# The reference exports its Triton launch config under this name
+# (mxfp4_gemm.py:23); here it documents the fixed tile shape of the kernel.
+CFG = dict(BLOCK_M=128, BLOCK_N=256, BLOCK_K=256, num_stages=4, num_warps=6)
+
+
+def _sf(scale, rows, K):
+    """fp32 [rows, K//32] scales -> scale-factor bytes; uint8 buffers pass through."""
+    if scale.dtype == torch.uint8:
+        assert scale.numel() == fp4.sf_bytes(rows, K), "scale-factor buffer has the wrong size"
+        return scale.contiguous()
+    assert scale.shape == (rows, K // 32), f"scale shape {tuple(scale.shape)} != {(rows, K // 32)}"
+    sf, _bad = fp4.scales_to_sf(scale)
+    return sf
+
+
+def mxfp4_gemm_packed(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloat16):
+    """a_pk [M, K//2] uint8, bt_pk [N, K//2] uint8 (both K-contiguous, even
+    index in the low nibble), a_scale [M, K//32], b_scale [N, K//32].
+    Returns C = A @ B_T.T as [M, N] of out_dtype (bf16 or fp32)."""
+    need_cuda(a_pk, bt_pk, a_scale, b_scale)
+    M, Kh = a_pk.shape
+    N, Kh2 = bt_pk.shape
+    K = Kh * 2
+    assert Kh == Kh2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
+    a_pk, bt_pk = a_pk.contiguous(), bt_pk.contiguous()
+    sfa, sfb = _sf(a_scale, M, K), _sf(b_scale, N, K)
+    c = torch.empty((M, N), device=a_pk.device, dtype=out_dtype)
+    check(lib().ls_mxfp4_gemm(ptr(a_pk), ptr(bt_pk), ptr(sfa), ptr(sfb), ptr(c), _lib.dtype_code(out_dtype),
+                              M, N, K, stream()))
+    return c
+
+
+_E4M3_TO_CODE = None
+
+
+def _e4m3_to_codes(x_fp8):
+    """Inverse of fp4.codes_to_e4m3 for bytes on the E2M1 grid."""
+    global _E4M3_TO_CODE
+    if _E4M3_TO_CODE is None or _E4M3_TO_CODE.device != x_fp8.device:
+        t = torch.full((256,), 255, dtype=torch.uint8)
+        t[fp4.E2M1_TO_E4M3.long()] = torch.arange(16, dtype=torch.uint8)
+        _E4M3_TO_CODE = t.to(x_fp8.device)
+    return _E4M3_TO_CODE[x_fp8.view(torch.uint8).long()]
+
+
+def mxfp4_gemm_fp8(a_fp8, b_fp8, a_scale, b_scale, out_dtype=torch.bfloat16):
+    """a_fp8 [M, K] K-contiguous, b_fp8 [K, N] N-contiguous, both E4M3 bytes
+    holding E2M1 values; a_scale [M, K//32], b_scale [K//32, N]
+    (mxfp4_gemm.py:74-87).  The operands are re-encoded to packed E2M1 (the
+    tensor core takes them natively) and go through the packed kernel."""
+    need_cuda(a_fp8, b_fp8, a_scale, b_scale)
+    M, K = a_fp8.shape
+    K2, N = b_fp8.shape
+    assert K == K2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
+    assert a_scale.shape == (M, K // 32) and b_scale.shape == (K // 32, N)
+    a_codes = _e4m3_to_codes(a_fp8)
+    b_codes = _e4m3_to_codes(b_fp8.t().contiguous())
+    assert int(torch.maximum(a_codes.max(), b_codes.max())) < 16, "operands must hold E2M1 values"
+    return mxfp4_gemm_packed(fp4.pack_fp4(a_codes), fp4.pack_fp4(b_codes), a_scale,
+                             b_scale.t().contiguous(), out_dtype)
+
+
+def gemm_status():
+    """Raises if a GEMM kernel launched since the last call gave up on a
+    bounded wait (a protocol fault; results are then undefined)."""
+    check(lib().ls_gemm_status(None))

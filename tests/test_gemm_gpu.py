@@ -1,0 +1,170 @@
+"""GPU parity of the tcgen05 MXFP4 GEMM (single and dual batch) through the
+C ABI.  Known-answer first (unit scales, integer-valued products: bit-exact),
+then the reference's dequantize + fp32 matmul path within the stated
+tolerance: rel-L2 <= 1e-3 and max-abs <= 2e-2 * ||row||_inf, both outputs in
+the same dtype."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_port
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from lockstep_b200 import dual_gemm, fp4, mxfp4_gemm
+    yield fp4, mxfp4_gemm, dual_gemm
+    mxfp4_gemm.gemm_status()
+
+
+def _check(c, ref, what=""):
+    c, ref = c.float().cpu(), ref.float().cpu()
+    rel = ((c - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+    row_inf = ref.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
+    worst = ((c - ref).abs() / row_inf).max().item()
+    assert rel <= 1e-3 and worst <= 2e-2, f"{what}: rel-L2 {rel:.3e}, max-abs/row-inf {worst:.3e}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (128, 256, 256), (256, 256, 128), (128, 512, 1024)])
+def test_unit_scale_bit_exact(mods, M, N, K):
+    # design of the reference's bench.py:41-57: unit scales, integer grid, exact
+    fp4, mg, _ = mods
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    ac = torch.randint(0, 16, (M, K), dtype=torch.uint8, device="cuda", generator=g)
+    bc = torch.randint(0, 16, (N, K), dtype=torch.uint8, device="cuda", generator=g)
+    ones_a = torch.ones(M, K // 32, device="cuda")
+    ones_b = torch.ones(N, K // 32, device="cuda")
+    c = mg.mxfp4_gemm_packed(fp4.pack_fp4(ac), fp4.pack_fp4(bc), ones_a, ones_b, out_dtype=torch.float32)
+    mg.gemm_status()
+    want = (fp4.codes_to_q(ac).double() @ fp4.codes_to_q(bc).double().t()) / 4
+    assert torch.equal(c.double(), want)
+
+
+def test_one_hot_nibble_order(mods):
+    # a single non-zero code at an odd and an even K index must land on the right product
+    fp4, mg, _ = mods
+    M, N, K = 128, 256, 128
+    for ka in (0, 1, 33, 126):
+        ac = torch.zeros(M, K, dtype=torch.uint8, device="cuda")
+        bc = torch.zeros(N, K, dtype=torch.uint8, device="cuda")
+        ac[5, ka] = 6           # 4.0
+        bc[:, :] = 2            # 1.0 everywhere
+        bc[7, ka] = 13          # -3.0
+        sa = torch.ones(M, K // 32, device="cuda")
+        sb = torch.ones(N, K // 32, device="cuda")
+        c = mg.mxfp4_gemm_packed(fp4.pack_fp4(ac), fp4.pack_fp4(bc), sa, sb, out_dtype=torch.float32)
+        want = torch.zeros(M, N)
+        want[5, :] = 4.0
+        want[5, 7] = -12.0
+        assert torch.equal(c.cpu(), want), ka
+
+
+def test_block_scales_exact_powers(mods):
+    # random power-of-two scales: products stay exactly representable in fp32
+    fp4, mg, _ = mods
+    M, N, K = 256, 512, 512
+    g = torch.Generator(device="cuda").manual_seed(7)
+    ac = torch.randint(0, 16, (M, K), dtype=torch.uint8, device="cuda", generator=g)
+    bc = torch.randint(0, 16, (N, K), dtype=torch.uint8, device="cuda", generator=g)
+    sa = torch.exp2(torch.randint(-3, 4, (M, K // 32), device="cuda", generator=g).float())
+    sb = torch.exp2(torch.randint(-3, 4, (N, K // 32), device="cuda", generator=g).float())
+    c = mg.mxfp4_gemm_packed(fp4.pack_fp4(ac), fp4.pack_fp4(bc), sa, sb, out_dtype=torch.float32)
+    mg.gemm_status()
+    want = fp4.dequantize_mxfp4(ac, sa).double() @ fp4.dequantize_mxfp4(bc, sb).double().t()
+    assert torch.equal(c.double(), want)       # |sum| < 2^24 quarter units: exact
+
+
+def test_config1_against_oracle(mods):
+    # A 256x1024 N(0,1) seed 0, W 1024x1024 N(0,0.02) seed 1, bf16
+    fp4, mg, _ = mods
+    a = torch.randn(256, 1024, generator=torch.Generator().manual_seed(0)).bfloat16()
+    w = (torch.randn(1024, 1024, generator=torch.Generator().manual_seed(1)) * 0.02).bfloat16()
+    ac, asc = ref_port.quantize(a)
+    wc, wsc = ref_port.quantize(w)
+    ref = ref_port.gemm_fake_quant(ac, asc, wc, wsc)                 # bf16
+    pa, sfa = fp4.quantize_mxfp4_packed(a.cuda())
+    pw, sfw = fp4.quantize_mxfp4_packed(w.cuda())
+    assert torch.equal(pa.cpu(), ref_port.pack(ac)) and torch.equal(pw.cpu(), ref_port.pack(wc))
+    c = mg.mxfp4_gemm_packed(pa, pw, sfa, sfw)
+    mg.gemm_status()
+    _check(c, ref, "config 1")
+    c32 = mg.mxfp4_gemm_packed(pa, pw, asc.cuda(), wsc.cuda(), out_dtype=torch.float32)
+    _check(c32, ref_port.gemm_fp64(ac, asc, wc, wsc), "config 1 fp32 vs fp64")
+    assert torch.equal(c32.bfloat16(), c)       # epilogue rounding = torch's round-to-nearest-even
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (16, 384, 256), (130, 200, 384), (257, 1000, 640),
+                                   (128, 8, 128), (300, 264, 1152)])
+def test_ragged_shapes(mods, M, N, K):
+    fp4, mg, _ = mods
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    ac, asc = ref_port.quantize(a)
+    wc, wsc = ref_port.quantize(w)
+    pa, sfa = fp4.quantize_mxfp4_packed(a.cuda())
+    pw, sfw = fp4.quantize_mxfp4_packed(w.cuda())
+    for dt in (torch.bfloat16, torch.float32):
+        guard = torch.full((M + 2, N), 777.0, device="cuda", dtype=dt)
+        c = mg.mxfp4_gemm_packed(pa, pw, sfa, sfw, out_dtype=dt)
+        mg.gemm_status()
+        _check(c, ref_port.gemm_fake_quant(ac, asc, wc, wsc, dt), f"{M}x{N}x{K} {dt}")
+        assert (guard == 777.0).all()
+
+
+def test_fp8_entry(mods):
+    fp4, mg, _ = mods
+    M, N, K = 128, 256, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    ac = fp4.random_codes((M, K), device="cuda")
+    bc = fp4.random_codes((K, N), device="cuda")
+    sa = torch.exp2(torch.randint(-2, 3, (M, K // 32), device="cuda", generator=g).float())
+    sb = torch.exp2(torch.randint(-2, 3, (K // 32, N), device="cuda", generator=g).float())
+    c = mg.mxfp4_gemm_fp8(fp4.codes_to_e4m3(ac), fp4.codes_to_e4m3(bc), sa, sb, out_dtype=torch.float32)
+    want = fp4.reference_mxfp4_gemm(ac, sa, bc, sb)
+    assert torch.allclose(c, want, rtol=1e-6, atol=0)
+
+
+def test_dual_matches_two_singles_and_oracle(mods):
+    fp4, mg, dg = mods
+    M, N, K = 384, 768, 1024
+    g = torch.Generator().manual_seed(11)
+    x1 = torch.randn(M, K, generator=g).bfloat16()
+    x2 = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    pw, sfw = fp4.quantize_mxfp4_packed(w.cuda())
+    c1, c2 = dg.dual_mxfp4(x1.cuda(), x2.cuda(), pw, sfw)
+    mg.gemm_status()
+    wc, wsc = ref_port.quantize(w)
+    for x, c in ((x1, c1), (x2, c2)):
+        xc, xs = ref_port.quantize(x)
+        _check(c, ref_port.gemm_fake_quant(xc, xs, wc, wsc), "dual")
+        p, sf = fp4.quantize_mxfp4_packed(x.cuda())
+        assert torch.equal(mg.mxfp4_gemm_packed(p, pw, sf, sfw), c)     # same kernel, same order: same bits
+
+
+def test_linearity_full_size(mods):
+    """Config-2 sized property check (2 x 4096x8192 @ 8192x8192): scaling a
+    batch's block scales by 2 doubles its output exactly; the other batch is
+    untouched; a sampled set of rows agrees with the oracle."""
+    fp4, mg, dg = mods
+    M, N, K = 4096, 8192, 8192
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x1 = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    x2 = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+    pw, sfw = fp4.quantize_mxfp4_packed(w)
+    p1, s1, sc1 = fp4.quantize_mxfp4_packed(x1, want_scale=True)
+    p2, s2 = fp4.quantize_mxfp4_packed(x2)
+    c1, c2 = dg.dual_mxfp4_packed(p1, p2, pw, s1, s2, sfw, out_dtype=torch.float32)
+    d1, d2 = dg.dual_mxfp4_packed(p1, p2, pw, sc1 * 2, s2, sfw, out_dtype=torch.float32)
+    mg.gemm_status()
+    assert torch.equal(d1, c1 * 2) and torch.equal(d2, c2)
+    rows = torch.tensor([0, 1, 127, 128, 2047, 4095])
+    wc, wsc = ref_port.quantize(w.cpu())
+    for x, c in ((x1, c1), (x2, c2)):
+        xc, xs = ref_port.quantize(x[rows.cuda()].cpu())
+        _check(c[rows.cuda()], ref_port.gemm_fake_quant(xc, xs, wc, wsc, torch.float32), "config 2 rows")
