@@ -1,0 +1,284 @@
+"""Benchmark of the MXFP4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one pass of the hot path over one synthetic batch of the dual-batch
+configuration: two activation batches of 4096 x 8192 bf16 are quantized to
+MXFP4 on the fly and multiplied, in one launch, by one pre-quantized
+8192 x 8192 MXFP4 weight (two 4096 x 8192 bf16 outputs, fp32 accumulation).
+With N > 1 every rank runs this step on its own GPU (the GEMM path does not
+shard: replicas only) and the line reports the aggregate.
+
+Prints one JSON line (rank 0).  `value` is device-timed with inputs resident
+in HBM; `e2e` is the same step through the public Python API with pinned HOST
+buffers, host<->device copies inside the timed region.
+
+`--impl reference` times the reference's own CPU path for the same step
+(quantize both batches, dequantize, fp32 F.linear: what lockstep's
+fp4_linear.py runs anywhere but on an H100) on the host cores, on a bounded
+row sample of the batch.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M, N, K = 4096, 8192, 8192
+FLOPS_PER_STEP = 2 * 2 * M * N * K                      # two batches
+METRIC = "dual MXFP4 GEMM TFLOPS/GPU (% FP4 peak); FP4 all-reduce algbw GB/s @1/2/4/8"
+WORKLOAD = "dual-batch packed MXFP4 GEMM: 2 x [4096x8192 bf16, quantized on the fly] @ 8192x8192 MXFP4 W -> 2 x 4096x8192 bf16"
+FP4_SPEC_TFLOPS = 9000.0
+CPU_SAMPLE_ROWS = 256                                   # rows per batch in the CPU-baseline sample
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.proc, self.path = None, None
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", uuid, f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+            t0 = time.time()                       # wait until the sampler is actually running
+            while time.time() - t0 < 5.0 and os.path.getsize(self.path) == 0:
+                time.sleep(0.02)
+            self.skip = len(Path(self.path).read_text().splitlines())
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        self.out.close()
+        rows = [r.split(",") for r in Path(self.path).read_text().splitlines()[self.skip:] if r.count(",") >= 6]
+        os.unlink(self.path)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[0]) for r in rows]
+        power = [float(r[2]) for r in rows if r[2].strip().replace(".", "").isdigit()]
+        busy = [s for s, r in zip(sm, rows)] if not power else \
+            [s for s, pw in zip(sm, power) if pw > 0.5 * max(power)] or sm
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any("Active" == r[3 + i].strip() for r in rows)]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": float(rows[0][1]), "reasons": reasons,
+                "samples": len(rows), "power_w_max": max(power) if power else None}
+
+
+def cpu_reference_step(rows, threads=None):
+    """The reference's CPU path for `rows` rows of each batch; returns
+    (seconds, flops).  Uses the oracle port: this leg is the one place the
+    benchmark may execute it."""
+    from oracle import ref_port
+    if threads:
+        torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    x1 = torch.randn(rows, K, generator=g).bfloat16()
+    x2 = torch.randn(rows, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    wc, ws = ref_port.quantize(w)                          # W is pre-quantized in this configuration
+    t0 = time.perf_counter()
+    outs = []
+    for x in (x1, x2):
+        xc, xs = ref_port.quantize(x)
+        outs.append(torch.nn.functional.linear(ref_port.dequantize(xc, xs),
+                                               ref_port.dequantize(wc, ws)).to(torch.bfloat16))
+    dt = time.perf_counter() - t0
+    return dt, 2 * 2 * rows * N * K
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    args.steps = min(args.steps, 5)          # each step is seconds of CPU work
+    cores = torch.get_num_threads()
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_step(CPU_SAMPLE_ROWS)
+    times = []
+    flops = 0
+    for _ in range(args.steps):
+        dt, flops = cpu_reference_step(CPU_SAMPLE_ROWS)
+        times.append(dt)
+    t = sum(times) / len(times)
+    val = flops / t / 1e12
+    sample = f"{CPU_SAMPLE_ROWS} of {M} rows of each batch, full 8192x8192 W, oracle port of fp4.py/fp4_linear.py on torch CPU"
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3 * (M / CPU_SAMPLE_ROWS),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4 (e2m1 x ue8m0), fp32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
+    args = ap.parse_args()
+    rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from lockstep_b200 import dual_gemm, fp4, mxfp4_gemm
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    m = 1024 if args.small else M
+    flops_step = 2 * 2 * m * N * K
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x1 = torch.randn(m, K, device=dev, generator=g).bfloat16()
+    x2 = torch.randn(m, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
+    w_pk, w_sf = fp4.quantize_mxfp4_packed(w)
+    del w
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)        # > 126 MB L2
+
+    def step():
+        p1, s1 = fp4.quantize_mxfp4_packed(x1)
+        p2, s2 = fp4.quantize_mxfp4_packed(x2)
+        return p1, p2, s1, s2
+
+    for _ in range(max(args.warmup, 3)):
+        p1, p2, s1, s2 = step()
+        dual_gemm.dual_mxfp4_packed(p1, p2, w_pk, s1, s2, w_sf)
+    mxfp4_gemm.gemm_status()
+
+    # ---- device-timed: inputs resident in HBM, L2 flushed between steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    sampler = ClockSampler(dev) if rank == 0 else None
+    for i in range(args.steps):
+        flush.zero_()
+        ev[i][0].record()
+        p1, p2, s1, s2 = step()
+        ev[i][1].record()
+        c1, c2 = dual_gemm.dual_mxfp4_packed(p1, p2, w_pk, s1, s2, w_sf)
+        ev[i][2].record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    mxfp4_gemm.gemm_status()
+    step_ms = sum(e[0].elapsed_time(e[2]) for e in ev)
+    gemm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    quant_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+
+    # ---- end to end: pinned host buffers in, pinned host buffers out, every step
+    hx1, hx2 = x1.cpu().pin_memory(), x2.cpu().pin_memory()
+    hc = torch.empty((2, m, N), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        d1 = hx1.to(dev, non_blocking=True)
+        d2 = hx2.to(dev, non_blocking=True)
+        o1, o2 = dual_gemm.dual_mxfp4(d1, d2, w_pk, w_sf)
+        hc[0].copy_(o1, non_blocking=True)
+        hc[1].copy_(o2, non_blocking=True)
+
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record()
+        barrier()
+        e2e_ms = a.elapsed_time(b) / e2e_steps
+
+    t = torch.tensor([step_ms, e2e_ms, gemm_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms_max, e2e_ms_max, gemm_ms_max = t.tolist()
+
+    if rank == 0:
+        pk = peaks()
+        value = world * flops_step * args.steps / (step_ms_max * 1e-3) / 1e12
+        gemm_tflops = flops_step / (gemm_ms * 1e-3) / 1e12
+        fp4_peak = 4 * pk["bf16"]
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": step_ms_max / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4 (e2m1 x ue8m0), fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD if not args.small else WORKLOAD.replace("4096x8192 bf16", "1024x8192 bf16"),
+                       "step": "quantize A1, A2 (2 launches) + dual GEMM (1 launch); W pre-quantized",
+                       "parallelism": f"replicas x{world}", "l2": "256 MiB buffer written between timed steps",
+                       "quantize_ms": quant_ms, "gemm_ms": gemm_ms},
+            "e2e": {"value": world * flops_step / (e2e_ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": hx1.numel() * 2 * 2, "d2h_bytes_per_step": hc.numel() * 2,
+                    "ms_per_step": e2e_ms_max},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_kernel<256> (dual batch)",
+                         "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
+                         "peak_source": f"4 x {pk['source']} bf16 burst {pk['bf16']} (no FP4 figure is measured); "
+                                        f"spec dense FP4 {FP4_SPEC_TFLOPS}",
+                         "frac_of_spec": gemm_tflops / FP4_SPEC_TFLOPS,
+                         "traffic": None},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            dt, fl = cpu_reference_step(CPU_SAMPLE_ROWS)
+            dt2, fl = cpu_reference_step(CPU_SAMPLE_ROWS)
+            line["cpu_baseline"] = {"value": fl / min(dt, dt2) / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                                    "kind": "port",
+                                    "sample": f"{CPU_SAMPLE_ROWS} of {M} rows of each batch against the full W, best of 2"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
