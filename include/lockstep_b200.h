@@ -115,6 +115,26 @@ int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t
  * raw word.  Blocks until prior work on the default stream is done. */
 int ls_gemm_status(int *status_host);
 
+/* MXFP4 linear forward without any allocation: quantizes x [M, K] (LS_BF16 or
+ * LS_F32) to MXFP4 and multiplies by a pre-quantized weight (w_pk [N, K/2],
+ * w_sf its scale-factor buffer), c [M, N] as in ls_mxfp4_gemm.  No counterpart
+ * in lockstep; added for callers that may not call cudaMalloc (a plugin
+ * inside a host's fixed memory plan, a loop that cannot afford an
+ * allocation's device-wide synchronisation).  The temporaries between the
+ * two kernels live in a 9.3 MB array inside the library image instead:
+ *   - limit: M * K <= 2^24 elements and ls_sf_bytes(M, K) <= 2^20; larger
+ *     shapes return LS_EINVAL;
+ *   - the first call on each device looks the array's address up
+ *     (cudaGetSymbolAddress); make that call before any stream capture;
+ *   - all calls on a device share the array: calls that may overlap on the GPU
+ *     (different streams) race; calls on one stream are safe.
+ * status (device int32, may be NULL) receives 0, or non-zero if the GEMM kernel
+ * abandoned a bounded wait.  Results equal ls_quantize_mxfp4 + ls_mxfp4_gemm
+ * bit for bit. */
+int ls_mxfp4_linear_noalloc(const void *x, int x_dtype, const uint8_t *w_pk, const uint8_t *w_sf,
+                            void *c, int out_dtype, int64_t M, int64_t N, int64_t K,
+                            int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -286,19 +286,6 @@ int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kby
     return LS_OK;
 }
 
-int *error_word()
-{
-    // one device int per device, allocated on first use and kept for the process
-    static int *words[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!words[dev]) {
-        if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
-        cudaMemset(words[dev], 0, sizeof(int));
-    }
-    return words[dev];
-}
-
 template <int BN>
 int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
            cudaStream_t st)
@@ -318,9 +305,27 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
     return LS_OK;
 }
 
+}  // namespace
+
+int *error_word()
+{
+    // one device int per device, allocated on first use and kept for the process
+    static int *words[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!words[dev]) {
+        if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(words[dev], 0, sizeof(int));
+    }
+    return words[dev];
+}
+
+// Shared by the public entry points.  `err` = device int that a kernel sets when
+// a bounded wait runs out; NULL selects the per-device word that
+// ls_gemm_status reads (allocated on first use).
 int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
                 const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
-                int64_t N, int64_t K, void *stream)
+                int64_t N, int64_t K, void *stream, int *err)
 {
     if (int rc = check_device()) return rc;
     if (M < 0 || N < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a multiple of 128", (long long)K);
@@ -335,7 +340,7 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     if (!aligned16(a0) || !aligned16(w) || !aligned16(sfa0) || !aligned16(sfb) || !aligned16(c0) ||
         (nbatch == 2 && (!aligned16(a1) || !aligned16(sfa1) || !aligned16(c1))))
         return fail(LS_EALIGN, "GEMM operands, scale buffers and outputs must be 16-byte aligned");
-    int *err = error_word();
+    if (!err) err = error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     const int bn = 256;
     CUtensorMap ta0, ta1, tb;
@@ -355,7 +360,6 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     return launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
 }
 
-}  // namespace
 }  // namespace ls
 
 using namespace ls;
@@ -363,20 +367,20 @@ using namespace ls;
 extern "C" int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
                              void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
 {
-    return gemm_common(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream);
+    return gemm_common(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream, nullptr);
 }
 
 extern "C" int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
                                   const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
                                   void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
 {
-    return gemm_common(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream);
+    return gemm_common(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream, nullptr);
 }
 
 extern "C" int ls_gemm_status(int *status_host)
 {
     if (int rc = check_device()) return rc;
-    int *err = error_word();
+    int *err = ls::error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     int v = 0;
     LS_CUDA(cudaMemcpy(&v, err, sizeof(int), cudaMemcpyDeviceToHost));
