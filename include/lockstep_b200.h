@@ -115,6 +115,46 @@ int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t
  * raw word.  Blocks until prior work on the default stream is done. */
 int ls_gemm_status(int *status_host);
 
+/* ---- FP4-compressed gradient all-reduce --------------------------------------
+ * Replaces the transport of wire.py:104-138 (Wire._integer: quantize, send each
+ * chunk to its owner, owner sums and re-encodes, gather) with the fp4.py codec
+ * as payload (block 32, 16 packed bytes + 1 UE8M0 byte): a reduce-scatter and
+ * an all-gather done by direct peer stores over NVLink.  One handle per Wire
+ * object and rank; at most 8 ranks, one process per GPU.
+ *   padded   elements covered, a positive multiple of world * 256
+ * Set-up: ls_wire_create, exchange ls_wire_local_handle blobs
+ * (ls_wire_handle_bytes each) through the process group, ls_wire_map_peers with
+ * all blobs in rank order.  ls_wire_map_local instead connects handles created
+ * in one process (single-GPU emulation of several ranks, used by the tests).
+ * ls_wire_create allocates the rank's receive arena and synchronises. */
+int64_t ls_wire_handle_bytes(void);
+int ls_wire_create(int rank, int world, int64_t padded, void **handle);
+int ls_wire_destroy(void *handle);
+int ls_wire_local_handle(void *handle, void *blob_host);
+int ls_wire_map_peers(void *handle, const void *all_blobs_host);
+int ls_wire_map_local(void *handle, void *const *handles_host);
+
+/* In-place average of g[numel] (fp32) over the ranks: the three phases of one
+ * step, enqueued on `stream`.  res [padded] / ores [padded / world] are the
+ * sender / owner error-feedback residuals (wire.py:109-111,128-135), updated in
+ * place; NULL disables error feedback.  reverse != 0 sums senders in
+ * descending order (wire.py:122-123).  Every rank must make the same calls in
+ * the same order.  ls_wire_allreduce = send + reduce + finish. */
+int ls_wire_send(void *handle, const float *g, int64_t numel, float *res, void *stream);
+int ls_wire_reduce(void *handle, float *ores, int reverse, void *stream);
+int ls_wire_finish(void *handle, float *g, int64_t numel, void *stream);
+int ls_wire_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, int reverse,
+                      void *stream);
+
+/* Synchronising: LS_ETIMEOUT (and clears it) if a wire kernel gave up waiting
+ * for a peer since the last call.  status_host (host int) may be NULL. */
+int ls_wire_status(void *handle, int *status_host);
+
+/* Copies the raw receive slots (which = 0) or gather slots (1) of this rank,
+ * world x slot bytes, to a device buffer; *slot_bytes_host receives the slot
+ * size.  For byte-exact checks of the wire format. */
+int ls_wire_debug_slots(void *handle, int which, uint8_t *out, int64_t *slot_bytes_host, void *stream);
+
 /* MXFP4 linear forward without any allocation: quantizes x [M, K] (LS_BF16 or
  * LS_F32) to MXFP4 and multiplies by a pre-quantized weight (w_pk [N, K/2],
  * w_sf its scale-factor buffer), c [M, N] as in ls_mxfp4_gemm.  No counterpart

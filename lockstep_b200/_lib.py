@@ -28,6 +28,18 @@ _SIGS = {
     "ls_mxfp4_gemm_dual": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_gemm_status": (c_int, [c_vp]),
     "ls_mxfp4_linear_noalloc": (c_int, [c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
+    "ls_wire_handle_bytes": (c_i64, []),
+    "ls_wire_create": (c_int, [c_int, c_int, c_i64, ctypes.POINTER(c_vp)]),
+    "ls_wire_destroy": (c_int, [c_vp]),
+    "ls_wire_local_handle": (c_int, [c_vp, c_vp]),
+    "ls_wire_map_peers": (c_int, [c_vp, c_vp]),
+    "ls_wire_map_local": (c_int, [c_vp, ctypes.POINTER(c_vp)]),
+    "ls_wire_send": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp]),
+    "ls_wire_reduce": (c_int, [c_vp, c_vp, c_int, c_vp]),
+    "ls_wire_finish": (c_int, [c_vp, c_vp, c_i64, c_vp]),
+    "ls_wire_allreduce": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_vp]),
+    "ls_wire_status": (c_int, [c_vp, c_vp]),
+    "ls_wire_debug_slots": (c_int, [c_vp, c_int, c_vp, ctypes.POINTER(c_i64), c_vp]),
     "ls_scales_to_sf": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
 }
 

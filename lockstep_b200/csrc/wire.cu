@@ -1,0 +1,443 @@
+// FP4-compressed gradient all-reduce: reduce-scatter + all-gather by direct
+// peer stores over NVLink, one process per GPU.
+//
+// Protocol (lockstep wire.py:104-138 with the fp4.py codec in place of the
+// integer grid; every rank owns one contiguous shard of the padded buffer):
+//   send    v = g + res; encode v to MXFP4 (16 packed bytes + 1 exponent byte
+//           per 32 values); res = v - decode; store shard o's bytes straight
+//           into owner o's receive slot [my rank]; raise flag[my rank] on o
+//   reduce  owner: wait for every sender's flag; val = sum of the decoded
+//           slots in ascending sender order from +0.0 (each add rounded to
+//           fp32); val += ores; encode; ores = val - decode; store the result
+//           into every rank's gather slot [my rank]; raise the gather flag
+//   finish  wait for every owner's gather flag; g = decode(all shards) / world
+// NCCL/gloo only carries the 64-byte IPC handles at set-up.  The three phases
+// are three launches on the caller's stream; a phase only ever waits for
+// kernels of OTHER GPUs (bounded, reported through the status word).
+// All arithmetic uses explicitly rounded intrinsics so that no multiply-add
+// contraction changes a bit against the CPU oracle.
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace ls {
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kThreads = 256;
+constexpr uint32_t kPollLimit = 1u << 22;     // x ~100 ns
+
+struct Header {                 // start of every rank's arena
+    uint32_t rs_flag[kMaxWorld];    // epoch of the last completed send from rank s
+    uint32_t ag_flag[kMaxWorld];    // epoch of the last completed reduce of owner o
+    uint32_t counter[2];            // CTA completion counters (send, reduce)
+    uint32_t status;                // non-zero: a wait ran out
+};
+constexpr size_t kHeaderBytes = 256;
+
+struct Peers { uint8_t *arena[kMaxWorld]; };
+
+struct WireGeom {
+    int rank, world;
+    int64_t padded, shard;          // elements
+    int64_t slot_bytes;             // packed + exponent bytes of one shard, 256-aligned
+    int64_t rs_off, ag_off;         // byte offsets of the slot arrays in an arena
+};
+
+struct Wire {
+    WireGeom g;
+    int dev;
+    size_t arena_bytes;
+    uint8_t *arena;
+    Peers peers;
+    bool mapped, opened[kMaxWorld];
+    uint32_t epoch;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One thread per CTA polls; returns after the flags of all `world` ranks reached `epoch`.
+__device__ __forceinline__ void wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch)
+{
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < world; s++) {
+            uint32_t polls = 0;
+            while (int32_t(ld_acquire_sys(flags + s) - epoch) < 0) {
+                if (++polls > kPollLimit) {
+                    atomicExch(&h->status, 1u);
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// After this CTA's stores: the last CTA of the grid raises flag[rank] = epoch on every peer.
+__device__ __forceinline__ void signal_done(Header *mine, uint32_t *counter, const Peers &peers, int world,
+                                            int rank, size_t flag_off, uint32_t epoch)
+{
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t done = atomicAdd(counter, 1u);
+        if (done == gridDim.x - 1) {
+            *counter = 0;
+            __threadfence_system();
+            for (int p = 0; p < world; p++)
+                st_release_sys(reinterpret_cast<uint32_t *>(peers.arena[p] + flag_off) + rank, epoch);
+        }
+    }
+}
+
+// Encodes 8 values held by this thread (4 adjacent lanes share a block of 32).
+// Returns packed nibbles; e8 = exponent byte of the block; dq[] = decoded values.
+__device__ __forceinline__ uint32_t encode8(const float (&v)[8], uint32_t &e8, float (&dq)[8])
+{
+    uint32_t amax = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = max(amax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    e8 = block_e8m0(amax);
+    const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+    const float sc = __uint_as_float(scale_bits(e8));
+    uint32_t pk = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        uint32_t c = e2m1_code<false>(__fmul_rn(v[i], inv));
+        pk |= c << (4 * i);
+        dq[i] = __fmul_rn(e2m1_value(c), sc);
+    }
+    return pk;
+}
+
+// The 8 exponent bytes of a warp's 8 blocks, gathered into lane 0 as one 64-bit word.
+__device__ __forceinline__ uint2 gather_exponents(uint32_t e8)
+{
+    uint2 w = make_uint2(0, 0);
+#pragma unroll
+    for (int b = 0; b < 4; b++) w.x |= __shfl_sync(0xFFFFFFFFu, e8, 4 * b) << (8 * b);
+#pragma unroll
+    for (int b = 0; b < 4; b++) w.y |= __shfl_sync(0xFFFFFFFFu, e8, 16 + 4 * b) << (8 * b);
+    return w;
+}
+
+__device__ __forceinline__ void load8(const float *p, int64_t i0, int64_t n, float (&v)[8])
+{
+    if (i0 + 8 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 15) == 0) {
+        float4 a = *reinterpret_cast<const float4 *>(p + i0), b = *reinterpret_cast<const float4 *>(p + i0 + 4);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = i0 + i < n ? p[i0 + i] : 0.0f;
+    }
+}
+__device__ __forceinline__ void store8(float *p, int64_t i0, int64_t n, const float (&v)[8])
+{
+    if (i0 + 8 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 15) == 0) {
+        *reinterpret_cast<float4 *>(p + i0) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(p + i0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (i0 + i < n) p[i0 + i] = v[i];
+    }
+}
+
+// ---- phase 1: sender ---------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, WireGeom geo, Peers peers,
+                 uint32_t epoch)
+{
+    const int64_t groups = geo.padded / 8;
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    const int lane = threadIdx.x & 31;
+    const int64_t g_per_shard = geo.shard / 8;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads; base < groups; base += stride) {
+        const int64_t g8 = base + threadIdx.x;           // padded % 256 == 0: whole warps stay in range
+        if (base + (threadIdx.x & ~31) >= groups) continue;
+        const int64_t i0 = g8 * 8;
+        float v[8], dq[8];
+        load8(g, i0, n, v);
+        if (res) {
+            float r[8];
+            load8(res, i0, geo.padded, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
+        }
+        uint32_t e8;
+        const uint32_t pk = encode8(v, e8, dq);
+        if (res) {
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], dq[i]);
+            store8(res, i0, geo.padded, r);
+        }
+        const int o = int(g8 / g_per_shard);
+        const int64_t in_shard = g8 - int64_t(o) * g_per_shard;
+        uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
+        reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
+        const uint2 ex = gather_exponents(e8);
+        if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + in_shard / 4) = ex;
+    }
+    Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
+    signal_done(mine, &mine->counter[0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
+}
+
+// ---- phase 2: owner ------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t epoch, int reverse)
+{
+    uint8_t *my = peers.arena[geo.rank];
+    Header *mine = reinterpret_cast<Header *>(my);
+    wait_flags(mine, mine->rs_flag, geo.world, epoch);
+    const int64_t groups = geo.shard / 8;
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    const int lane = threadIdx.x & 31;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads; base < groups; base += stride) {
+        const int64_t g8 = base + threadIdx.x;
+        if (base + (threadIdx.x & ~31) >= groups) continue;
+        float val[8], dq[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) val[i] = 0.0f;
+        for (int t = 0; t < geo.world; t++) {
+            const int s = reverse ? geo.world - 1 - t : t;
+            const uint8_t *slot = my + geo.rs_off + int64_t(s) * geo.slot_bytes;
+            const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[g8];
+            const float sc = __uint_as_float(scale_bits(slot[geo.shard / 2 + g8 / 4]));
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                val[i] = __fadd_rn(val[i], __fmul_rn(e2m1_value((pk >> (4 * i)) & 0xFu), sc));
+        }
+        if (ores) {
+            float r[8];
+            load8(ores, g8 * 8, geo.shard, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
+        }
+        uint32_t e8;
+        const uint32_t pk = encode8(val, e8, dq);
+        if (ores) {
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(val[i], dq[i]);
+            store8(ores, g8 * 8, geo.shard, r);
+        }
+        const uint2 ex = gather_exponents(e8);
+        for (int p = 0; p < geo.world; p++) {
+            uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
+            reinterpret_cast<uint32_t *>(slot)[g8] = pk;
+            if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + g8 / 4) = ex;
+        }
+    }
+    signal_done(mine, &mine->counter[1], peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
+}
+
+// ---- phase 3: everyone ---------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
+{
+    uint8_t *my = peers.arena[geo.rank];
+    Header *mine = reinterpret_cast<Header *>(my);
+    wait_flags(mine, mine->ag_flag, geo.world, epoch);
+    const int64_t groups = (n + 7) / 8;
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    const int64_t g_per_shard = geo.shard / 8;
+    const float w = float(geo.world);
+    for (int64_t g8 = int64_t(blockIdx.x) * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
+        const int o = int(g8 / g_per_shard);
+        const int64_t in_shard = g8 - int64_t(o) * g_per_shard;
+        const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
+        const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[in_shard];
+        const float sc = __uint_as_float(scale_bits(slot[geo.shard / 2 + in_shard / 4]));
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __fdiv_rn(__fmul_rn(e2m1_value((pk >> (4 * i)) & 0xFu), sc), w);
+        store8(g, g8 * 8, n, v);
+    }
+}
+
+int grid_for(int64_t groups)
+{
+    int64_t want = (groups + kThreads - 1) / kThreads;
+    int64_t cap = int64_t(sm_count()) * 8;
+    return int(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+Wire *as_wire(void *h) { return static_cast<Wire *>(h); }
+
+int check_call(Wire *w, const float *g, int64_t numel)
+{
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    if (!w->mapped) return fail(LS_ESTATE, "wire peers are not mapped yet");
+    if (!g || numel <= 0 || numel > w->g.padded) return fail(LS_EINVAL, "numel %lld does not fit the wire (padded %lld)", (long long)numel, (long long)w->g.padded);
+    return LS_OK;
+}
+
+}  // namespace
+}  // namespace ls
+
+using namespace ls;
+
+extern "C" int64_t ls_wire_handle_bytes(void) { return int64_t(sizeof(cudaIpcMemHandle_t)); }
+
+extern "C" int ls_wire_create(int rank, int world, int64_t padded, void **out)
+{
+    if (int rc = check_device()) return rc;
+    if (!out) return fail(LS_EINVAL, "null output");
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return fail(LS_EINVAL, "rank %d / world %d unsupported (world <= %d)", rank, world, kMaxWorld);
+    if (padded <= 0 || padded % (int64_t(world) * 256) != 0)
+        return fail(LS_EINVAL, "padded=%lld must be a positive multiple of world*256", (long long)padded);
+    Wire *w = new (std::nothrow) Wire();
+    if (!w) return fail(LS_ECUDA, "out of host memory");
+    w->g.rank = rank, w->g.world = world, w->g.padded = padded, w->g.shard = padded / world;
+    int64_t raw = w->g.shard / 2 + w->g.shard / 32;
+    w->g.slot_bytes = (raw + 255) / 256 * 256;
+    w->g.rs_off = int64_t(kHeaderBytes);
+    w->g.ag_off = w->g.rs_off + w->g.slot_bytes * world;
+    w->arena_bytes = size_t(w->g.ag_off + w->g.slot_bytes * world);
+    w->mapped = false;
+    w->epoch = 0;
+    for (int i = 0; i < kMaxWorld; i++) w->opened[i] = false, w->peers.arena[i] = nullptr;
+    cudaError_t e = cudaGetDevice(&w->dev);
+    if (e == cudaSuccess) e = cudaMalloc(&w->arena, w->arena_bytes);
+    if (e == cudaSuccess) e = cudaMemset(w->arena, 0, w->arena_bytes);
+    if (e != cudaSuccess) {
+        size_t bytes = w->arena_bytes;
+        delete w;
+        return fail(LS_ECUDA, "wire arena of %zu bytes: %s", bytes, cudaGetErrorString(e));
+    }
+    w->peers.arena[rank] = w->arena;
+    if (world == 1) w->mapped = true;
+    *out = w;
+    return LS_OK;
+}
+
+extern "C" int ls_wire_destroy(void *h)
+{
+    Wire *w = as_wire(h);
+    if (!w) return LS_OK;
+    cudaDeviceSynchronize();
+    for (int i = 0; i < kMaxWorld; i++)
+        if (w->opened[i]) cudaIpcCloseMemHandle(w->peers.arena[i]);
+    cudaFree(w->arena);
+    delete w;
+    return LS_OK;
+}
+
+extern "C" int ls_wire_local_handle(void *h, void *out)
+{
+    Wire *w = as_wire(h);
+    if (!w || !out) return fail(LS_EINVAL, "null argument");
+    cudaIpcMemHandle_t mh;
+    LS_CUDA(cudaIpcGetMemHandle(&mh, w->arena));
+    memcpy(out, &mh, sizeof mh);
+    return LS_OK;
+}
+
+extern "C" int ls_wire_map_peers(void *h, const void *all_handles)
+{
+    Wire *w = as_wire(h);
+    if (!w || !all_handles) return fail(LS_EINVAL, "null argument");
+    if (w->mapped) return LS_OK;
+    const cudaIpcMemHandle_t *hs = static_cast<const cudaIpcMemHandle_t *>(all_handles);
+    for (int p = 0; p < w->g.world; p++) {
+        if (p == w->g.rank) continue;
+        void *ptr = nullptr;
+        LS_CUDA(cudaIpcOpenMemHandle(&ptr, hs[p], cudaIpcMemLazyEnablePeerAccess));
+        w->peers.arena[p] = static_cast<uint8_t *>(ptr);
+        w->opened[p] = true;
+    }
+    w->mapped = true;
+    return LS_OK;
+}
+
+extern "C" int ls_wire_map_local(void *h, void *const *wires)
+{
+    Wire *w = as_wire(h);
+    if (!w || !wires) return fail(LS_EINVAL, "null argument");
+    for (int p = 0; p < w->g.world; p++) {
+        Wire *o = as_wire(wires[p]);
+        if (!o || o->g.world != w->g.world || o->g.rank != p || o->g.padded != w->g.padded)
+            return fail(LS_EINVAL, "wire %d does not match", p);
+        w->peers.arena[p] = o->arena;
+    }
+    w->mapped = true;
+    return LS_OK;
+}
+
+extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, void *stream)
+{
+    Wire *w = as_wire(h);
+    if (int rc = check_call(w, g, numel)) return rc;
+    w->epoch++;
+    wire_send_kernel<<<grid_for(w->g.padded / 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, numel, res, w->g, w->peers, w->epoch);
+    LS_LAUNCH_CHECK("wire_send");
+    return LS_OK;
+}
+
+extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
+{
+    Wire *w = as_wire(h);
+    if (!w || !w->mapped) return fail(LS_ESTATE, "wire not ready");
+    wire_reduce_kernel<<<grid_for(w->g.shard / 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        ores, w->g, w->peers, w->epoch, reverse);
+    LS_LAUNCH_CHECK("wire_reduce");
+    return LS_OK;
+}
+
+extern "C" int ls_wire_finish(void *h, float *g, int64_t numel, void *stream)
+{
+    Wire *w = as_wire(h);
+    if (int rc = check_call(w, g, numel)) return rc;
+    wire_finish_kernel<<<grid_for((numel + 7) / 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, numel, w->g, w->peers, w->epoch);
+    LS_LAUNCH_CHECK("wire_finish");
+    return LS_OK;
+}
+
+extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, float *ores, int reverse,
+                                 void *stream)
+{
+    if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
+    if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
+    return ls_wire_finish(h, g, numel, stream);
+}
+
+extern "C" int ls_wire_status(void *h, int *status_host)
+{
+    Wire *w = as_wire(h);
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    uint32_t v = 0;
+    Header *hd = reinterpret_cast<Header *>(w->arena);
+    LS_CUDA(cudaMemcpy(&v, &hd->status, sizeof v, cudaMemcpyDeviceToHost));
+    if (v) LS_CUDA(cudaMemset(&hd->status, 0, sizeof v));
+    if (status_host) *status_host = int(v);
+    return v ? fail(LS_ETIMEOUT, "a wire kernel gave up waiting for a peer's flag") : LS_OK;
+}
+
+// Raw bytes of the arena, for byte-exact checks of what crossed the wire:
+// which = 0 receive slots (world x slot), 1 gather slots.  Copies to a device buffer.
+extern "C" int ls_wire_debug_slots(void *h, int which, uint8_t *out, int64_t *slot_bytes, void *stream)
+{
+    Wire *w = as_wire(h);
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    if (slot_bytes) *slot_bytes = w->g.slot_bytes;
+    if (out)
+        LS_CUDA(cudaMemcpyAsync(out, w->arena + (which ? w->g.ag_off : w->g.rs_off), size_t(w->g.slot_bytes) * w->g.world,
+                                cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+    return LS_OK;
+}

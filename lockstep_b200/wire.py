@@ -1,0 +1,305 @@
+"""Gradient all-reduce with the API of lockstep's wire.py, plus the FP4 wires.
+
+  fp32     all_reduce in fp32                                  (wire.py:93-96)
+  bf16     all_reduce in bf16                                  (wire.py:97-101)
+  int16    integers on a shared per-64 grid, owner-reduced     (wire.py:104-138)
+  int8     the same at 8 bits
+  int8ef   8 bits with error feedback at sender and owner
+  mxfp4    (new) MXFP4 payload: block-32 E2M1 + one UE8M0 byte, each block
+           scaled by its own rank, so no MAX pre-collective; owner decodes and
+           sums in fp32 in ascending sender order, re-encodes, gathers
+  mxfp4ef  mxfp4 with error feedback at sender and owner
+
+The MXFP4 wires run as three hand-written kernels per step that store the
+packed bytes straight into the owner's / every rank's memory over NVLink
+(`csrc/wire.cu`); the process group only carries the IPC handles at set-up.
+The reference's own methods keep their exact arithmetic, on the GPU, over
+torch.distributed collectives.  `Wire(method, numel, world, rank)(g)` averages
+the flat fp32 gradient `g` in place, as the reference does.
+"""
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import check, lib, need_cuda, ptr, stream
+
+CHUNK = 64                                     # elements per integer scale
+METHODS = ("fp32", "bf16", "int16", "int8ef", "mxfp4", "mxfp4ef")
+_KUNIT = 256                                   # the kernels pad to world * 256 elements
+
+
+def env_rank():
+    """(rank, world, local rank) from torchrun, SLURM or MPI variables; else one process (wire.py:30-36)."""
+    def first(names, default):
+        for n in names:
+            if n in os.environ:
+                return int(os.environ[n])
+        return default
+    return (first(("RANK", "SLURM_PROCID", "OMPI_COMM_WORLD_RANK"), 0),
+            first(("WORLD_SIZE", "SLURM_NTASKS", "OMPI_COMM_WORLD_SIZE"), 1),
+            first(("LOCAL_RANK", "SLURM_LOCALID", "OMPI_COMM_WORLD_LOCAL_RANK"), 0))
+
+
+def init():
+    """Join the process group if there is more than one rank; (rank, world, device) (wire.py:39-50)."""
+    rank, world, local = env_rank()
+    if not torch.cuda.is_available():
+        raise RuntimeError("lockstep_b200.wire needs a CUDA device (there is no CPU path)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    return rank, world, device
+
+
+def _as_bytes(x):
+    return x.view(torch.uint8) if x.dtype == torch.int16 else x
+
+
+def _all_to_all(x, world):
+    if world == 1:
+        return x
+    out = torch.empty_like(x)
+    dist.all_to_all_single(_as_bytes(out), _as_bytes(x))
+    return out
+
+
+def _all_gather(x, world):
+    if world == 1:
+        return x
+    out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(_as_bytes(out), _as_bytes(x))
+    return out
+
+
+class Wire:
+    """Averages a flat fp32 gradient across ranks, in place, with one method."""
+
+    def __init__(self, method, numel, world=1, rank=0):
+        bits = {"int16": 16, "int8": 8, "int8ef": 8}.get(method)
+        self.method, self.world, self.rank, self.n = method, world, rank, numel
+        self.fp4 = method in ("mxfp4", "mxfp4ef")
+        self.ef = method in ("int8ef", "mxfp4ef")
+        self.lim = 2 ** (bits - 1) - 1 if bits else None
+        self.dtype = {16: torch.int16, 8: torch.int8}.get(bits)
+        span = world * CHUNK
+        self.padded = -(-numel // span) * span
+        self.res = self.ores = None                # sender and owner residuals (EF)
+        if self.fp4:
+            self.bytes_per_el = 0.5 + 1 / 32       # 16 packed bytes + 1 exponent byte per 32
+        else:
+            self.bytes_per_el = {"fp32": 4.0, "bf16": 2.0}.get(method) or bits / 8 + 4 / CHUNK
+        self._h = None
+        self._kpadded = -(-numel // (world * _KUNIT)) * world * _KUNIT
+
+    # ---- MXFP4 transport -----------------------------------------------------
+    def _handle(self, device):
+        if self._h is None:
+            h = ctypes.c_void_p()
+            check(lib().ls_wire_create(self.rank, self.world, self._kpadded, ctypes.byref(h)))
+            self._h = h
+            if self.world > 1:
+                nb = int(lib().ls_wire_handle_bytes())
+                blob = (ctypes.c_uint8 * nb)()
+                check(lib().ls_wire_local_handle(h, blob))
+                mine = torch.tensor(list(blob), dtype=torch.uint8, device=device)
+                everyone = torch.empty(self.world * nb, dtype=torch.uint8, device=device)
+                dist.all_gather_into_tensor(everyone, mine)
+                raw = bytes(everyone.cpu().tolist())
+                check(lib().ls_wire_map_peers(h, raw))
+                dist.barrier()
+        return self._h
+
+    def _mxfp4(self, g, reverse):
+        need_cuda(g)
+        assert g.dtype == torch.float32 and g.is_contiguous() and g.numel() == self.n
+        h = self._handle(g.device)
+        if self.ef and self.res is None:
+            self.res = torch.zeros(self._kpadded, device=g.device)
+            self.ores = torch.zeros(self._kpadded // self.world, device=g.device)
+        check(lib().ls_wire_allreduce(h, ptr(g), self.n, ptr(self.res), ptr(self.ores), int(bool(reverse)),
+                                      stream()))
+        return g
+
+    def status(self):
+        """Raises if a wire kernel gave up waiting for a peer (synchronises)."""
+        if self._h is not None:
+            check(lib().ls_wire_status(self._h, None))
+
+    def close(self):
+        if self._h is not None:
+            if self.world > 1 and dist.is_initialized():
+                torch.cuda.synchronize()
+                dist.barrier()
+            lib().ls_wire_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def state_dict(self):
+        """Residuals carried across steps (what a checkpoint must hold)."""
+        return {"res": self.res, "ores": self.ores}
+
+    def load_state_dict(self, sd):
+        self.res, self.ores = sd["res"], sd["ores"]
+
+    # ---- call ----------------------------------------------------------------
+    def __call__(self, g, reverse=False):
+        need_cuda(g)
+        if self.method == "fp32":
+            if self.world > 1:
+                dist.all_reduce(g)
+            return g.div_(self.world)
+        if self.method == "bf16":
+            h = g.to(torch.bfloat16)
+            if self.world > 1:
+                dist.all_reduce(h)
+            return g.copy_(h).div_(self.world)
+        if self.fp4:
+            return self._mxfp4(g, reverse)
+        return self._integer(g, reverse)
+
+    def _integer(self, g, reverse):
+        """The reference's integer wires, same operations in the same order
+        (wire.py:104-138), on the GPU."""
+        world, lim = self.world, self.lim
+        v = torch.zeros(self.padded, device=g.device)
+        v[:self.n] = g
+        if self.ef:
+            if self.res is None:
+                self.res = torch.zeros_like(v)
+            v += self.res
+        c = v.view(-1, CHUNK)
+        m = c.abs().amax(1)
+        if world > 1:
+            dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        s = torch.where(m > 0, lim / m, torch.ones_like(m))
+        q = torch.round(c * s[:, None]).clamp_(-lim, lim)
+        if self.ef:
+            self.res = v - (q / s[:, None]).view(-1)
+        own = c.shape[0] // world
+        parts = _all_to_all(q.to(self.dtype), world).view(world, own, CHUNK)
+        if reverse:
+            parts = parts.flip(0)
+        val = parts.to(torch.int32).sum(0).float()
+        lo = self.rank * own
+        val /= s[lo:lo + own, None]
+        if self.ef:
+            if self.ores is None:
+                self.ores = torch.zeros_like(val)
+            val += self.ores
+        m2 = val.abs().amax(1)
+        s2 = torch.where(m2 > 0, lim / m2, torch.ones_like(m2))
+        q2 = torch.round(val * s2[:, None]).clamp_(-lim, lim)
+        if self.ef:
+            self.ores = val - q2 / s2[:, None]
+        q2 = _all_gather(q2.to(self.dtype), world).view(-1, CHUNK)
+        s2 = _all_gather(s2, world)
+        return g.copy_((q2.float() / s2[:, None]).view(-1)[:self.n]).div_(world)
+
+
+class LocalWireGroup:
+    """All ranks of an MXFP4 wire inside ONE process on one GPU: handles are
+    connected with plain pointers and the phases run rank after rank on one
+    stream, so no kernel ever waits for another.  Exercises exactly the kernels,
+    addressing and flags of the multi-GPU path; used by the single-GPU tests."""
+
+    def __init__(self, world, numel, ef=False):
+        self.world, self.n, self.ef = world, numel, ef
+        self.kpadded = -(-numel // (world * _KUNIT)) * world * _KUNIT
+        self.handles = []
+        for r in range(world):
+            h = ctypes.c_void_p()
+            check(lib().ls_wire_create(r, world, self.kpadded, ctypes.byref(h)))
+            self.handles.append(h)
+        arr = (ctypes.c_void_p * world)(*[h.value for h in self.handles])
+        for h in self.handles:
+            check(lib().ls_wire_map_local(h, arr))
+        dev = torch.device("cuda")
+        self.res = [torch.zeros(self.kpadded, device=dev) for _ in range(world)] if ef else [None] * world
+        self.ores = [torch.zeros(self.kpadded // world, device=dev) for _ in range(world)] if ef else [None] * world
+
+    def step(self, gs, reverse=False):
+        L = lib()
+        for r, h in enumerate(self.handles):
+            check(L.ls_wire_send(h, ptr(gs[r]), self.n, ptr(self.res[r]), stream()))
+        for r, h in enumerate(self.handles):
+            check(L.ls_wire_reduce(h, ptr(self.ores[r]), int(reverse), stream()))
+        for r, h in enumerate(self.handles):
+            check(L.ls_wire_finish(h, ptr(gs[r]), self.n, stream()))
+        for h in self.handles:
+            check(L.ls_wire_status(h, None))
+        return gs
+
+    def slots(self, rank, which):
+        """Raw bytes this rank received: [world, slot_bytes] uint8."""
+        sb = ctypes.c_int64()
+        check(lib().ls_wire_debug_slots(self.handles[rank], which, None, ctypes.byref(sb), None))
+        out = torch.empty(self.world, sb.value, dtype=torch.uint8, device="cuda")
+        check(lib().ls_wire_debug_slots(self.handles[rank], which, ptr(out), ctypes.byref(sb), stream()))
+        return out
+
+    def close(self):
+        torch.cuda.synchronize()
+        for h in self.handles:
+            lib().ls_wire_destroy(h)
+        self.handles = []
+
+
+def bench(out, numel, iters):
+    """Time and error of each wire on one gradient-sized buffer (wire.py:141-185)."""
+    import csv
+    import statistics
+    import time
+    from pathlib import Path
+    rank, world, dev = init()
+    gen = torch.Generator(device=dev).manual_seed(1)
+    signal = torch.randn(numel, device=dev, generator=gen)
+    gen.manual_seed(100 + rank)
+    g0 = signal / world + 3 * torch.randn(numel, device=dev, generator=gen) / world ** 0.5
+    ref = g0.double()
+    if world > 1:
+        dist.all_reduce(ref)
+    ref /= world
+    rows = []
+    for method in ("fp32", "bf16", "int16", "int8", "mxfp4"):
+        t0 = time.perf_counter()
+        w = Wire(method, numel, world, rank)
+        res = w(g0.clone())
+        times = []
+        for _ in range(iters):
+            x = g0.clone()
+            if world > 1:
+                dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            w(x)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        ms = statistics.median(times)
+        rows.append(dict(method=method, gpus=world, B_per_el=round(w.bytes_per_el, 4), ms=round(ms, 3),
+                         grad_GBps=round(numel * 4 / ms / 1e6, 1),
+                         rel_err=f"{((res.double() - ref).norm() / ref.norm()).item():.3e}",
+                         seconds=round(time.perf_counter() - t0, 1)))
+        w.close()
+        if rank == 0:
+            print(rows[-1], flush=True)
+    if rank == 0:
+        Path(out).mkdir(parents=True, exist_ok=True)
+        with open(Path(out) / "wire.csv", "w", newline="") as f:
+            wr = csv.DictWriter(f, fieldnames=list(rows[0]))
+            wr.writeheader()
+            wr.writerows(rows)
+    if world > 1:
+        dist.destroy_process_group()

@@ -117,11 +117,13 @@ def wire_decode(packed, e8m0, n, world):
     return g
 
 
-def wire_step(gs, res=None, ores=None, reverse=False):
-    """All ranks of one step in this process.  Returns (out, sent, owned)."""
+def wire_step(gs, res=None, ores=None, reverse=False, unit=64):
+    """All ranks of one step in this process.  Returns (out, sent, owned).
+    unit: padding granularity per rank (64 in wire.py:86-87; the CUDA kernels
+    pad to 256, which moves shard boundaries but no block's arithmetic)."""
     world = len(gs)
     n = gs[0].size
-    span = world * 64
+    span = world * unit
     padded = -(-n // span) * span
     shard = padded // world
     sent = [wire_encode(gs[r], padded, None if res is None else res[r]) for r in range(world)]
