@@ -148,11 +148,12 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-wire", action="store_true", help="skip the all-reduce leg")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
     args = ap.parse_args()
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
@@ -238,10 +239,39 @@ def main():
         barrier()
         e2e_ms = a.elapsed_time(b) / e2e_steps
 
-    t = torch.tensor([step_ms, e2e_ms, gemm_ms], device=dev, dtype=torch.float64)
+    # ---- FP4-compressed all-reduce of a 256 MiB fp32 gradient per rank (error feedback on)
+    from lockstep_b200 import wire
+    wn = (8 << 20) if args.small else (64 << 20)
+    wsteps = 0 if args.no_wire else max(3, min(args.steps, 30))
+    wire_ms = float("nan")
+    if wsteps:
+        del flush
+        gw = torch.Generator(device=dev).manual_seed(100 + rank)
+        z = torch.randn(wn, device=dev, generator=gw)
+        chi = torch.zeros(wn, device=dev)
+        for _ in range(3):
+            chi += torch.randn(wn, device=dev, generator=gw) ** 2
+        grad = z / (chi / 3).sqrt() * 1e-3                   # Student-t(3) * 1e-3
+        del z, chi
+        wobj = wire.Wire("mxfp4ef", wn, world, rank)
+        for _ in range(3):
+            wobj(grad)
+        wobj.status()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(wsteps):
+            wobj(grad)
+        b.record()
+        barrier()
+        wobj.status()
+        wire_ms = a.elapsed_time(b) / wsteps
+        wobj.close()
+
+    t = torch.tensor([step_ms, e2e_ms, gemm_ms, wire_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    step_ms_max, e2e_ms_max, gemm_ms_max = t.tolist()
+    step_ms_max, e2e_ms_max, gemm_ms_max, wire_ms_max = t.tolist()
 
     if rank == 0:
         pk = peaks()
@@ -260,7 +290,7 @@ def main():
             "e2e": {"value": world * flops_step / (e2e_ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": hx1.numel() * 2 * 2, "d2h_bytes_per_step": hc.numel() * 2,
                     "ms_per_step": e2e_ms_max},
-            "gpu_launches": 3 * args.steps,
+            "gpu_launches": 3 * args.steps + 3 * wsteps,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_kernel<256> (dual batch)",
                          "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
@@ -269,6 +299,18 @@ def main():
                          "frac_of_spec": gemm_tflops / FP4_SPEC_TFLOPS,
                          "traffic": None},
         }
+        if wsteps:
+            comp = wn * 0.53125                              # packed + exponent bytes of one buffer
+            # per rank and step: send reads g, res and writes res, payload; reduce reads W payloads,
+            # ores, writes ores and W payloads; finish reads the payload and writes g
+            hbm = wn * (12 + 0.53125) + (wn / world) * (world * 0.53125 + 8 + world * 0.53125) + wn * (0.53125 + 4)
+            line["allreduce"] = {
+                "method": "mxfp4ef", "world": world, "elements_per_rank": wn, "steps": wsteps,
+                "ms": wire_ms_max, "algbw_gbs": wn * 4 / (wire_ms_max * 1e-3) / 1e9,
+                "link_busbw_gbs": 2 * (world - 1) / world * comp / (wire_ms_max * 1e-3) / 1e9,
+                "link_peak_gbs": 900.0, "hbm_bytes_per_rank": hbm,
+                "hbm_gbs": hbm / (wire_ms_max * 1e-3) / 1e9, "hbm_peak_gbs": pk["hbm"],
+                "hbm_frac": hbm / (wire_ms_max * 1e-3) / 1e9 / pk["hbm"], "data": "Student-t(3) * 1e-3, seed 100 + rank"}
         if world == 1 and not args.no_cpu_baseline:
             dt, fl = cpu_reference_step(CPU_SAMPLE_ROWS)
             dt2, fl = cpu_reference_step(CPU_SAMPLE_ROWS)

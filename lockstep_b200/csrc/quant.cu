@@ -15,30 +15,62 @@ struct QuantOut {
     float *scale;
     uint32_t kblocks;               // blocks per row (K / BLOCK)
     uint32_t ktiles;                // K / 128 (scale-factor tiles per row)
+    uint32_t div_mul, div_shift;    // row = block / kblocks by multiply-shift (scale-factor layout only)
+    uint32_t nblocks;               // rows * kblocks
 };
 
-// Stores the results of one 8-element group.  `g8` = index of the group,
-// `lane_in_block` = position of the group inside its quantization block.
-template <int BLOCK>
-__device__ __forceinline__ void store_group(const QuantOut &o, int64_t g8, uint32_t pk,
-                                            uint32_t e8, bool leader)
+// floor(b / kblocks) for any 32-bit b: t = hi(b * mul); q = (t + ((b - t) >> 1)) >> shift
+__device__ __forceinline__ uint32_t div_kblocks(const QuantOut &o, uint32_t b)
 {
-    if (o.packed) reinterpret_cast<uint32_t *>(o.packed)[g8] = pk;
-    if (o.codes) {
-        uint2 c;
-        c.x = (pk & 0xFu) | ((pk & 0xF0u) << 4) | ((pk & 0xF00u) << 8) | ((pk & 0xF000u) << 12);
-        uint32_t h = pk >> 16;
-        c.y = (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
-        reinterpret_cast<uint2 *>(o.codes)[g8] = c;
+    uint32_t t = __umulhi(b, o.div_mul);
+    return (t + ((b - t) >> 1)) >> o.div_shift;
+}
+
+// Stores the results of one 8-element group.  Lanes of a warp hold 32
+// consecutive groups; a "quad" (16 lanes, BLOCK = 32) covers 4 consecutive
+// blocks of one row, whose exponent bytes are contiguous in every scale
+// output, so one lane per quad writes them as one word.
+template <int BLOCK>
+__device__ __forceinline__ void store_group(const QuantOut &o, uint32_t g8, uint32_t pk, uint32_t e8, bool in_range)
+{
+    constexpr int LPB = BLOCK / 8;
+    if (in_range) {
+        if (o.packed) reinterpret_cast<uint32_t *>(o.packed)[g8] = pk;
+        if (o.codes) {
+            uint2 c;
+            c.x = (pk & 0xFu) | ((pk & 0xF0u) << 4) | ((pk & 0xF00u) << 8) | ((pk & 0xF000u) << 12);
+            uint32_t h = pk >> 16;
+            c.y = (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
+            reinterpret_cast<uint2 *>(o.codes)[g8] = c;
+        }
     }
-    if (leader) {
-        int64_t blk = g8 / (BLOCK / 8);
-        if (o.scale) o.scale[blk] = __uint_as_float(scale_bits(e8));
-        if (o.e8m0) o.e8m0[blk] = uint8_t(e8);
+    // gather 4 consecutive blocks' exponent bytes into the first lane of each group of 4 blocks
+    uint32_t w = e8;
+    w |= __shfl_down_sync(0xFFFFFFFFu, e8, LPB) << 8;
+    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 2 * LPB) << 16;
+    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 3 * LPB) << 24;
+    const uint32_t lane = threadIdx.x & 31;
+    if (in_range && (lane & (4 * LPB - 1)) == 0) {
+        const uint32_t blk = g8 / LPB;                  // first of 4 blocks, blk % 4 == 0
+        if (blk + 4 <= o.nblocks) {
+            if (o.e8m0) *reinterpret_cast<uint32_t *>(o.e8m0 + blk) = w;
+            if (o.scale) {
+                uint4 sc;
+                sc.x = scale_bits(w & 0xFFu), sc.y = scale_bits((w >> 8) & 0xFFu);
+                sc.z = scale_bits((w >> 16) & 0xFFu), sc.w = scale_bits(w >> 24);
+                *reinterpret_cast<uint4 *>(o.scale + blk) = sc;
+            }
+        } else {                                        // fewer than 4 blocks left in the tensor
+            for (uint32_t i = 0; blk + i < o.nblocks; i++) {
+                const uint32_t e = (w >> (8 * i)) & 0xFFu;
+                if (o.e8m0) o.e8m0[blk + i] = uint8_t(e);
+                if (o.scale) o.scale[blk + i] = __uint_as_float(scale_bits(e));
+            }
+        }
         if (o.sf) {
-            uint32_t row = uint32_t(blk / o.kblocks);
-            uint32_t kb = uint32_t(blk - int64_t(row) * o.kblocks);
-            o.sf[sf_offset(row, kb, o.ktiles)] = uint8_t(e8);
+            const uint32_t row = div_kblocks(o, blk);
+            const uint32_t kb = blk - row * o.kblocks;
+            *reinterpret_cast<uint32_t *>(o.sf + sf_offset(row, kb, o.ktiles)) = w;
         }
     }
 }
@@ -60,61 +92,63 @@ __device__ __forceinline__ uint32_t codes8(const float (&q)[8])
 // keeps the smaller magnitude) the divisor carries a factor (1 - 2^-12): a
 // bf16 value has 8 significant bits, the factor 12, so the product is exact
 // in fp32, lies strictly below every halfway point the value sat on, and
-// never crosses one it did not.
+// never crosses one it did not.  Each CTA handles kUnroll * 256 groups; all of
+// a thread's loads are issued before the first use.
 template <int BLOCK, bool RNE>
 __global__ void __launch_bounds__(kThreads)
-quantize_bf16_kernel(const uint4 *__restrict__ x, int64_t n8, QuantOut o)
+quantize_bf16_kernel(const uint4 *__restrict__ x, uint32_t n8, QuantOut o)
 {
     constexpr int LPB = BLOCK / 8;
-    const int64_t stride = int64_t(gridDim.x) * kThreads * kUnroll;
-    for (int64_t base = int64_t(blockIdx.x) * kThreads * kUnroll; base < n8; base += stride) {
-        uint4 v[kUnroll];
+    const uint32_t base = blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
+    uint4 v[kUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-            int64_t g8 = base + u * kThreads + threadIdx.x;
-            v[u] = g8 < n8 ? ld_stream(x + g8) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < kUnroll; u++) {
+        const uint32_t g8 = base + u * kThreads;
+        v[u] = g8 < n8 ? ld_stream(x + g8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+        const uint32_t g8 = base + u * kThreads;
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        // |x| maxima on packed bf16 pairs, NaN-propagating
+        __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
+#pragma unroll
+        for (int i = 1; i < 4; i++)
+            m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+        uint32_t mb = *reinterpret_cast<uint32_t *>(&m);
+#pragma unroll
+        for (int off = 1; off < LPB; off <<= 1) {
+            uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, mb, off);
+            __nv_bfloat162 mm = __hmax2_nan(*reinterpret_cast<__nv_bfloat162 *>(&mb),
+                                            *reinterpret_cast<__nv_bfloat162 *>(&other));
+            mb = *reinterpret_cast<uint32_t *>(&mm);
         }
+        const uint32_t amax = max(mb & 0xFFFF0000u, mb << 16);      // as fp32 bits
+        // a bf16 maximum is never within 44 ulps (fp32) below a power of two: plain exponent
+        uint32_t e8 = (max(amax, kBitsClamp) >> 23) - 2u;
+        if (amax == 0u) e8 = 127u;
+        float q[8];
+        uint32_t pk;
+        if (amax < kBitsInf) {
+            const uint32_t mul = RNE ? inv_scale_bits(e8) : (((253u - e8) << 23) | 0x7FF000u);
+            const float c = __uint_as_float(mul);
 #pragma unroll
-        for (int u = 0; u < kUnroll; u++) {
-            int64_t g8 = base + u * kThreads + threadIdx.x;
-            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-            // |x| maxima on packed bf16 pairs, NaN-propagating
-            __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
-#pragma unroll
-            for (int i = 1; i < 4; i++)
-                m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
-            uint32_t mb = *reinterpret_cast<uint32_t *>(&m);
-#pragma unroll
-            for (int off = 1; off < LPB; off <<= 1) {
-                uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, mb, off);
-                __nv_bfloat162 mm = __hmax2_nan(*reinterpret_cast<__nv_bfloat162 *>(&mb),
-                                                *reinterpret_cast<__nv_bfloat162 *>(&other));
-                mb = *reinterpret_cast<uint32_t *>(&mm);
+            for (int i = 0; i < 4; i++) {
+                q[2 * i] = __uint_as_float(w[i] << 16) * c;
+                q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
             }
-            uint32_t amax = max(mb & 0xFFFF0000u, mb << 16);      // as fp32 bits
-            uint32_t e8 = block_e8m0(amax);
-            float q[8];
-            uint32_t pk;
-            if (e8 <= 252u) {
-                uint32_t mul = RNE ? inv_scale_bits(e8) : (((253u - e8) << 23) | 0x7FF000u);
-                float c = __uint_as_float(mul);
+            pk = cvt_e2m1x8(q);
+        } else {                                   // infinite or NaN block maximum
+            e8 = amax == kBitsInf ? 254u : 255u;
+            const float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    q[2 * i] = __uint_as_float(w[i] << 16) * c;
-                    q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
-                }
-                pk = cvt_e2m1x8(q);
-            } else {                                   // infinite or NaN block maximum
-                float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    q[2 * i] = __uint_as_float(w[i] << 16) * c;
-                    q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
-                }
-                pk = codes8<RNE>(q);
+            for (int i = 0; i < 4; i++) {
+                q[2 * i] = __uint_as_float(w[i] << 16) * c;
+                q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
             }
-            if (g8 < n8) store_group<BLOCK>(o, g8, pk, e8, (threadIdx.x & (LPB - 1)) == 0);
+            pk = codes8<RNE>(q);
         }
+        store_group<BLOCK>(o, g8, pk, e8, g8 < n8);
     }
 }
 
@@ -123,39 +157,37 @@ quantize_bf16_kernel(const uint4 *__restrict__ x, int64_t n8, QuantOut o)
 // Integer rounding on the bit pattern; exact for every fp32 input.
 template <int BLOCK, bool RNE>
 __global__ void __launch_bounds__(kThreads)
-quantize_f32_kernel(const uint4 *__restrict__ x, int64_t n8, QuantOut o)
+quantize_f32_kernel(const uint4 *__restrict__ x, uint32_t n8, QuantOut o)
 {
     constexpr int LPB = BLOCK / 8;
     constexpr int U = kUnroll / 2;
-    const int64_t stride = int64_t(gridDim.x) * kThreads * U;
-    for (int64_t base = int64_t(blockIdx.x) * kThreads * U; base < n8; base += stride) {
-        uint4 v[U][2];
+    const uint32_t base = blockIdx.x * (kThreads * U) + threadIdx.x;
+    uint4 v[U][2];
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            int64_t g8 = base + u * kThreads + threadIdx.x;
-            bool ok = g8 < n8;
-            v[u][0] = ok ? ld_stream(x + 2 * g8) : make_uint4(0, 0, 0, 0);
-            v[u][1] = ok ? ld_stream(x + 2 * g8 + 1) : make_uint4(0, 0, 0, 0);
-        }
+    for (int u = 0; u < U; u++) {
+        const uint32_t g8 = base + u * kThreads;
+        const bool ok = g8 < n8;
+        v[u][0] = ok ? ld_stream(x + 2 * size_t(g8)) : make_uint4(0, 0, 0, 0);
+        v[u][1] = ok ? ld_stream(x + 2 * size_t(g8) + 1) : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            int64_t g8 = base + u * kThreads + threadIdx.x;
-            const uint32_t w[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w,
-                                   v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
-            uint32_t amax = 0;
+    for (int u = 0; u < U; u++) {
+        const uint32_t g8 = base + u * kThreads;
+        const uint32_t w[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w,
+                               v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
+        uint32_t amax = 0;
 #pragma unroll
-            for (int i = 0; i < 8; i++) amax = max(amax, w[i] & 0x7FFFFFFFu);
+        for (int i = 0; i < 8; i++) amax = max(amax, w[i] & 0x7FFFFFFFu);
 #pragma unroll
-            for (int off = 1; off < LPB; off <<= 1)
-                amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-            uint32_t e8 = block_e8m0(amax);
-            float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
-            float q[8];
+        for (int off = 1; off < LPB; off <<= 1)
+            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+        const uint32_t e8 = block_e8m0(amax);
+        const float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+        float q[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) q[i] = __uint_as_float(w[i]) * c;
-            uint32_t pk = codes8<RNE>(q);
-            if (g8 < n8) store_group<BLOCK>(o, g8, pk, e8, (threadIdx.x & (LPB - 1)) == 0);
-        }
+        for (int i = 0; i < 8; i++) q[i] = __uint_as_float(w[i]) * c;
+        const uint32_t pk = codes8<RNE>(q);
+        store_group<BLOCK>(o, g8, pk, e8, g8 < n8);
     }
 }
 
@@ -316,14 +348,25 @@ extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64
     if (!x) return fail(LS_EINVAL, "x is null");
     if (!aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7) || (reinterpret_cast<uintptr_t>(packed) & 3))
         return fail(LS_EALIGN, "x must be 16-byte, codes 8-byte, packed 4-byte aligned");
-    if (n / block >= (int64_t(1) << 32)) return fail(LS_EINVAL, "too many blocks");
-    QuantOut o{codes, packed, e8m0, sf, scale, uint32_t(K / block), uint32_t(K / 128)};
-    int64_t n8 = n / 8;
+    if (n / 8 >= (int64_t(1) << 31)) return fail(LS_EINVAL, "more than 2^34 elements in one call");
+    if ((reinterpret_cast<uintptr_t>(scale) & 15) || (reinterpret_cast<uintptr_t>(e8m0) & 3) ||
+        (reinterpret_cast<uintptr_t>(sf) & 3))
+        return fail(LS_EALIGN, "scale must be 16-byte, e8m0 and sf 4-byte aligned");
+    QuantOut o{codes, packed, e8m0, sf, scale, uint32_t(K / block), uint32_t(K / 128), 0u, 0u, uint32_t(n / block)};
+    {   // multiply-shift division by kblocks (>= 4 whenever the scale-factor layout is requested)
+        uint32_t d = o.kblocks, sh = 0;
+        while ((1ull << sh) < d) sh++;
+        if (d > 1) {
+            o.div_mul = uint32_t(((1ull << 32) * ((1ull << sh) - d)) / d + 1);
+            o.div_shift = sh - 1;
+        }
+    }
+    uint32_t n8 = uint32_t(n / 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint4 *xp = static_cast<const uint4 *>(x);
     bool rne = rounding == LS_ROUND_RNE;
     if (x_dtype == LS_BF16) {
-        int grid = grid_for(n8, kThreads * kUnroll);
+        int grid = int((n8 + kThreads * kUnroll - 1) / (kThreads * kUnroll));
         if (block == 32) {
             if (rne) quantize_bf16_kernel<32, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
             else quantize_bf16_kernel<32, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
@@ -332,7 +375,7 @@ extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64
             else quantize_bf16_kernel<16, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
         }
     } else {
-        int grid = grid_for(n8, kThreads * kUnroll / 2);
+        int grid = int((n8 + kThreads * kUnroll / 2 - 1) / (kThreads * kUnroll / 2));
         if (block == 32) {
             if (rne) quantize_f32_kernel<32, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
             else quantize_f32_kernel<32, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
