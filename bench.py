@@ -154,6 +154,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--no-wire", action="store_true", help="skip the all-reduce leg")
+    ap.add_argument("--no-train", action="store_true", help="skip the FP4-linear training-step leg")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
     args = ap.parse_args()
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
@@ -311,6 +312,16 @@ def main():
                 "link_peak_gbs": 900.0, "hbm_bytes_per_rank": hbm,
                 "hbm_gbs": hbm / (wire_ms_max * 1e-3) / 1e9, "hbm_peak_gbs": pk["hbm"],
                 "hbm_frac": hbm / (wire_ms_max * 1e-3) / 1e9 / pk["hbm"], "data": "Student-t(3) * 1e-3, seed 100 + rank"}
+        if world == 1 and not args.no_train and not args.small:
+            from lockstep_b200 import gpt
+            torch.cuda.empty_cache()
+            tr = {}
+            for mode in ("ste", "mxfp4"):
+                sec, loss = gpt.training_step_time(backward=mode, steps=5, warmup=2, device=dev)
+                tr[mode] = {"tokens_per_s": 16 * 1024 / sec, "ms_per_step": sec * 1e3, "loss": loss}
+            line["train_step"] = {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 vocab32000, every block "
+                                           "linear MXFP4Linear, bf16 autocast, fused AdamW, synthetic ids seed 0",
+                                  "backward": tr}
         if world == 1 and not args.no_cpu_baseline:
             dt, fl = cpu_reference_step(CPU_SAMPLE_ROWS)
             dt2, fl = cpu_reference_step(CPU_SAMPLE_ROWS)

@@ -1,0 +1,81 @@
+"""GPU parity of the MXFP4 linear layer: forward against the reference's
+fake-quant path (golden output of the real fp4_linear.MXFP4Linear), the
+straight-through backward against the reference's gradients, and the MXFP4
+backward against its oracle composition (quantize along the contracted axis,
+dequantize, fp32 matmul)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_port
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(u16):
+    return torch.from_numpy(u16.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def _close(got, ref, what, rel_tol=1e-3):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    rel = ((got - ref).norm() / ref.norm()).item()
+    assert rel <= rel_tol, f"{what}: rel-L2 {rel:.3e}"
+
+
+def test_forward_and_ste_backward_against_reference_golden(golden):
+    from lockstep_b200 import fp4_linear
+    gd = golden("linear_ste")
+    lin = fp4_linear.MXFP4Linear(256, 160).cuda()
+    assert fp4_linear.FP4Linear is fp4_linear.MXFP4Linear and fp4_linear.path() == "tcgen05-mxfp4"
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(gd["w"]))
+    x = _bf16(gd["x"]).cuda().requires_grad_(True)
+    y = lin(x)
+    assert y.shape == (4, 24, 160) and y.dtype == torch.bfloat16
+    _close(y, _bf16(gd["y"]), "forward")
+    worst = ((y.float().cpu() - _bf16(gd["y"]).float()).abs().reshape(-1, 160) /
+             _bf16(gd["y"]).float().abs().reshape(-1, 160).amax(1, keepdim=True)).max().item()
+    assert worst <= 2e-2
+    y.backward(_bf16(gd["gy"]).cuda())
+    _close(x.grad, _bf16(gd["gx"]), "dX (ste)", 1e-2)          # bf16 matmuls, different GEMM library
+    _close(lin.weight.grad, torch.from_numpy(gd["gw"]), "dW (ste)", 1e-2)
+    with pytest.raises(AssertionError):
+        fp4_linear.MXFP4Linear(8, 8, bias=True)
+
+
+def test_autocast_dtype_follows_reference():
+    from lockstep_b200 import fp4_linear
+    lin = fp4_linear.MXFP4Linear(128, 128).cuda()
+    x = torch.randn(4, 128, device="cuda")
+    with torch.autocast("cuda", torch.bfloat16):
+        assert lin(x).dtype == torch.bfloat16                 # fp4_linear.py:56
+    assert lin(x).dtype == torch.float32
+
+
+def test_mxfp4_backward_against_oracle():
+    from lockstep_b200 import fp4_linear
+    T, K, N = 256, 384, 512
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    w = torch.randn(N, K, generator=g) * 0.02
+    gy = torch.randn(T, N, generator=g).bfloat16()
+    lin = fp4_linear.MXFP4Linear(K, N, backward="mxfp4").cuda()
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    xin = x.cuda().requires_grad_(True)
+    lin(xin).backward(gy.cuda())
+
+    def fq(t):                                                 # quantize along the last axis, dequantize
+        return ref_port.dequantize(*ref_port.quantize(t))
+    gx_ref = fq(gy) @ fq(w.t().contiguous()).t()               # contract over N
+    gw_ref = fq(gy.t().contiguous()) @ fq(x.t().contiguous()).t()   # contract over tokens
+    _close(xin.grad, gx_ref.bfloat16(), "dX (mxfp4)")
+    _close(lin.weight.grad, gw_ref, "dW (mxfp4)")
+
+
+def test_tiny_gpt_trains():
+    from lockstep_b200 import gpt
+    sec, loss0 = gpt.training_step_time(layers=2, dim=256, heads=4, seq=128, batch=8, vocab=512, steps=1, warmup=1)
+    sec, loss1 = gpt.training_step_time(layers=2, dim=256, heads=4, seq=128, batch=8, vocab=512, steps=8, warmup=1)
+    assert np.isfinite(loss1) and loss1 < loss0               # the loss goes down on a repeated batch
