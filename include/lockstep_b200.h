@@ -109,6 +109,11 @@ int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t
                        const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
                        void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 
+/* Which GEMM kernel the two entry points above launch: 0 = by shape (default),
+ * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles
+ * (cta_group::2).  Results are identical; for measurements and tests. */
+int ls_gemm_set_variant(int variant);
+
 /* Synchronises the device's error word to the host: returns LS_ETIMEOUT (and
  * clears the word) if any GEMM kernel since the last call abandoned a bounded
  * wait, LS_OK otherwise.  `status_host` (host int, may be NULL) receives the

@@ -16,6 +16,7 @@
 // epilogue drains the shared columns first and only then lets the next tile's
 // MMAs start.
 #include <cuda.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -84,6 +85,37 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, in
                 reinterpret_cast<uint4 *>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
         } else {
             for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __uint_as_float(r[j]);
+        }
+    }
+}
+
+// One pipeline stage on the tensor pipe: scale tiles shared -> tensor memory, then the
+// K = 64 MMAs.  ATOMS = number of 128-element k-tiles in the stage (2, or 1 at the K
+// tail); everything else is a compile-time offset so that the issuing thread spends
+// its time on the tcgen05 instructions, not on address arithmetic.
+template <int CTAS, int ATOMS, int SFB_ATOMS>
+__device__ __forceinline__ void issue_stage(uint32_t acc, uint64_t adesc, uint64_t bdesc, uint64_t sfa_desc,
+                                            uint64_t sfb_desc, uint32_t sfa_t, uint32_t sfb_t, uint32_t idesc,
+                                            bool first_of_tile, bool skip_cp, bool skip_mma)
+{
+    constexpr int SFB_COLS = 4 * SFB_ATOMS;                 // columns per k-tile
+    if (!skip_cp) {
+#pragma unroll
+        for (int j = 0; j < ATOMS; j++) {
+            ptx::tmem_cp_sf<CTAS>(sfa_t + 4 * j, sfa_desc + 32 * j);
+#pragma unroll
+            for (int r = 0; r < SFB_ATOMS; r++)
+                ptx::tmem_cp_sf<CTAS>(sfb_t + SFB_COLS * j + 4 * r, sfb_desc + 64 * r + 32 * j);
+        }
+    }
+    if (!skip_mma) {
+#pragma unroll
+        for (int kb = 0; kb < 2 * ATOMS; kb++) {
+            constexpr uint32_t kId[2] = {0u, 2u};           // byte of the scale column used by this MMA
+            const uint32_t id = kId[kb & 1];
+            ptx::mma_mxf4<CTAS>(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc | (id << 29) | (id << 4),
+                                sfa_t + 4 * (kb >> 1) + (id << 30), sfb_t + SFB_COLS * (kb >> 1) + (id << 30),
+                                (kb == 0 && first_of_tile) ? 0u : 1u);
         }
     }
 }
@@ -172,6 +204,9 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         // ------------------------------------------------------------ MMA issuer
         if (ptx::elect_one()) {
             constexpr uint32_t idesc = ptx::idesc_mxf4(BM, BN);
+            const uint64_t adesc0 = ptx::desc_sw128(smem_base), bdesc0 = ptx::desc_sw128(smem_base + C::A_BYTES);
+            const uint64_t sfadesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES);
+            const uint64_t sfbdesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES + C::SFA_BYTES);
             uint32_t it = 0;
             int lt = 0;
             bool ok = true;
@@ -184,25 +219,13 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
                     ptx::tc_fence_after();
-                    const int atoms = min(2, k_atoms - 2 * kt);
-                    const uint32_t st = smem_base + s * C::STAGE_BYTES;
-                    const uint32_t sfa_s = st + C::A_BYTES + C::B_BYTES, sfb_s = sfa_s + C::SFA_BYTES;
-                    for (int j = 0; j < atoms; j++) {
-                        ptx::tmem_cp_sf<1>(tmem_base + C::SFA_COL + 4 * j, ptx::desc_sf(sfa_s + 512 * j));
-#pragma unroll
-                        for (int r = 0; r < BN / 128; r++)
-                            ptx::tmem_cp_sf<1>(tmem_base + C::SFB_COL + (BN / 32) * j + 4 * r,
-                                               ptx::desc_sf(sfb_s + 1024 * r + 512 * j));
-                    }
-                    const uint64_t adesc = ptx::desc_sw128(st), bdesc = ptx::desc_sw128(st + C::A_BYTES);
-                    for (int kb = 0; kb < 2 * atoms; kb++) {
-                        const uint32_t id = (kb & 1) * 2u;                 // byte of the scale column
-                        ptx::mma_mxf4<1>(acc, adesc + 2 * kb, bdesc + 2 * kb,
-                                         idesc | (id << 29) | (id << 4),
-                                         tmem_base + C::SFA_COL + 4 * (kb >> 1) + (id << 30),
-                                         tmem_base + C::SFB_COL + (BN / 32) * (kb >> 1) + (id << 30),
-                                         (kt | kb) ? 1u : 0u);
-                    }
+                    const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);       // stage offset in 16-byte units
+                    if (2 * kt + 2 <= k_atoms)
+                        issue_stage<1, 2, BN / 128>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == 0, false, false);
+                    else
+                        issue_stage<1, 1, BN / 128>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == 0, false, false);
                     ptx::tc_commit(empty_bar(s));
                 }
                 if (ok) ptx::tc_commit(acc_full_bar);
@@ -249,6 +272,214 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// ---- CTA-pair kernel ---------------------------------------------------------------
+// Two CTAs of a cluster work on one 256 x 256 tile with cta_group::2 MMAs: each
+// CTA stages its own 128 rows of A and its own 128 rows (half) of the W tile,
+// the tensor cores of both SMs read both halves of W, and each CTA's tensor
+// memory receives the accumulator of its own 128 rows.  Per SM this halves the
+// shared-memory traffic of the W operand and makes room for six stages.
+// Dual batch: CTA 0 takes batch 0's row tile, CTA 1 batch 1's, against the same
+// W tile -- the two activation batches share one weight stream inside the MMA.
+// Single batch: the pair takes two consecutive row tiles.
+//
+// Roles per CTA: warp 0 lane: TMA producer for this CTA's stage halves (every
+// load of either CTA completes on CTA 0's barrier).  Warp 1 lane of CTA 0: the
+// MMA issuer for the pair (warp 1 of CTA 1 only takes part in the tensor-memory
+// allocation).  Warps 2-5: epilogue.
+struct PairCfg {
+    static constexpr int BN = 256;                         // tile columns (128 rows of W per CTA)
+    static constexpr int STAGES = 6;
+    static constexpr int A_BYTES = BM * BKB;               // 16 KB
+    static constexpr int B_BYTES = 128 * BKB;              // this CTA's half of the W tile
+    static constexpr int SFA_BYTES = 1024;
+    static constexpr int SFB_BYTES = 2048;                 // scales of all 256 W rows, in both CTAs
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    // Tensor memory: accumulators [0,256) and [224,480) share 32 columns; scale columns
+    // at 480 (8 for A, 16 for W).  A second set of scale columns (tried with a 64-column
+    // overlap) did not speed the kernel up.
+    static constexpr int OVL = 32;
+    static constexpr int ACC1 = BN - OVL;                  // 224
+    static constexpr int SF_COL = 2 * BN - OVL;            // 480
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
+                       const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfa0,
+                       const __grid_constant__ CUtensorMap tm_sfa1, const __grid_constant__ CUtensorMap tm_sfb,
+                       const GemmParams p)
+{
+    using C = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
+    const uint32_t acc_full_bar = bar_base + 8u * (2 * C::STAGES);
+    const uint32_t acc_free_bar = acc_full_bar + 8u;                                    // used in CTA 0
+    const uint32_t tmem_slot = acc_free_bar + 8u;
+    uint8_t *gen_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_p =
+        reinterpret_cast<volatile uint32_t *>(gen_base + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 2));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot_p + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = cluster_ctarank();                 // 0 = leader
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + C::BN - 1) / C::BN;
+    const int mp_tiles = p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2;   // row-tile pairs
+    const int total = mp_tiles * n_tiles;
+    const int k_tiles = (p.K / 2 + BKB - 1) / BKB;
+    const int k_atoms = p.K / 128;
+    // this CTA's batch and row tile inside pair-tile index mp
+    const int my_batch = p.nbatch == 2 ? int(cta) : 0;
+    auto my_mtile = [&](int mp) { return p.nbatch == 2 ? mp : 2 * mp + int(cta); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        ptx::mbar_init(acc_full_bar, 1);
+        ptx::mbar_init(acc_free_bar, 8);                    // 4 epilogue warps of each CTA
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<2>(tmem_slot, kTmemCols);
+        ptx::tmem_relinquish<2>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                         // both CTAs' barriers exist before any remote arrive
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_p;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (both CTAs)
+        // Every load of either CTA completes on CTA 0's "full" barrier of the stage: the
+        // MMA thread there waits once for both halves.  All boxes have a fixed size
+        // (rows or scale tiles outside the tensors are zero-filled), so the byte count
+        // per stage is constant.
+        if (ptx::elect_one()) {
+            const CUtensorMap *tma = my_batch ? &tm_a1 : &tm_a0;
+            const CUtensorMap *tsfa = my_batch ? &tm_sfa1 : &tm_sfa0;
+            ptx::prefetch_tmap(tma);
+            ptx::prefetch_tmap(&tm_b);
+            ptx::prefetch_tmap(tsfa);
+            ptx::prefetch_tmap(&tm_sfb);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += npairs) {
+                const int mp = t % mp_tiles, nt = t / mp_tiles;
+                const int mt = my_mtile(mp);
+                for (int kt = 0; kt < k_tiles; kt++) {
+                    if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag))) break;
+                    const uint32_t st = smem_base + s * C::STAGE_BYTES;
+                    const uint32_t bar = ptx::map_to_cta(full_bar(s), 0);
+                    if (cta == 0) ptx::mbar_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);
+                    ptx::tma_load_2d_pair(st, tma, kt * BKB, mt * BM, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES, &tm_b, kt * BKB, nt * C::BN + int(cta) * 128, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES, tsfa, 0, mt * k_atoms + 2 * kt, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES, &tm_sfb, 0,
+                                          (2 * nt) * k_atoms + 2 * kt, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + 1024, &tm_sfb, 0,
+                                          (2 * nt + 1) * k_atoms + 2 * kt, bar);
+                    if (++s == C::STAGES) s = 0, ph ^= 1;
+                }
+            }
+            for (int i = 0; i < C::STAGES && ok; i++) {     // wait until the MMA side is done with every stage
+                ok = ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag);
+                if (++s == C::STAGES) s = 0, ph ^= 1;
+            }
+        }
+    } else if (warp == 1 && cta == 0) {
+        // ------------------------------------------------------------ MMA issuer (CTA 0, for the pair)
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_mxf4(256, C::BN);
+            const uint64_t adesc0 = ptx::desc_sw128(smem_base), bdesc0 = ptx::desc_sw128(smem_base + C::A_BYTES);
+            const uint64_t sfadesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES);
+            const uint64_t sfbdesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES + C::SFA_BYTES);
+            int s = 0, lt = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += npairs, lt++) {
+                if (lt > 0 && !(ok = ptx::mbar_wait(acc_free_bar, (lt - 1) & 1, abort_flag))) break;
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0);
+                for (int kt = 0; kt < k_tiles; kt++) {
+                    if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
+                    ptx::tc_fence_after();
+                    const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);
+                    const uint32_t sfa_t = tmem_base + C::SF_COL, sfb_t = sfa_t + 8;
+                    if (2 * kt + 2 <= k_atoms)
+                        issue_stage<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
+                                             sfb_t, idesc, kt == 0, false, false);
+                    else
+                        issue_stage<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
+                                             sfb_t, idesc, kt == 0, false, false);
+                    ptx::tc_commit_pair(empty_bar(s), 3);      // frees the stage in both CTAs
+                    if (++s == C::STAGES) s = 0, ph ^= 1;
+                }
+                if (ok) ptx::tc_commit_pair(acc_full_bar, 3);  // publishes the tile to both epilogues
+            }
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ epilogue (both CTAs)
+        const int q = warp & 3;
+        int lt = 0;
+        bool ok = true;
+        for (int t = pair; t < total && ok; t += npairs, lt++) {
+            const int mp = t % mp_tiles, nt = t / mp_tiles;
+            const int mt = my_mtile(mp);
+            if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
+            ptx::tc_fence_after();
+            const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
+            const int row = mt * BM + 32 * q + lane;
+            constexpr int CH = C::BN / 32;
+            constexpr int SHARED = C::OVL / 32;             // chunks shared with the other accumulator
+            const int first = !(lt & 1) ? CH - SHARED : 0;
+            for (int i = 0; i < CH; i++) {
+                const int c = (first + i) % CH;
+                uint32_t r[32];
+                ptx::tmem_ld32(acc + 32 * c, r);
+                ptx::tmem_ld_wait();
+                if (i == SHARED - 1) {                      // shared columns drained: next tile may start
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
+                }
+                store_chunk(p, p.c[my_batch], row, nt * C::BN + 32 * c, r);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        for (int i = 0; i < 4096; i++) __nanosleep(256);
+        if (threadIdx.x == 0) atomicExch(p.err, 1);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                         // neither CTA leaves while the other may still signal it
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<2>(tmem_base, kTmemCols);
     }
 }
 
@@ -305,6 +536,62 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
     return LS_OK;
 }
 
+// Scale-factor buffer as [tiles, 128] 32-bit words (512 bytes per 128-row x 4-block tile);
+// one box = two consecutive k-tiles of one row tile.
+int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K)
+{
+    EncodeFn fn = encode_fn();
+    if (!fn) return fail(LS_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {128, cuuint64_t(((rows + 127) / 128) * (K / 128))};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, 2};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LS_ECUDA, "cuTensorMapEncodeTiled (scales) failed with %d", int(r));
+    return LS_OK;
+}
+
+int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
+                cudaStream_t st)
+{
+    CUtensorMap tsa0, tsa1, tsb;
+    if (int rc = make_sf_map(&tsa0, p.sfa[0], p.M, p.K)) return rc;
+    if (int rc = make_sf_map(&tsa1, p.sfa[1], p.M, p.K)) return rc;
+    if (int rc = make_sf_map(&tsb, p.sfb, p.N, p.K)) return rc;
+    using C = PairCfg;
+    static int resident_pairs[64] = {};
+    int dev = 0;
+    LS_CUDA(cudaGetDevice(&dev));
+    if (!resident_pairs[dev]) {
+        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        // The kernel is persistent: the grid must not exceed the CTA pairs that can be
+        // resident at once (fewer than SMs / 2 when a TPC has a single SM enabled).
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
+        cfg.blockDim = dim3(kGemmThreads, 1, 1);
+        cfg.dynamicSmemBytes = C::SMEM;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
+        cfg.attrs = at, cfg.numAttrs = 1;
+        int n = 0;
+        LS_CUDA(cudaOccupancyMaxActiveClusters(&n, mxfp4_gemm_pair_kernel, &cfg));
+        if (n < 1) return fail(LS_ECUDA, "no CTA pair of the GEMM kernel fits on this device");
+        resident_pairs[dev] = n;
+    }
+    int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + C::BN - 1) / C::BN;
+    int pairs = (p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2) * n_tiles;
+    int max_pairs = resident_pairs[dev];
+    int grid = 2 * (pairs < max_pairs ? pairs : max_pairs);
+    mxfp4_gemm_pair_kernel<<<grid, kGemmThreads, C::SMEM, st>>>(ta0, ta1, tb, tsa0, tsa1, tsb, p);
+    LS_LAUNCH_CHECK("mxfp4_gemm_pair");
+    return LS_OK;
+}
+
+int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
+
 }  // namespace
 
 int *error_word()
@@ -346,7 +633,8 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     CUtensorMap ta0, ta1, tb;
     if (int rc = make_operand_map(&ta0, a0, M, K / 2, BM)) return rc;
     if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, BM)) return rc;
-    if (int rc = make_operand_map(&tb, w, N, K / 2, bn)) return rc;
+    const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && (nbatch == 2 || M > BM));
+    if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
     p.sfa[1] = nbatch == 2 ? sfa1 : sfa0;
@@ -357,6 +645,7 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     p.nbatch = nbatch;
     p.out_bf16 = out_dtype == LS_BF16;
     p.err = err;
+    if (pair) return launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
     return launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
 }
 
@@ -387,4 +676,11 @@ extern "C" int ls_gemm_status(int *status_host)
     if (v) LS_CUDA(cudaMemset(err, 0, sizeof(int)));
     if (status_host) *status_host = v;
     return v ? fail(LS_ETIMEOUT, "a GEMM kernel gave up waiting on a barrier") : LS_OK;
+}
+
+extern "C" int ls_gemm_set_variant(int variant)
+{
+    if (variant < 0 || variant > 2) return fail(LS_EINVAL, "variant must be 0, 1 or 2");
+    g_gemm_variant = variant;
+    return LS_OK;
 }
