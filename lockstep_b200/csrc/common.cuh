@@ -110,6 +110,22 @@ __device__ __forceinline__ float e2m1_value(uint32_t code)
     return __uint_as_float(__float_as_uint(v) | ((code & 8u) << 28));
 }
 
+// Four E2M1 codes (the low 16 bits of pk) -> their fp32 values, by two byte-permute
+// table lookups: the upper 16 bits of the fp32 pattern of each magnitude are
+// 0000 3F00 3F80 3FC0 4000 4040 4080 40C0, the lower 16 bits are zero.
+__device__ __forceinline__ void e2m1x4_values(uint32_t pk, float (&v)[4])
+{
+    const uint32_t sel = pk & 0x7777u;
+    const uint32_t tops = __byte_perm(0x3F3F3F00u, 0x40404040u, sel);     // byte i: bits 31..24 of value i
+    const uint32_t secs = __byte_perm(0xC0800000u, 0xC0804000u, sel);     // byte i: bits 23..16 of value i
+    const uint32_t a01 = __byte_perm(tops, secs, 0x1504u);                // value 1 in the high half, 0 in the low
+    const uint32_t a23 = __byte_perm(tops, secs, 0x3726u);
+    v[0] = __uint_as_float((a01 << 16) | ((pk << 28) & 0x80000000u));
+    v[1] = __uint_as_float((a01 & 0xFFFF0000u) | ((pk << 24) & 0x80000000u));
+    v[2] = __uint_as_float((a23 << 16) | ((pk << 20) & 0x80000000u));
+    v[3] = __uint_as_float((a23 & 0xFFFF0000u) | ((pk << 16) & 0x80000000u));
+}
+
 // Two floats -> one byte of two E2M1 codes (lo in the low nibble), hardware
 // round-to-nearest-even with saturation.
 __device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&q)[8])

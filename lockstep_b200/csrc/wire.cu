@@ -161,36 +161,35 @@ __global__ void __launch_bounds__(kThreads)
 wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, WireGeom geo, Peers peers,
                  uint32_t epoch)
 {
-    const int64_t groups = geo.padded / 8;
-    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    const uint32_t stride = gridDim.x * kThreads;
     const int lane = threadIdx.x & 31;
-    const int64_t g_per_shard = geo.shard / 8;
-    for (int64_t base = int64_t(blockIdx.x) * kThreads; base < groups; base += stride) {
-        const int64_t g8 = base + threadIdx.x;           // padded % 256 == 0: whole warps stay in range
-        if (base + (threadIdx.x & ~31) >= groups) continue;
-        const int64_t i0 = g8 * 8;
-        float v[8], dq[8];
-        load8(g, i0, n, v);
-        if (res) {
-            float r[8];
-            load8(res, i0, geo.padded, r);
-#pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
-        }
-        uint32_t e8;
-        const uint32_t pk = encode8(v, e8, dq);
-        if (res) {
-            float r[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], dq[i]);
-            store8(res, i0, geo.padded, r);
-        }
-        const int o = int(g8 / g_per_shard);
-        const int64_t in_shard = g8 - int64_t(o) * g_per_shard;
+    const uint32_t g_per_shard = uint32_t(geo.shard / 8);      // a multiple of 32: warps never straddle shards
+    for (int o = 0; o < geo.world; o++) {
         uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
-        reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
-        const uint2 ex = gather_exponents(e8);
-        if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + in_shard / 4) = ex;
+        uint8_t *slot_e = slot + geo.shard / 2;
+        const int64_t first = int64_t(o) * geo.shard;          // first element of the shard
+        for (uint32_t in_shard = blockIdx.x * kThreads + threadIdx.x; in_shard - lane < g_per_shard; in_shard += stride) {
+            const int64_t i0 = first + int64_t(in_shard) * 8;
+            float v[8], dq[8];
+            load8(g, i0, n, v);
+            if (res) {
+                float r[8];
+                load8(res, i0, geo.padded, r);
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
+            }
+            uint32_t e8;
+            const uint32_t pk = encode8(v, e8, dq);
+            if (res) {
+                float r[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], dq[i]);
+                store8(res, i0, geo.padded, r);
+            }
+            reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
+            const uint2 ex = gather_exponents(e8);
+            if (lane == 0) *reinterpret_cast<uint2 *>(slot_e + in_shard / 4) = ex;
+        }
     }
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
     signal_done(mine, &mine->counter[0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
@@ -217,9 +216,14 @@ wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t
             const uint8_t *slot = my + geo.rs_off + int64_t(s) * geo.slot_bytes;
             const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[g8];
             const float sc = __uint_as_float(scale_bits(slot[geo.shard / 2 + g8 / 4]));
+            float lo[4], hi[4];
+            e2m1x4_values(pk, lo);
+            e2m1x4_values(pk >> 16, hi);
 #pragma unroll
-            for (int i = 0; i < 8; i++)
-                val[i] = __fadd_rn(val[i], __fmul_rn(e2m1_value((pk >> (4 * i)) & 0xFu), sc));
+            for (int i = 0; i < 4; i++) {
+                val[i] = __fadd_rn(val[i], __fmul_rn(lo[i], sc));
+                val[4 + i] = __fadd_rn(val[4 + i], __fmul_rn(hi[i], sc));
+            }
         }
         if (ores) {
             float r[8];
@@ -246,26 +250,59 @@ wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t
 }
 
 // ---- phase 3: everyone ---------------------------------------------------------------
+// One thread decodes 4 values (two packed bytes) per step and writes one 16-byte
+// word, so every load and store of a warp is one contiguous segment.  POW2: the
+// world size is a power of two, so dividing by it is an exact multiplication that
+// folds into the block scale.
+template <bool POW2>
 __global__ void __launch_bounds__(kThreads)
 wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
 {
+    constexpr int U = 4;                                        // independent quads in flight per thread
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
     wait_flags(mine, mine->ag_flag, geo.world, epoch);
-    const int64_t groups = (n + 7) / 8;
-    const int64_t stride = int64_t(gridDim.x) * kThreads;
-    const int64_t g_per_shard = geo.shard / 8;
-    const float w = float(geo.world);
-    for (int64_t g8 = int64_t(blockIdx.x) * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
-        const int o = int(g8 / g_per_shard);
-        const int64_t in_shard = g8 - int64_t(o) * g_per_shard;
+    const uint32_t stride = gridDim.x * kThreads;
+    const uint32_t q_per_shard = uint32_t(geo.shard / 4);
+    const float w = float(geo.world), rw = 1.0f / w;
+    const bool vec = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+    for (int o = 0; o < geo.world; o++) {
         const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
-        const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[in_shard];
-        const float sc = __uint_as_float(scale_bits(slot[geo.shard / 2 + in_shard / 4]));
-        float v[8];
+        const uint8_t *slot_e = slot + geo.shard / 2;
+        const int64_t first = int64_t(o) * geo.shard;
+        if (first >= n) break;
+        const int64_t left = (n - first + 3) / 4;
+        const uint32_t count = left < int64_t(q_per_shard) ? uint32_t(left) : q_per_shard;
+        float *gs = g + first;
+        const int64_t ns = n - first;                           // elements of g in this shard and beyond
+        for (uint32_t q0 = blockIdx.x * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
+            uint32_t pk[U], e8[U];
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = __fdiv_rn(__fmul_rn(e2m1_value((pk >> (4 * i)) & 0xFu), sc), w);
-        store8(g, g8 * 8, n, v);
+            for (int u = 0; u < U; u++) {
+                const uint32_t q = q0 + u * stride;
+                const bool ok = q < count;
+                pk[u] = ok ? reinterpret_cast<const uint16_t *>(slot)[q] : 0u;
+                e8[u] = ok ? slot_e[q >> 3] : 127u;
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const uint32_t q = q0 + u * stride;
+                if (q >= count) break;
+                float sc = __uint_as_float(scale_bits(e8[u]));
+                if (POW2) sc = __fmul_rn(sc, rw);
+                float t[4];
+                e2m1x4_values(pk[u], t);
+#pragma unroll
+                for (int i = 0; i < 4; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
+                const int64_t i0 = int64_t(q) * 4;
+                if (vec && i0 + 4 <= ns) {
+                    *reinterpret_cast<float4 *>(gs + i0) = make_float4(t[0], t[1], t[2], t[3]);
+                } else {
+                    for (int i = 0; i < 4; i++)
+                        if (i0 + i < ns) gs[i0 + i] = t[i];
+                }
+            }
+        }
     }
 }
 
@@ -403,8 +440,10 @@ extern "C" int ls_wire_finish(void *h, float *g, int64_t numel, void *stream)
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
-    wire_finish_kernel<<<grid_for((numel + 7) / 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        g, numel, w->g, w->peers, w->epoch);
+    const bool pow2 = (w->g.world & (w->g.world - 1)) == 0;
+    const int grid = grid_for((numel + 15) / 16);        // four quads per thread and step
+    if (pow2) wire_finish_kernel<true><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(g, numel, w->g, w->peers, w->epoch);
+    else wire_finish_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(g, numel, w->g, w->peers, w->epoch);
     LS_LAUNCH_CHECK("wire_finish");
     return LS_OK;
 }

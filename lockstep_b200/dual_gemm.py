@@ -57,7 +57,20 @@ def dual_mxfp4_packed(a1_pk, a2_pk, bt_pk, a1_scale, a2_scale, b_scale, out_dtyp
 
 def dual_mxfp4(x1, x2, w_pk, w_sf, out_dtype=torch.bfloat16):
     """Quantize two bf16/fp32 activation batches on the fly and multiply both
-    by a pre-quantized weight (packed bytes + scale-factor buffer)."""
+    by a pre-quantized weight (packed bytes + scale-factor buffer).
+
+    When the two batches are the two halves of one allocation (as the
+    reference's train_step.py:97-103 lays its microbatches out) and the batch
+    height is a multiple of 128, both are quantized by a single launch."""
+    M, K = x1.shape
+    adjacent = (x1.is_contiguous() and x2.is_contiguous() and x1.dtype == x2.dtype and x1.shape == x2.shape
+                and M % 128 == 0 and x2.data_ptr() == x1.data_ptr() + x1.numel() * x1.element_size()
+                and x1.untyped_storage().data_ptr() == x2.untyped_storage().data_ptr())
+    if adjacent:
+        both = torch.as_strided(x1, (2 * M, K), (K, 1))
+        p, sf = fp4.quantize_mxfp4_packed(both)
+        half = sf.numel() // 2
+        return dual_mxfp4_packed(p[:M], p[M:], w_pk, sf[:half], sf[half:], w_sf, out_dtype)
     p1, s1 = fp4.quantize_mxfp4_packed(x1)
     p2, s2 = fp4.quantize_mxfp4_packed(x2)
     return dual_mxfp4_packed(p1, p2, w_pk, s1, s2, w_sf, out_dtype)
