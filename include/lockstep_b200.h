@@ -52,7 +52,7 @@ int64_t ls_sf_bytes(int64_t rows, int64_t K);
 /* Fused MXFP4 quantizer along the last dimension.
  * Replaces fp4.py:57-72 (quantize_mxfp4), :43-54 (_round_to_e2m1) and,
  * through `packed`, :91-94 (pack_fp4).
- *   x        [rows, K] row-major, LS_F32 or LS_BF16; 16-byte aligned
+ *   x        [rows, K] row-major, LS_F32 or LS_BF16; 32-byte aligned
  *   block    32 or 16; K % block == 0
  * Outputs, each may be NULL (at least one must not be):
  *   codes    [rows, K] one E2M1 code per byte (bit 3 = sign)

@@ -144,6 +144,24 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&q)[8])
     return out;
 }
 
+// Eight finite fp32 values -> eight E2M1 codes with the reference rule (halfway keeps
+// the smaller magnitude), through the hardware converter.  The converter rounds
+// halfway cases to even; the seven halfway points all have their low 21 mantissa
+// bits clear, so every non-zero value with those bits clear is first moved one ulp
+// toward zero: a halfway value then rounds down, and no other value changes its
+// code (one ulp cannot carry a value with clear low bits across a halfway point).
+__device__ __forceinline__ uint32_t cvt_ref_e2m1x8(const float (&q)[8])
+{
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t u = __float_as_uint(q[i]);
+        const bool nudge = ((u << 11) == 0u) && ((u << 1) != 0u);
+        r[i] = __uint_as_float(u - (nudge ? 1u : 0u));
+    }
+    return cvt_e2m1x8(r);
+}
+
 // byte offset of the scale factor of (row, kblock) in the tcgen05 layout:
 // tiles of 128 rows x 4 k-blocks (512 B), k-tiles innermost; inside a tile
 // row r sits at (r % 32) * 16 + (r / 32) * 4 + (kblock % 4).

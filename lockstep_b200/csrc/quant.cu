@@ -30,20 +30,30 @@ __device__ __forceinline__ uint32_t div_kblocks(const QuantOut &o, uint32_t b)
 // consecutive groups; a "quad" (16 lanes, BLOCK = 32) covers 4 consecutive
 // blocks of one row, whose exponent bytes are contiguous in every scale
 // output, so one lane per quad writes them as one word.
+__device__ __forceinline__ uint32_t spread_codes(uint32_t h)   // 16 bits -> 4 code bytes
+{
+    return (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
+}
+
+// Exponent bytes of 4 consecutive blocks -> every scale output, written by the lane
+// that owns the first of the four.  LPB = lanes per block.
+template <int LPB>
+__device__ __forceinline__ void store_scales(const QuantOut &o, uint32_t blk_of_lane, uint32_t e8, bool in_range);
+
 template <int BLOCK>
 __device__ __forceinline__ void store_group(const QuantOut &o, uint32_t g8, uint32_t pk, uint32_t e8, bool in_range)
 {
     constexpr int LPB = BLOCK / 8;
     if (in_range) {
         if (o.packed) reinterpret_cast<uint32_t *>(o.packed)[g8] = pk;
-        if (o.codes) {
-            uint2 c;
-            c.x = (pk & 0xFu) | ((pk & 0xF0u) << 4) | ((pk & 0xF00u) << 8) | ((pk & 0xF000u) << 12);
-            uint32_t h = pk >> 16;
-            c.y = (h & 0xFu) | ((h & 0xF0u) << 4) | ((h & 0xF00u) << 8) | ((h & 0xF000u) << 12);
-            reinterpret_cast<uint2 *>(o.codes)[g8] = c;
-        }
+        if (o.codes) reinterpret_cast<uint2 *>(o.codes)[g8] = make_uint2(spread_codes(pk & 0xFFFFu), spread_codes(pk >> 16));
     }
+    store_scales<LPB>(o, g8 / LPB, e8, in_range);
+}
+
+template <int LPB>
+__device__ __forceinline__ void store_scales(const QuantOut &o, uint32_t blk_of_lane, uint32_t e8, bool in_range)
+{
     // gather 4 consecutive blocks' exponent bytes into the first lane of each group of 4 blocks
     uint32_t w = e8;
     w |= __shfl_down_sync(0xFFFFFFFFu, e8, LPB) << 8;
@@ -51,7 +61,7 @@ __device__ __forceinline__ void store_group(const QuantOut &o, uint32_t g8, uint
     w |= __shfl_down_sync(0xFFFFFFFFu, e8, 3 * LPB) << 24;
     const uint32_t lane = threadIdx.x & 31;
     if (in_range && (lane & (4 * LPB - 1)) == 0) {
-        const uint32_t blk = g8 / LPB;                  // first of 4 blocks, blk % 4 == 0
+        const uint32_t blk = blk_of_lane;               // first of 4 blocks, blk % 4 == 0
         if (blk + 4 <= o.nblocks) {
             if (o.e8m0) *reinterpret_cast<uint32_t *>(o.e8m0 + blk) = w;
             if (o.scale) {
@@ -86,39 +96,54 @@ __device__ __forceinline__ uint32_t codes8(const float (&q)[8])
 }
 
 // ---- bf16 input -------------------------------------------------------------
-// One thread owns 8 consecutive elements (one 16-byte load); BLOCK/8 adjacent
-// lanes share a quantization block.  The codes come from the hardware
-// E2M1 converter (round-to-nearest-even).  For the reference rule (halfway
-// keeps the smaller magnitude) the divisor carries a factor (1 - 2^-12): a
-// bf16 value has 8 significant bits, the factor 12, so the product is exact
-// in fp32, lies strictly below every halfway point the value sat on, and
-// never crosses one it did not.  Each CTA handles kUnroll * 256 groups; all of
-// a thread's loads are issued before the first use.
+// One thread owns 16 consecutive elements (one 32-byte load); two adjacent lanes
+// share a block of 32 (a thread owns a whole block of 16).  The codes come from
+// the hardware E2M1 converter (round-to-nearest-even).  For the reference rule
+// (halfway keeps the smaller magnitude) the divisor carries a factor
+// (1 - 2^-12): a bf16 value has 8 significant bits, the factor 12, so the
+// product is exact in fp32, lies strictly below every halfway point the value
+// sat on, and never crosses one it did not.  Each CTA handles kUnroll16 * 256
+// groups; all of a thread's loads are issued before the first use.
+constexpr int kUnroll16 = 2;
+
+struct U8x32 { uint32_t w[8]; };
+
+__device__ __forceinline__ U8x32 ld_stream32(const void *p)
+{
+    U8x32 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                   "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+    return v;
+}
+
 template <int BLOCK, bool RNE>
 __global__ void __launch_bounds__(kThreads)
-quantize_bf16_kernel(const uint4 *__restrict__ x, uint32_t n8, QuantOut o)
+quantize_bf16_kernel(const uint8_t *__restrict__ x, uint32_t n16, QuantOut o)
 {
-    constexpr int LPB = BLOCK / 8;
-    const uint32_t base = blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
-    uint4 v[kUnroll];
+    constexpr int LPB = BLOCK / 16;                    // 2 or 1 lanes per block
+    const uint32_t base = blockIdx.x * (kThreads * kUnroll16) + threadIdx.x;
+    U8x32 v[kUnroll16];
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++) {
-        const uint32_t g8 = base + u * kThreads;
-        v[u] = g8 < n8 ? ld_stream(x + g8) : make_uint4(0, 0, 0, 0);
+    for (int u = 0; u < kUnroll16; u++) {
+        const uint32_t g = base + u * kThreads;
+        if (g < n16) v[u] = ld_stream32(x + size_t(g) * 32);
+        else
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[u].w[i] = 0u;
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; u++) {
-        const uint32_t g8 = base + u * kThreads;
-        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+    for (int u = 0; u < kUnroll16; u++) {
+        const uint32_t g = base + u * kThreads;
+        const uint32_t(&w)[8] = v[u].w;
         // |x| maxima on packed bf16 pairs, NaN-propagating
         __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
 #pragma unroll
-        for (int i = 1; i < 4; i++)
+        for (int i = 1; i < 8; i++)
             m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
         uint32_t mb = *reinterpret_cast<uint32_t *>(&m);
-#pragma unroll
-        for (int off = 1; off < LPB; off <<= 1) {
-            uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, mb, off);
+        if (LPB == 2) {
+            uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, mb, 1);
             __nv_bfloat162 mm = __hmax2_nan(*reinterpret_cast<__nv_bfloat162 *>(&mb),
                                             *reinterpret_cast<__nv_bfloat162 *>(&other));
             mb = *reinterpret_cast<uint32_t *>(&mm);
@@ -127,54 +152,67 @@ quantize_bf16_kernel(const uint4 *__restrict__ x, uint32_t n8, QuantOut o)
         // a bf16 maximum is never within 44 ulps (fp32) below a power of two: plain exponent
         uint32_t e8 = (max(amax, kBitsClamp) >> 23) - 2u;
         if (amax == 0u) e8 = 127u;
-        float q[8];
-        uint32_t pk;
+        uint32_t pk[2];
         if (amax < kBitsInf) {
-            const uint32_t mul = RNE ? inv_scale_bits(e8) : (((253u - e8) << 23) | 0x7FF000u);
-            const float c = __uint_as_float(mul);
+            const float c = __uint_as_float(RNE ? inv_scale_bits(e8) : (((253u - e8) << 23) | 0x7FF000u));
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                q[2 * i] = __uint_as_float(w[i] << 16) * c;
-                q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
+            for (int h = 0; h < 2; h++) {
+                float q[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    q[2 * i] = __uint_as_float(w[4 * h + i] << 16) * c;
+                    q[2 * i + 1] = __uint_as_float(w[4 * h + i] & 0xFFFF0000u) * c;
+                }
+                pk[h] = cvt_e2m1x8(q);
             }
-            pk = cvt_e2m1x8(q);
         } else {                                   // infinite or NaN block maximum
             e8 = amax == kBitsInf ? 254u : 255u;
             const float c = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                q[2 * i] = __uint_as_float(w[i] << 16) * c;
-                q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u) * c;
+            for (int h = 0; h < 2; h++) {
+                float q[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    q[2 * i] = __uint_as_float(w[4 * h + i] << 16) * c;
+                    q[2 * i + 1] = __uint_as_float(w[4 * h + i] & 0xFFFF0000u) * c;
+                }
+                pk[h] = codes8<RNE>(q);
             }
-            pk = codes8<RNE>(q);
         }
-        store_group<BLOCK>(o, g8, pk, e8, g8 < n8);
+        const bool in_range = g < n16;
+        if (in_range) {
+            if (o.packed) reinterpret_cast<uint2 *>(o.packed)[g] = make_uint2(pk[0], pk[1]);
+            if (o.codes)
+                reinterpret_cast<uint4 *>(o.codes)[g] = make_uint4(spread_codes(pk[0] & 0xFFFFu), spread_codes(pk[0] >> 16),
+                                                                   spread_codes(pk[1] & 0xFFFFu), spread_codes(pk[1] >> 16));
+        }
+        store_scales<LPB>(o, g / LPB, e8, in_range);
     }
 }
 
 // ---- fp32 input -------------------------------------------------------------
-// One thread owns 8 consecutive elements (two adjacent 16-byte loads).
-// Integer rounding on the bit pattern; exact for every fp32 input.
+// One thread owns 8 consecutive elements (one 32-byte load).  Integer rounding
+// on the bit pattern; exact for every fp32 input.
 template <int BLOCK, bool RNE>
 __global__ void __launch_bounds__(kThreads)
-quantize_f32_kernel(const uint4 *__restrict__ x, uint32_t n8, QuantOut o)
+quantize_f32_kernel(const uint8_t *__restrict__ x, uint32_t n8, QuantOut o)
 {
     constexpr int LPB = BLOCK / 8;
     constexpr int U = kUnroll / 2;
     const uint32_t base = blockIdx.x * (kThreads * U) + threadIdx.x;
-    uint4 v[U][2];
+    U8x32 v[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const uint32_t g8 = base + u * kThreads;
-        const bool ok = g8 < n8;
-        v[u][0] = ok ? ld_stream(x + 2 * size_t(g8)) : make_uint4(0, 0, 0, 0);
-        v[u][1] = ok ? ld_stream(x + 2 * size_t(g8) + 1) : make_uint4(0, 0, 0, 0);
+        if (g8 < n8) v[u] = ld_stream32(x + size_t(g8) * 32);
+        else
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[u].w[i] = 0u;
     }
 #pragma unroll
     for (int u = 0; u < U; u++) {
         const uint32_t g8 = base + u * kThreads;
-        const uint32_t w[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w,
-                               v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
+        const uint32_t(&w)[8] = v[u].w;
         uint32_t amax = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) amax = max(amax, w[i] & 0x7FFFFFFFu);
@@ -186,7 +224,9 @@ quantize_f32_kernel(const uint4 *__restrict__ x, uint32_t n8, QuantOut o)
         float q[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) q[i] = __uint_as_float(w[i]) * c;
-        const uint32_t pk = codes8<RNE>(q);
+        uint32_t pk;
+        if (amax < kBitsInf) pk = RNE ? cvt_e2m1x8(q) : cvt_ref_e2m1x8(q);     // all quotients finite
+        else pk = codes8<RNE>(q);
         store_group<BLOCK>(o, g8, pk, e8, g8 < n8);
     }
 }
@@ -240,44 +280,48 @@ unpack_kernel(const uint2 *__restrict__ packed, uint4 *__restrict__ codes, int64
 }
 
 // ---- dequantize ---------------------------------------------------------------
-// One thread produces 8 outputs from 8 codes (8 bytes, or 4 packed bytes).
+// One thread turns 4 codes (4 bytes, or 2 packed bytes) into 4 outputs per step, so
+// that each load and each 16-byte (fp32) store of a warp is one contiguous segment.
 template <bool PACKED, bool OUT_BF16>
 __global__ void __launch_bounds__(kThreads)
 dequantize_kernel(const uint8_t *__restrict__ q, const float *__restrict__ scale,
-                  const uint8_t *__restrict__ e8m0, int64_t n8, int block, void *__restrict__ out)
+                  const uint8_t *__restrict__ e8m0, uint32_t n4, int block, void *__restrict__ out)
 {
-    const int64_t stride = int64_t(gridDim.x) * kThreads;
-    for (int64_t g8 = int64_t(blockIdx.x) * kThreads + threadIdx.x; g8 < n8; g8 += stride) {
-        uint32_t pk;
-        if (PACKED) {
-            pk = reinterpret_cast<const uint32_t *>(q)[g8];
-        } else {
-            uint2 c = reinterpret_cast<const uint2 *>(q)[g8];
-            auto squeeze = [](uint32_t a) {
-                a &= 0x0F0F0F0Fu;
-                uint32_t t = a | (a >> 4);
-                return (t & 0xFFu) | ((t >> 8) & 0xFF00u);
-            };
-            pk = squeeze(c.x) | (squeeze(c.y) << 16);
-        }
-        int64_t blk = g8 * 8 / block;
-        float s = scale ? scale[blk] : __uint_as_float(scale_bits(e8m0[blk]));
-        float f[8];
+    constexpr int U = 4;
+    const uint32_t stride = gridDim.x * kThreads;
+    const uint32_t qpb = uint32_t(block) / 4;                 // quads per block
+    for (uint32_t q0 = blockIdx.x * kThreads + threadIdx.x; q0 < n4; q0 += U * stride) {
+        uint32_t pk[U];
+        float sc[U];
 #pragma unroll
-        for (int i = 0; i < 8; i++) f[i] = e2m1_value((pk >> (4 * i)) & 0xFu) * s;
-        if (OUT_BF16) {
-            uint4 r;
-            uint32_t *rw = &r.x;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                rw[i] = *reinterpret_cast<uint32_t *>(&h);
+        for (int u = 0; u < U; u++) {
+            const uint32_t i = q0 + u * stride;
+            const bool ok = i < n4;
+            if (PACKED) {
+                pk[u] = ok ? reinterpret_cast<const uint16_t *>(q)[i] : 0u;
+            } else {
+                uint32_t c = ok ? reinterpret_cast<const uint32_t *>(q)[i] : 0u;
+                c &= 0x0F0F0F0Fu;
+                c |= c >> 4;
+                pk[u] = (c & 0xFFu) | ((c >> 8) & 0xFF00u);
             }
-            reinterpret_cast<uint4 *>(out)[g8] = r;
-        } else {
-            float4 *o4 = reinterpret_cast<float4 *>(out) + 2 * g8;
-            o4[0] = make_float4(f[0], f[1], f[2], f[3]);
-            o4[1] = make_float4(f[4], f[5], f[6], f[7]);
+            const uint32_t blk = i / qpb;
+            sc[u] = !ok ? 0.0f : (scale ? scale[blk] : __uint_as_float(scale_bits(e8m0[blk])));
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t i = q0 + u * stride;
+            if (i >= n4) break;
+            float f[4];
+            e2m1x4_values(pk[u], f);
+#pragma unroll
+            for (int k = 0; k < 4; k++) f[k] *= sc[u];
+            if (OUT_BF16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
+                reinterpret_cast<uint2 *>(out)[i] = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+            } else {
+                reinterpret_cast<float4 *>(out)[i] = make_float4(f[0], f[1], f[2], f[3]);
+            }
         }
     }
 }
@@ -346,8 +390,9 @@ extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64
     int64_t n = rows * K;
     if (n == 0) return LS_OK;
     if (!x) return fail(LS_EINVAL, "x is null");
-    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 7) || (reinterpret_cast<uintptr_t>(packed) & 3))
-        return fail(LS_EALIGN, "x must be 16-byte, codes 8-byte, packed 4-byte aligned");
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(packed) & 7) ||
+        (reinterpret_cast<uintptr_t>(x) & 31))
+        return fail(LS_EALIGN, "x must be 32-byte, codes 16-byte, packed 8-byte aligned");
     if (n / 8 >= (int64_t(1) << 31)) return fail(LS_EINVAL, "more than 2^34 elements in one call");
     if ((reinterpret_cast<uintptr_t>(scale) & 15) || (reinterpret_cast<uintptr_t>(e8m0) & 3) ||
         (reinterpret_cast<uintptr_t>(sf) & 3))
@@ -363,25 +408,27 @@ extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64
     }
     uint32_t n8 = uint32_t(n / 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const uint4 *xp = static_cast<const uint4 *>(x);
     bool rne = rounding == LS_ROUND_RNE;
     if (x_dtype == LS_BF16) {
-        int grid = int((n8 + kThreads * kUnroll - 1) / (kThreads * kUnroll));
+        const uint32_t n16 = n8 / 2;
+        const uint8_t *xb = static_cast<const uint8_t *>(x);
+        int grid = int((n16 + kThreads * kUnroll16 - 1) / (kThreads * kUnroll16));
         if (block == 32) {
-            if (rne) quantize_bf16_kernel<32, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
-            else quantize_bf16_kernel<32, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            if (rne) quantize_bf16_kernel<32, true><<<grid, kThreads, 0, st>>>(xb, n16, o);
+            else quantize_bf16_kernel<32, false><<<grid, kThreads, 0, st>>>(xb, n16, o);
         } else {
-            if (rne) quantize_bf16_kernel<16, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
-            else quantize_bf16_kernel<16, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            if (rne) quantize_bf16_kernel<16, true><<<grid, kThreads, 0, st>>>(xb, n16, o);
+            else quantize_bf16_kernel<16, false><<<grid, kThreads, 0, st>>>(xb, n16, o);
         }
     } else {
+        const uint8_t *xf = static_cast<const uint8_t *>(x);
         int grid = int((n8 + kThreads * kUnroll / 2 - 1) / (kThreads * kUnroll / 2));
         if (block == 32) {
-            if (rne) quantize_f32_kernel<32, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
-            else quantize_f32_kernel<32, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            if (rne) quantize_f32_kernel<32, true><<<grid, kThreads, 0, st>>>(xf, n8, o);
+            else quantize_f32_kernel<32, false><<<grid, kThreads, 0, st>>>(xf, n8, o);
         } else {
-            if (rne) quantize_f32_kernel<16, true><<<grid, kThreads, 0, st>>>(xp, n8, o);
-            else quantize_f32_kernel<16, false><<<grid, kThreads, 0, st>>>(xp, n8, o);
+            if (rne) quantize_f32_kernel<16, true><<<grid, kThreads, 0, st>>>(xf, n8, o);
+            else quantize_f32_kernel<16, false><<<grid, kThreads, 0, st>>>(xf, n8, o);
         }
     }
     LS_LAUNCH_CHECK("quantize_mxfp4");
@@ -433,15 +480,16 @@ extern "C" int ls_dequantize_mxfp4(const uint8_t *q, int is_packed, const float 
     if (n == 0) return LS_OK;
     if (!q || !out) return fail(LS_EINVAL, "null pointer");
     if (!aligned16(out) || (reinterpret_cast<uintptr_t>(q) & (is_packed ? 3 : 7))) return fail(LS_EALIGN, "misaligned buffer");
-    int64_t n8 = n / 8;
-    int grid = grid_for(n8, kThreads);
+    if (n / 4 >= (int64_t(1) << 32)) return fail(LS_EINVAL, "more than 2^34 elements in one call");
+    uint32_t n4 = uint32_t(n / 4);
+    int grid = grid_for(n4, kThreads * 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (is_packed) {
-        if (out_dtype == LS_BF16) dequantize_kernel<true, true><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
-        else dequantize_kernel<true, false><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
+        if (out_dtype == LS_BF16) dequantize_kernel<true, true><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n4, block, out);
+        else dequantize_kernel<true, false><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n4, block, out);
     } else {
-        if (out_dtype == LS_BF16) dequantize_kernel<false, true><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
-        else dequantize_kernel<false, false><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n8, block, out);
+        if (out_dtype == LS_BF16) dequantize_kernel<false, true><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n4, block, out);
+        else dequantize_kernel<false, false><<<grid, kThreads, 0, st>>>(q, scale, e8m0, n4, block, out);
     }
     LS_LAUNCH_CHECK("dequantize_mxfp4");
     return LS_OK;

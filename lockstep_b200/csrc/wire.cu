@@ -113,12 +113,24 @@ __device__ __forceinline__ uint32_t encode8(const float (&v)[8], uint32_t &e8, f
     e8 = block_e8m0(amax);
     const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
     const float sc = __uint_as_float(scale_bits(e8));
-    uint32_t pk = 0;
+    float q[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        uint32_t c = e2m1_code<false>(__fmul_rn(v[i], inv));
-        pk |= c << (4 * i);
-        dq[i] = __fmul_rn(e2m1_value(c), sc);
+    for (int i = 0; i < 8; i++) q[i] = __fmul_rn(v[i], inv);
+    uint32_t pk;
+    if (amax < kBitsInf) {
+        pk = cvt_ref_e2m1x8(q);                          // all quotients finite: hardware converter
+    } else {
+        pk = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) pk |= e2m1_code<false>(q[i]) << (4 * i);
+    }
+    float lo[4], hi[4];
+    e2m1x4_values(pk, lo);
+    e2m1x4_values(pk >> 16, hi);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        dq[i] = __fmul_rn(lo[i], sc);
+        dq[4 + i] = __fmul_rn(hi[i], sc);
     }
     return pk;
 }

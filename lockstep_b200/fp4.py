@@ -49,7 +49,10 @@ def _as_rows(x, block):
     assert K % block == 0, f"K={K} must be a multiple of block={block}"
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.float()
-    return x.contiguous(), lead, K, (x.numel() // K if K else 0)
+    x = x.contiguous()
+    if x.data_ptr() % 32:                      # the kernels read 32-byte words
+        x = x.clone()
+    return x, lead, K, (x.numel() // K if K else 0)
 
 
 def quantize_mxfp4(x: torch.Tensor, block: int = 32, rounding: str = "ref"):
