@@ -145,6 +145,50 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args):
+    """Shape sweep of the single MXFP4 GEMM: M in {1, 16, 128, 4096, 16384}, N = K in
+    {4096, 8192, 16384}; weights N(0, 0.02), activations N(0, 1) with 1 % of the entries
+    multiplied by 50.  One JSON line per shape: TFLOP/s, and for M <= 16 the fraction of
+    the bytes roofline (packed W + scales + A + output over the measured HBM peak)."""
+    from lockstep_b200 import fp4, mxfp4_gemm
+    dev = torch.device("cuda", 0)
+    pk = peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+    for nk in (4096, 8192, 16384):
+        w = (torch.randn(nk, nk, device=dev, generator=g) * 0.02).bfloat16()
+        w_pk, w_sf = fp4.quantize_mxfp4_packed(w)
+        del w
+        for m in (1, 16, 128, 4096, 16384):
+            a = torch.randn(m, nk, device=dev, generator=g)
+            a = torch.where(torch.rand(m, nk, device=dev, generator=g) < 0.01, a * 50, a).bfloat16()
+            a_pk, a_sf = fp4.quantize_mxfp4_packed(a)
+            for _ in range(3):
+                mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf)
+            reps = 20 if m <= 4096 else 5
+            # replayed as a CUDA graph so that small shapes show device time, not launch overhead
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                for _ in range(reps):
+                    c = mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf)
+            graph.replay()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0.record()
+            graph.replay()
+            t1.record()
+            torch.cuda.synchronize()
+            ms = t0.elapsed_time(t1) / reps
+            del graph, c
+            nbytes = nk * nk * 17 / 32 + m * nk * 17 / 32 + 2 * m * nk
+            line = {"shape": [m, nk, nk], "us": ms * 1e3, "tflops": 2 * m * nk * nk / ms / 1e9,
+                    "gbs": nbytes / ms / 1e6}
+            if m <= 16:
+                line["bytes_roofline_frac"] = nbytes / ms / 1e6 / pk["hbm"]
+            print(json.dumps(line), flush=True)
+    mxfp4_gemm.gemm_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -156,11 +200,16 @@ def main():
     ap.add_argument("--no-wire", action="store_true", help="skip the all-reduce leg")
     ap.add_argument("--no-train", action="store_true", help="skip the FP4-linear training-step leg")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
+    ap.add_argument("--sweep", action="store_true", help="shape sweep of the single GEMM instead of the benchmark step")
     args = ap.parse_args()
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.sweep:
+        if rank == 0:
+            run_sweep(args)
         return
 
     import torch.distributed as dist

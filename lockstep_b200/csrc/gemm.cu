@@ -53,13 +53,16 @@ struct GemmParams {
     int nbatch;
     int out_bf16;
     int *err;                      // device int, set non-zero when a wait ran out
+    int splits;                    // split-K factor of the single-CTA kernel (1 = off)
+    int kt_per_split;              // k-tiles per split
+    float *partial;                // [splits, M, N] fp32 partial sums when splits > 1
 };
 
-__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, int row, int col0,
+__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bool bf16, int row, int col0,
                                             const uint32_t (&r)[32])
 {
     if (row >= p.M || col0 >= p.N) return;
-    if (p.out_bf16) {
+    if (bf16) {
         __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(cbase) + int64_t(row) * p.N + col0;
         if (col0 + 32 <= p.N && (p.N & 7) == 0) {
 #pragma unroll
@@ -140,10 +143,14 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
-    const int total_tiles = m_tiles * n_tiles * p.nbatch;
+    const int total_tiles = m_tiles * n_tiles * p.nbatch * p.splits;
     const int k_tiles = (p.K / 2 + BKB - 1) / BKB;
     const int k_atoms = p.K / 128;                    // scale tiles (4 k-blocks each) per row tile
     const int n_atoms = (p.N + 127) / 128;            // 128-row scale tiles of W
+    // tile index -> (split, batch, row tile, column tile); a split covers k-tiles [kt0, kt1)
+    auto split_of = [&](int t) { return t % p.splits; };
+    auto kt_begin = [&](int ks) { return ks * p.kt_per_split; };
+    auto kt_end = [&](int ks) { return min(k_tiles, (ks + 1) * p.kt_per_split); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) {
@@ -173,11 +180,12 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             uint32_t it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int b = t % p.nbatch, rest = t / p.nbatch;
+                const int ks = split_of(t), tt = t / p.splits;
+                const int b = tt % p.nbatch, rest = tt / p.nbatch;
                 const int mt = rest % m_tiles, nt = rest / m_tiles;
                 const CUtensorMap *tma = b ? &tm_a1 : &tm_a0;
                 const uint8_t *sfa = p.sfa[b] + int64_t(mt) * k_atoms * 512;
-                for (int kt = 0; kt < k_tiles; kt++, it++) {
+                for (int kt = kt_begin(ks); kt < kt_end(ks); kt++, it++) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag))) break;
@@ -214,7 +222,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 if (lt > 0 && !(ok = ptx::mbar_wait(acc_free_bar, (lt - 1) & 1, abort_flag))) break;
                 ptx::tc_fence_after();
                 const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0);
-                for (int kt = 0; kt < k_tiles; kt++, it++) {
+                const int kt0 = kt_begin(split_of(t)), kt1 = kt_end(split_of(t));
+                for (int kt = kt0; kt < kt1; kt++, it++) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
@@ -222,10 +231,10 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);       // stage offset in 16-byte units
                     if (2 * kt + 2 <= k_atoms)
                         issue_stage<1, 2, BN / 128>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
-                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == 0, false, false);
+                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false);
                     else
                         issue_stage<1, 1, BN / 128>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
-                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == 0, false, false);
+                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false);
                     ptx::tc_commit(empty_bar(s));
                 }
                 if (ok) ptx::tc_commit(acc_full_bar);
@@ -237,8 +246,12 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
         int lt = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
-            const int b = t % p.nbatch, rest = t / p.nbatch;
+            const int ks = split_of(t), tt = t / p.splits;
+            const int b = tt % p.nbatch, rest = tt / p.nbatch;
             const int mt = rest % m_tiles, nt = rest / m_tiles;
+            // split-K: fp32 partial sums into the scratch slab of (batch, split)
+            void *dst = p.splits > 1 ? static_cast<void *>(p.partial + int64_t(b * p.splits + ks) * p.M * p.N) : p.c[b];
+            const bool dst_bf16 = p.splits > 1 ? false : bool(p.out_bf16);
             if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
@@ -256,7 +269,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_free_bar);
                 }
-                store_chunk(p, p.c[b], row, nt * BN + 32 * c, r);
+                store_chunk(p, dst, dst_bf16, row, nt * BN + 32 * c, r);
             }
         }
     }
@@ -272,6 +285,36 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// Sums the split-K partial slabs in ascending split order and writes the output type.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float *__restrict__ partial, void *__restrict__ out, int64_t mn, int splits, int out_bf16)
+{
+    const int64_t stride = int64_t(gridDim.x) * 256;
+    const bool vec = (mn & 3) == 0;
+    if (vec) {
+        for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < mn / 4; i += stride) {
+            float4 acc = reinterpret_cast<const float4 *>(partial)[i];
+            for (int s = 1; s < splits; s++) {
+                const float4 v = reinterpret_cast<const float4 *>(partial + int64_t(s) * mn)[i];
+                acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+            }
+            if (out_bf16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+                reinterpret_cast<uint2 *>(out)[i] = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+            } else {
+                reinterpret_cast<float4 *>(out)[i] = acc;
+            }
+        }
+    } else {
+        for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < mn; i += stride) {
+            float acc = partial[i];
+            for (int s = 1; s < splits; s++) acc += partial[int64_t(s) * mn + i];
+            if (out_bf16) static_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(acc);
+            else static_cast<float *>(out)[i] = acc;
+        }
     }
 }
 
@@ -464,7 +507,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
                 }
-                store_chunk(p, p.c[my_batch], row, nt * C::BN + 32 * c, r);
+                store_chunk(p, p.c[my_batch], p.out_bf16, row, nt * C::BN + 32 * c, r);
             }
         }
     }
@@ -529,7 +572,7 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
         LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         attr_set[dev] = true;
     }
-    int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.nbatch;
+    int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.nbatch * p.splits;
     int grid = tiles < sm_count() ? tiles : sm_count();
     mxfp4_gemm_kernel<BN><<<grid, kGemmThreads, C::SMEM, st>>>(ta0, ta1, tb, p);
     LS_LAUNCH_CHECK("mxfp4_gemm");
@@ -592,6 +635,26 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
 
 int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
 
+// Per-device scratch for split-K partial sums; grows on demand and is kept.
+float *splitk_scratch(size_t bytes)
+{
+    static float *buf[64] = {};
+    static size_t cap[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cap[dev] < bytes) {
+        if (buf[dev]) {
+            cudaDeviceSynchronize();
+            cudaFree(buf[dev]);
+            buf[dev] = nullptr, cap[dev] = 0;
+        }
+        size_t want = bytes < (size_t(32) << 20) ? (size_t(32) << 20) : bytes;
+        if (cudaMalloc(&buf[dev], want) != cudaSuccess) return nullptr;
+        cap[dev] = want;
+    }
+    return buf[dev];
+}
+
 }  // namespace
 
 int *error_word()
@@ -627,6 +690,7 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     if (!aligned16(a0) || !aligned16(w) || !aligned16(sfa0) || !aligned16(sfb) || !aligned16(c0) ||
         (nbatch == 2 && (!aligned16(a1) || !aligned16(sfa1) || !aligned16(c1))))
         return fail(LS_EALIGN, "GEMM operands, scale buffers and outputs must be 16-byte aligned");
+    const bool caller_err = err != nullptr;
     if (!err) err = error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     const int bn = 256;
@@ -645,8 +709,37 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     p.nbatch = nbatch;
     p.out_bf16 = out_dtype == LS_BF16;
     p.err = err;
+    p.splits = 1;
+    p.kt_per_split = int((K / 2 + BKB - 1) / BKB);
+    p.partial = nullptr;
     if (pair) return launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
-    return launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
+    // Few tiles and a long K (decode-like shapes): split K over otherwise idle SMs.  Not on the
+    // allocation-free path (caller-supplied error word), which must not touch an allocator.
+    const int tiles = int(((M + BM - 1) / BM) * ((N + bn - 1) / bn)) * nbatch;
+    const int k_tiles = p.kt_per_split;
+    if (!caller_err && M <= 32 && tiles * 2 <= sm_count() && k_tiles >= 4) {      // partial traffic grows with M
+        int s = sm_count() / tiles;
+        if (s > k_tiles / 2) s = k_tiles / 2;
+        if (s > 16) s = 16;
+        if (s > 1) {
+            p.kt_per_split = (k_tiles + s - 1) / s;
+            p.splits = (k_tiles + p.kt_per_split - 1) / p.kt_per_split;
+            p.partial = splitk_scratch(size_t(p.splits) * nbatch * M * N * sizeof(float));
+            if (!p.partial) return fail(LS_ECUDA, "could not allocate split-K scratch");
+        }
+    }
+    if (int rc = launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
+    if (p.splits > 1) {
+        for (int b = 0; b < nbatch; b++) {
+            const int64_t mn = M * N;
+            int64_t want = (mn / 4 + 255) / 256;
+            int grid = int(want < 1 ? 1 : (want > sm_count() * 8 ? sm_count() * 8 : want));
+            splitk_reduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+                p.partial + int64_t(b) * p.splits * mn, p.c[b], mn, p.splits, p.out_bf16);
+        }
+        LS_LAUNCH_CHECK("splitk_reduce");
+    }
+    return LS_OK;
 }
 
 }  // namespace ls

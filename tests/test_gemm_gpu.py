@@ -115,6 +115,25 @@ def test_ragged_shapes(mods, M, N, K):
         assert (guard == 777.0).all()
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 2048, 8192), (100, 512, 2048), (128, 1000, 1152)])
+def test_skinny_shapes_split_k(mods, M, N, K):
+    # few tiles and a long K: the kernel splits K across SMs and sums fp32 partials
+    fp4, mg, _ = mods
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g)
+    a = torch.where(torch.rand(M, K, generator=g) < 0.01, a * 50, a).bfloat16()       # 1 % outliers x 50
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    ac, asc = ref_port.quantize(a)
+    wc, wsc = ref_port.quantize(w)
+    pa, sfa = fp4.quantize_mxfp4_packed(a.cuda())
+    pw, sfw = fp4.quantize_mxfp4_packed(w.cuda())
+    for dt in (torch.bfloat16, torch.float32):
+        c = mg.mxfp4_gemm_packed(pa, pw, sfa, sfw, out_dtype=dt)
+        mg.gemm_status()
+        _check(c, ref_port.gemm_fake_quant(ac, asc, wc, wsc, dt), f"{M}x{N}x{K} {dt}")
+    assert torch.equal(mg.mxfp4_gemm_packed(pa, pw, sfa, sfw), mg.mxfp4_gemm_packed(pa, pw, sfa, sfw))   # deterministic
+
+
 def test_fp8_entry(mods):
     fp4, mg, _ = mods
     M, N, K = 128, 256, 256
