@@ -151,6 +151,11 @@ int ls_wire_finish(void *handle, float *g, int64_t numel, void *stream);
 int ls_wire_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, int reverse,
                       void *stream);
 
+/* How many times (about 100 ns apart, default 2^22 = ~0.5 s) a kernel polls a
+ * peer's flag before it gives up, records a time-out in the status word and
+ * carries on with whatever its buffers hold; the context stays usable. */
+int ls_wire_set_poll_limit(void *handle, int64_t polls);
+
 /* Synchronising: LS_ETIMEOUT (and clears it) if a wire kernel gave up waiting
  * for a peer since the last call.  status_host (host int) may be NULL. */
 int ls_wire_status(void *handle, int *status_host);

@@ -26,7 +26,7 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 constexpr int kThreads = 256;
-constexpr uint32_t kPollLimit = 1u << 22;     // x ~100 ns
+constexpr uint32_t kPollLimit = 1u << 22;     // default polls (x ~100 ns sleep each) before a wait gives up
 
 struct Header {                 // start of every rank's arena
     uint32_t rs_flag[kMaxWorld];    // epoch of the last completed send from rank s
@@ -43,6 +43,7 @@ struct WireGeom {
     int64_t padded, shard;          // elements
     int64_t slot_bytes;             // packed + exponent bytes of one shard, 256-aligned
     int64_t rs_off, ag_off;         // byte offsets of the slot arrays in an arena
+    uint32_t poll_limit;            // polls before a wait on a peer's flag gives up
 };
 
 struct Wire {
@@ -67,13 +68,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
 }
 
 // One thread per CTA polls; returns after the flags of all `world` ranks reached `epoch`.
-__device__ __forceinline__ void wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch)
+__device__ __forceinline__ void wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch,
+                                           uint32_t poll_limit)
 {
     if (threadIdx.x == 0) {
         for (int s = 0; s < world; s++) {
             uint32_t polls = 0;
             while (int32_t(ld_acquire_sys(flags + s) - epoch) < 0) {
-                if (++polls > kPollLimit) {
+                if (++polls > poll_limit) {
                     atomicExch(&h->status, 1u);
                     break;
                 }
@@ -213,7 +215,7 @@ wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->rs_flag, geo.world, epoch);
+    wait_flags(mine, mine->rs_flag, geo.world, epoch, geo.poll_limit);
     const int64_t groups = geo.shard / 8;
     const int64_t stride = int64_t(gridDim.x) * kThreads;
     const int lane = threadIdx.x & 31;
@@ -273,7 +275,7 @@ wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, 
     constexpr int U = 4;                                        // independent quads in flight per thread
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->ag_flag, geo.world, epoch);
+    wait_flags(mine, mine->ag_flag, geo.world, epoch, geo.poll_limit);
     const uint32_t stride = gridDim.x * kThreads;
     const uint32_t q_per_shard = uint32_t(geo.shard / 4);
     const float w = float(geo.world), rw = 1.0f / w;
@@ -356,6 +358,7 @@ extern "C" int ls_wire_create(int rank, int world, int64_t padded, void **out)
     w->g.slot_bytes = (raw + 255) / 256 * 256;
     w->g.rs_off = int64_t(kHeaderBytes);
     w->g.ag_off = w->g.rs_off + w->g.slot_bytes * world;
+    w->g.poll_limit = kPollLimit;
     w->arena_bytes = size_t(w->g.ag_off + w->g.slot_bytes * world);
     w->mapped = false;
     w->epoch = 0;
@@ -466,6 +469,14 @@ extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, f
     if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
     if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
     return ls_wire_finish(h, g, numel, stream);
+}
+
+extern "C" int ls_wire_set_poll_limit(void *h, int64_t polls)
+{
+    Wire *w = as_wire(h);
+    if (!w || polls < 1 || polls > (int64_t(1) << 31)) return fail(LS_EINVAL, "bad wire handle or poll limit");
+    w->g.poll_limit = uint32_t(polls);
+    return LS_OK;
 }
 
 extern "C" int ls_wire_status(void *h, int *status_host)

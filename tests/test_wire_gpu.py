@@ -148,3 +148,33 @@ def test_ranks_come_from_torchrun_then_slurm(wire, monkeypatch):
     for k, v in (("RANK", "3"), ("WORLD_SIZE", "8"), ("LOCAL_RANK", "3")):
         monkeypatch.setenv(k, v)
     assert wire.env_rank() == (3, 8, 3)
+
+
+def test_missing_peer_is_reported_not_hung(wire):
+    """Failure detection: rank 1 never sends.  Rank 0's owner kernel polls rank 1's
+    flag a bounded number of times, records a time-out and returns; the host reads
+    the status as an error, and the same handles work again afterwards."""
+    import ctypes
+    from lockstep_b200._lib import check, lib, ptr, stream
+    L = lib()
+    world, n = 2, 4096
+    grp = wire.LocalWireGroup(world, n)
+    for h in grp.handles:
+        check(L.ls_wire_set_poll_limit(h, 2000))             # ~ a few ms
+    g0 = torch.randn(n, device="cuda")
+    check(L.ls_wire_send(grp.handles[0], ptr(g0), n, None, stream()))   # rank 1's send is "lost"
+    check(L.ls_wire_reduce(grp.handles[0], None, 0, stream()))
+    status = ctypes.c_int(0)
+    rc = L.ls_wire_status(grp.handles[0], ctypes.byref(status))
+    assert rc == -4 and status.value != 0                    # LS_ETIMEOUT
+    assert b"gave up" in L.ls_last_error()
+    assert L.ls_wire_status(grp.handles[0], None) == 0       # cleared; context still usable
+    # bring rank 1 level with rank 0's epoch, then a complete step works
+    g1 = torch.randn(n, device="cuda")
+    check(L.ls_wire_send(grp.handles[1], ptr(g1), n, None, stream()))
+    check(L.ls_wire_reduce(grp.handles[1], None, 0, stream()))
+    gs = [torch.randn(n, device="cuda") for _ in range(world)]
+    want, _, _ = cref.wire_step([g.cpu().numpy() for g in gs], unit=256)
+    grp.step(gs)
+    assert np.array_equal(gs[0].cpu().numpy(), want) and np.array_equal(gs[1].cpu().numpy(), want)
+    grp.close()
