@@ -210,57 +210,82 @@ wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res
 }
 
 // ---- phase 2: owner ------------------------------------------------------------------
+// WORLD > 0: the world size as a compile-time constant, so that the loads of all
+// senders' slots are issued together before the first decode.  WORLD = 0: any size.
+template <int WORLD>
 __global__ void __launch_bounds__(kThreads)
 wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t epoch, int reverse)
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->rs_flag, geo.world, epoch, geo.poll_limit);
-    const int64_t groups = geo.shard / 8;
-    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    const int world = WORLD ? WORLD : geo.world;
+    wait_flags(mine, mine->rs_flag, world, epoch, geo.poll_limit);
+    const uint32_t groups = uint32_t(geo.shard / 8);           // a multiple of 32
+    const uint32_t stride = gridDim.x * kThreads;
     const int lane = threadIdx.x & 31;
-    for (int64_t base = int64_t(blockIdx.x) * kThreads; base < groups; base += stride) {
-        const int64_t g8 = base + threadIdx.x;
-        if (base + (threadIdx.x & ~31) >= groups) continue;
-        float val[8], dq[8];
+    const uint8_t *rs = my + geo.rs_off;
+    const int64_t exp_off = geo.shard / 2;
+    for (uint32_t g8 = blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
+        float val[8], dq[8], r[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) val[i] = 0.0f;
-        for (int t = 0; t < geo.world; t++) {
-            const int s = reverse ? geo.world - 1 - t : t;
-            const uint8_t *slot = my + geo.rs_off + int64_t(s) * geo.slot_bytes;
-            const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[g8];
-            const float sc = __uint_as_float(scale_bits(slot[geo.shard / 2 + g8 / 4]));
-            float lo[4], hi[4];
-            e2m1x4_values(pk, lo);
-            e2m1x4_values(pk >> 16, hi);
+        if (ores) load8(ores, int64_t(g8) * 8, geo.shard, r);
+        if (WORLD) {
+            uint32_t pk[WORLD ? WORLD : 1], eb[WORLD ? WORLD : 1];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                val[i] = __fadd_rn(val[i], __fmul_rn(lo[i], sc));
-                val[4 + i] = __fadd_rn(val[4 + i], __fmul_rn(hi[i], sc));
+            for (int t = 0; t < WORLD; t++) {
+                const uint8_t *slot = rs + int64_t(reverse ? WORLD - 1 - t : t) * geo.slot_bytes;
+                pk[t] = reinterpret_cast<const uint32_t *>(slot)[g8];
+                eb[t] = slot[exp_off + g8 / 4];
+            }
+#pragma unroll
+            for (int t = 0; t < WORLD; t++) {
+                const float sc = __uint_as_float(scale_bits(eb[t]));
+                float lo[4], hi[4];
+                e2m1x4_values(pk[t], lo);
+                e2m1x4_values(pk[t] >> 16, hi);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    val[i] = __fadd_rn(val[i], __fmul_rn(lo[i], sc));
+                    val[4 + i] = __fadd_rn(val[4 + i], __fmul_rn(hi[i], sc));
+                }
+            }
+        } else {
+            for (int t = 0; t < world; t++) {
+                const uint8_t *slot = rs + int64_t(reverse ? world - 1 - t : t) * geo.slot_bytes;
+                const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[g8];
+                const float sc = __uint_as_float(scale_bits(slot[exp_off + g8 / 4]));
+                float lo[4], hi[4];
+                e2m1x4_values(pk, lo);
+                e2m1x4_values(pk >> 16, hi);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    val[i] = __fadd_rn(val[i], __fmul_rn(lo[i], sc));
+                    val[4 + i] = __fadd_rn(val[4 + i], __fmul_rn(hi[i], sc));
+                }
             }
         }
         if (ores) {
-            float r[8];
-            load8(ores, g8 * 8, geo.shard, r);
 #pragma unroll
             for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
         }
         uint32_t e8;
-        const uint32_t pk = encode8(val, e8, dq);
+        const uint32_t pk2 = encode8(val, e8, dq);
         if (ores) {
-            float r[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) r[i] = __fsub_rn(val[i], dq[i]);
-            store8(ores, g8 * 8, geo.shard, r);
+            store8(ores, int64_t(g8) * 8, geo.shard, r);
         }
         const uint2 ex = gather_exponents(e8);
-        for (int p = 0; p < geo.world; p++) {
+#pragma unroll
+        for (int p = 0; p < (WORLD ? WORLD : kMaxWorld); p++) {
+            if (p >= world) break;
             uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
-            reinterpret_cast<uint32_t *>(slot)[g8] = pk;
-            if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + g8 / 4) = ex;
+            reinterpret_cast<uint32_t *>(slot)[g8] = pk2;
+            if (lane == 0) *reinterpret_cast<uint2 *>(slot + exp_off + g8 / 4) = ex;
         }
     }
-    signal_done(mine, &mine->counter[1], peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
+    signal_done(mine, &mine->counter[1], peers, world, geo.rank, offsetof(Header, ag_flag), epoch);
 }
 
 // ---- phase 3: everyone ---------------------------------------------------------------
@@ -445,8 +470,15 @@ extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
 {
     Wire *w = as_wire(h);
     if (!w || !w->mapped) return fail(LS_ESTATE, "wire not ready");
-    wire_reduce_kernel<<<grid_for(w->g.shard / 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        ores, w->g, w->peers, w->epoch, reverse);
+    const int grid = grid_for(w->g.shard / 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (w->g.world) {
+    case 1: wire_reduce_kernel<1><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
+    case 2: wire_reduce_kernel<2><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
+    case 4: wire_reduce_kernel<4><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
+    case 8: wire_reduce_kernel<8><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
+    default: wire_reduce_kernel<0><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
+    }
     LS_LAUNCH_CHECK("wire_reduce");
     return LS_OK;
 }

@@ -43,7 +43,7 @@ def test_mxfp4_wire_golden_outputs(wire, golden, world, ef):
     grp.close()
 
 
-@pytest.mark.parametrize("world,n", [(1, 1000), (2, 4096 + 13), (8, 100_003), (4, 1 << 20)])
+@pytest.mark.parametrize("world,n", [(1, 1000), (2, 4096 + 13), (3, 70_001), (8, 100_003), (4, 1 << 20)])
 def test_mxfp4_wire_bytes_and_residuals_vs_oracle(wire, world, n):
     grp = wire.LocalWireGroup(world, n, ef=True)
     padded, shard = grp.kpadded, grp.kpadded // world
