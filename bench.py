@@ -39,6 +39,10 @@ FLOPS_PER_STEP = 2 * 2 * M * N * K                      # two batches
 METRIC = "dual MXFP4 GEMM TFLOPS/GPU (% FP4 peak); FP4 all-reduce algbw GB/s @1/2/4/8"
 WORKLOAD = "dual-batch packed MXFP4 GEMM: 2 x [4096x8192 bf16, quantized on the fly] @ 8192x8192 MXFP4 W -> 2 x 4096x8192 bf16"
 FP4_SPEC_TFLOPS = 9000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one dual-GEMM launch on this workload, from the
+# ncu capture summarised in profiles/mxfp4_gemm_pair_dual_4096x8192x8192.md
+GEMM_DRAM_BYTES_PER_LAUNCH = 182.36e6
+GEMM_ALGORITHMIC_BYTES = 2 * (M * K // 2 + M * K // 32) + (N * K // 2 + N * K // 32) + 2 * M * N * 2
 CPU_SAMPLE_ROWS = 256                                   # rows per batch in the CPU-baseline sample
 
 
@@ -372,12 +376,14 @@ def main():
                     "ms_per_step": e2e_ms_max},
             "gpu_launches": 2 * args.steps + 3 * wsteps,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_kernel<256> (dual batch)",
+            "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_pair_kernel (cta_group::2, dual batch)",
                          "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
                          "peak_source": f"4 x {pk['source']} bf16 burst {pk['bf16']} (no FP4 figure is measured); "
                                         f"spec dense FP4 {FP4_SPEC_TFLOPS}",
                          "frac_of_spec": gemm_tflops / FP4_SPEC_TFLOPS,
-                         "traffic": None},
+                         "flop_per_launch": flops_step,
+                         "traffic": None if args.small else GEMM_DRAM_BYTES_PER_LAUNCH,
+                         "algorithmic_bytes": None if args.small else GEMM_ALGORITHMIC_BYTES},
         }
         if wsteps:
             comp = wn * 0.53125                              # packed + exponent bytes of one buffer
