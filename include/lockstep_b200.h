@@ -65,6 +65,15 @@ int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int b
                       int rounding, uint8_t *codes, uint8_t *packed, float *scale,
                       uint8_t *e8m0, uint8_t *sf, void *stream);
 
+/* Transposed form: x [R, C] row-major -> MXFP4 of x^T, i.e. blocks of 32 run down
+ * the columns of x.  Same arithmetic as ls_quantize_mxfp4 applied to a
+ * transposed copy (lockstep composes fp4.quantize_mxfp4(x.t().contiguous()) for
+ * GEMMs that contract over rows); no copy is made here.  R % 128 == 0.
+ *   packed [C, R/2], scale fp32 [C, R/32], sf = scale-factor layout of a
+ *   [C, R] operand (ls_sf_bytes(C, R)); each may be NULL. */
+int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
+                        uint8_t *packed, float *scale, uint8_t *sf, void *stream);
+
 /* Replaces fp4.py:43-54 (_round_to_e2m1) on values already divided by their
  * scale: q fp32 [n] -> codes [n]. */
 int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *codes, void *stream);

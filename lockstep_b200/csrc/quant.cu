@@ -231,6 +231,77 @@ quantize_f32_kernel(const uint8_t *__restrict__ x, uint32_t n8, QuantOut o)
     }
 }
 
+// ---- transposed quantizer -------------------------------------------------------
+// x [R, C] row-major -> MXFP4 of x^T [C, R], blocks of 32 running down a column of x
+// (what a GEMM that contracts over R needs).  A CTA stages a 128 x 64 tile in shared
+// memory with coalesced row reads, then each thread walks one column segment of 32
+// values, so the packed output of a column is written in 64-byte pieces.
+constexpr int kTR = 128, kTC = 64;
+
+template <typename T, bool RNE>
+__global__ void __launch_bounds__(kThreads)
+quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__restrict__ packed,
+                  float *__restrict__ scale, uint8_t *__restrict__ sf)
+{
+    constexpr int STRIDE = kTC + (sizeof(T) == 2 ? 2 : 1);      // elements; keeps rows on different banks
+    __shared__ T tile[kTR * STRIDE];
+    const int64_t r0 = int64_t(blockIdx.y) * kTR, c0 = int64_t(blockIdx.x) * kTC;
+    constexpr int VEC = 16 / sizeof(T);                          // elements per 16-byte load
+    constexpr int CHUNKS = kTC / VEC;                            // per tile row
+    const bool vec_ok = (C % VEC) == 0;
+    for (int i = threadIdx.x; i < kTR * CHUNKS; i += kThreads) {
+        const int r = i / CHUNKS, cc = (i % CHUNKS) * VEC;
+        T v[VEC];
+        if (vec_ok && c0 + cc + VEC <= C) {
+            *reinterpret_cast<uint4 *>(v) = ld_stream(reinterpret_cast<const uint4 *>(x + (r0 + r) * C + c0 + cc));
+        } else {
+#pragma unroll
+            for (int k = 0; k < VEC; k++) v[k] = c0 + cc + k < C ? x[(r0 + r) * C + c0 + cc + k] : T(0.0f);
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; k++) tile[r * STRIDE + cc + k] = v[k];
+    }
+    __syncthreads();
+    const int rb = threadIdx.x & 3, c = threadIdx.x >> 2;        // 4 blocks of 32 per column, 64 columns
+    float q[32];
+    uint32_t amax = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        q[i] = float(tile[(rb * 32 + i) * STRIDE + c]);
+        amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
+    }
+    const uint32_t e8 = block_e8m0(amax);
+    const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+    uint32_t pk[4];
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = q[8 * h + i] * inv;
+        if (amax < kBitsInf) pk[h] = RNE ? cvt_e2m1x8(t) : cvt_ref_e2m1x8(t);
+        else pk[h] = codes8<RNE>(t);
+    }
+    const int64_t col = c0 + c;
+    // exponent bytes of this column's 4 blocks (lanes rb = 0..3) -> one word at lane rb = 0
+    uint32_t w = e8;
+    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 1) << 8;
+    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 2) << 16;
+    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 3) << 24;
+    if (col < C) {
+        if (packed) *reinterpret_cast<uint4 *>(packed + col * (R / 2) + (r0 + rb * 32) / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        if (rb == 0) {
+            const int64_t kb = r0 / 32;                          // first of 4 blocks: one scale tile
+            if (scale) {
+                uint4 sc;
+                sc.x = scale_bits(w & 0xFFu), sc.y = scale_bits((w >> 8) & 0xFFu);
+                sc.z = scale_bits((w >> 16) & 0xFFu), sc.w = scale_bits(w >> 24);
+                *reinterpret_cast<uint4 *>(scale + col * (R / 32) + kb) = sc;
+            }
+            if (sf) *reinterpret_cast<uint32_t *>(sf + sf_offset(uint32_t(col), uint32_t(kb), uint32_t(R / 128))) = w;
+        }
+    }
+}
+
 // ---- pack / unpack ----------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 pack_kernel(const uint4 *__restrict__ codes, uint2 *__restrict__ packed, int64_t n16,
@@ -520,5 +591,33 @@ extern "C" int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *c
     if (rounding == LS_ROUND_RNE) round_e2m1_kernel<true><<<grid, kThreads, 0, st>>>(q, n, codes);
     else round_e2m1_kernel<false><<<grid, kThreads, 0, st>>>(q, n, codes);
     LS_LAUNCH_CHECK("round_e2m1");
+    return LS_OK;
+}
+
+extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
+                                   uint8_t *packed, float *scale, uint8_t *sf, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (x_dtype != LS_F32 && x_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported dtype %d", x_dtype);
+    if (rounding != LS_ROUND_REF && rounding != LS_ROUND_RNE) return fail(LS_EINVAL, "bad rounding %d", rounding);
+    if (R < 0 || C < 0 || R % 128 != 0) return fail(LS_EINVAL, "R=%lld must be a multiple of 128", (long long)R);
+    if (R == 0 || C == 0) return LS_OK;
+    if (!x || (!packed && !scale && !sf)) return fail(LS_EINVAL, "null pointer");
+    if (!aligned16(x) || !aligned16(packed) || !aligned16(scale) || (reinterpret_cast<uintptr_t>(sf) & 3))
+        return fail(LS_EALIGN, "x, packed and scale must be 16-byte aligned, sf 4-byte");
+    if (C >= (int64_t(1) << 31) || R / 128 > 65535) return fail(LS_EINVAL, "shape too large");
+    dim3 grid(unsigned((C + kTC - 1) / kTC), unsigned(R / kTR));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool rne = rounding == LS_ROUND_RNE;
+    if (x_dtype == LS_BF16) {
+        auto xp = static_cast<const __nv_bfloat16 *>(x);
+        if (rne) quantize_t_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
+        else quantize_t_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
+    } else {
+        auto xp = static_cast<const float *>(x);
+        if (rne) quantize_t_kernel<float, true><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
+        else quantize_t_kernel<float, false><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
+    }
+    LS_LAUNCH_CHECK("quantize_mxfp4_t");
     return LS_OK;
 }

@@ -86,6 +86,24 @@ def quantize_mxfp4_packed(x: torch.Tensor, rounding: str = "ref", want_scale: bo
     return (packed, sf, scale) if want_scale else (packed, sf)
 
 
+def quantize_mxfp4_packed_t(x: torch.Tensor, rounding: str = "ref", want_scale: bool = False):
+    """(extension) quantize_mxfp4_packed(x.t().contiguous()) without the copy:
+    x [R, C] -> packed [C, R // 2] and the scale-factor buffer of a [C, R]
+    operand, blocks of 32 running down the columns of x.  R % 128 == 0."""
+    need_cuda(x)
+    assert x.dim() == 2 and x.shape[0] % 128 == 0, "rows must be a multiple of 128"
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.float()
+    x = x.contiguous()
+    R, C = x.shape
+    packed = torch.empty((C, R // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(C, R), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((C, R // 32), dtype=torch.float32, device=x.device) if want_scale else None
+    check(lib().ls_quantize_mxfp4_t(ptr(x), _lib.dtype_code(x.dtype), R, C, _ROUNDING[rounding],
+                                    ptr(packed), ptr(scale), ptr(sf), stream()))
+    return (packed, sf, scale) if want_scale else (packed, sf)
+
+
 def sf_bytes(rows: int, K: int) -> int:
     """(extension) Size of the scale-factor buffer of a [rows, K] operand."""
     return int(lib().ls_sf_bytes(rows, K))

@@ -36,14 +36,27 @@ def path():
     return "tcgen05-mxfp4" if kernel() else "unavailable"
 
 
-def _gemm(a, b_t, out_dtype):
-    """a [M, K] @ b_t [N, K].T with both operands quantized along K."""
+def _need_kernel():
     k = kernel()
     if k is None:
         raise RuntimeError("MXFP4Linear needs an sm_100 GPU (there is no CPU or fake-quant fallback)")
+    return k
+
+
+def _gemm(a, b_t, out_dtype):
+    """a [M, K] @ b_t [N, K].T with both operands quantized along K."""
+    k = _need_kernel()
     pa, sa = fp4.quantize_mxfp4_packed(a)
     pb, sb = fp4.quantize_mxfp4_packed(b_t)
     return k(pa, pb, sa, sb, out_dtype=out_dtype)
+
+
+def _quant_t(x):
+    """MXFP4 of x.T (blocks run down the columns of x), without a transposed copy
+    when the row count allows the fused kernel."""
+    if x.shape[0] % 128 == 0:
+        return fp4.quantize_mxfp4_packed_t(x)
+    return fp4.quantize_mxfp4_packed(x.t().contiguous())
 
 
 class _MXFP4Matmul(torch.autograd.Function):
@@ -58,9 +71,14 @@ class _MXFP4Matmul(torch.autograd.Function):
         x, w = ctx.saved_tensors
         if ctx.backward_mode == "ste":
             return (gy @ w.to(gy.dtype)).to(x.dtype), (gy.t() @ x.to(gy.dtype)).to(w.dtype), None
+        k = _need_kernel()
         gy = gy.contiguous()
-        gx = _gemm(gy, w.t().contiguous(), x.dtype)                           # [T, K], contract over N
-        gw = _gemm(gy.t().contiguous(), x.t().contiguous(), torch.float32)    # [N, K], contract over T
+        pg, sg = fp4.quantize_mxfp4_packed(gy)                    # gy along N
+        pwt, swt = _quant_t(w)                                    # w.T along N
+        gx = k(pg, pwt, sg, swt, out_dtype=x.dtype)               # [T, K], contract over N
+        pgt, sgt = _quant_t(gy)                                   # gy.T along tokens
+        pxt, sxt = _quant_t(x)                                    # x.T along tokens
+        gw = k(pgt, pxt, sgt, sxt, out_dtype=torch.float32)       # [N, K], contract over tokens
         return gx, gw.to(w.dtype), None
 
 

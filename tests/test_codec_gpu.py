@@ -206,6 +206,27 @@ def test_quantize_random_vs_c_oracle(fp4, dtype, shape):
             assert np.array_equal(sf2[r // 128, kb // 4, r % 32, (r % 128) // 32, kb % 4], e[:, kb])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,C", [(128, 64), (256, 100), (384, 1000), (1024, 4096)])
+def test_transposed_quantizer_equals_quantizer_of_transpose(fp4, dtype, R, C, golden):
+    g = torch.Generator().manual_seed(R + C)
+    x = torch.randn(R, C, generator=g) * torch.exp2(torch.randint(-20, 20, (1, C), generator=g).float())
+    x = torch.where(torch.rand(R, C, generator=g) < 0.01, x * 50, x)
+    if R == 128:                                   # adversarial rows of the golden set as columns
+        adv = torch.from_numpy(golden("quant_adversarial_f32")["x"].view(np.float32).copy())[:C * 4]
+        x = adv.reshape(C, 4 * 32).t().contiguous()
+    x = x.to(dtype)
+    want = cref.quantize(x.t().contiguous().float().numpy())
+    packed, sf, scale = fp4.quantize_mxfp4_packed_t(x.cuda(), want_scale=True)
+    assert np.array_equal(_np(packed), want["packed"])
+    assert np.array_equal(_np(scale), want["scale"])
+    p2, sf2 = fp4.quantize_mxfp4_packed(x.t().contiguous().cuda())
+    assert torch.equal(packed, p2)
+    rows = np.arange(C)                            # rows past C in the last 128-row tile are padding
+    a, b = (_np(t).reshape(-1, R // 128, 32, 4, 4)[rows // 128, :, rows % 32, (rows % 128) // 32] for t in (sf, sf2))
+    assert np.array_equal(a, b)
+
+
 def test_fp32_exponent_rule_on_gpu(fp4):
     # block maxima a few ulps below powers of two: fp32 log2 rounds up
     vals = []
