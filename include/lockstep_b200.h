@@ -118,6 +118,20 @@ int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t
                        const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
                        void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 
+/* GEMM whose epilogue also emits MXFP4 of act(C) for a following MXFP4 GEMM
+ * (scale blocks of 32 along N), so that C is not re-read by a quantize pass.
+ * Covers the chain  _MXFP4Matmul -> F.gelu -> _MXFP4Matmul  of lockstep's
+ * block (fp4_linear.py:33-40 twice, train.py:53); no single lockstep function
+ * does this.  The quantized values are those a separate pass would see: C
+ * rounded to out_dtype, act in fp32, rounded to out_dtype, then
+ * ls_quantize_mxfp4's arithmetic.
+ *   c         [M, N] or NULL (then only the quantized form is written)
+ *   act       0 = none, 1 = GELU, 0.5 x (1 + erf(x / sqrt 2))
+ *   q_packed  [M, N/2];  q_sf  ls_sf_bytes(M, N) bytes;  N % 128 == 0 */
+int ls_mxfp4_gemm_quant(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                        void *c, int out_dtype, int act, uint8_t *q_packed, uint8_t *q_sf, int64_t M,
+                        int64_t N, int64_t K, void *stream);
+
 /* Which GEMM kernel the two entry points above launch: 0 = by shape (default),
  * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles
  * (cta_group::2).  Results are identical; for measurements and tests. */

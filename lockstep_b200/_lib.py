@@ -27,6 +27,7 @@ _SIGS = {
     "ls_dequantize_mxfp4": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_int, c_vp, c_int, c_vp]),
     "ls_mxfp4_gemm": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_mxfp4_gemm_dual": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
+    "ls_mxfp4_gemm_quant": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
     "ls_gemm_status": (c_int, [c_vp]),
     "ls_gemm_set_variant": (c_int, [c_int]),
     "ls_mxfp4_linear_noalloc": (c_int, [c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),

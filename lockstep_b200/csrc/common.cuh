@@ -14,6 +14,14 @@ namespace ls {
 int fail(int code, const char *fmt, ...);          // records the message, returns code
 int check_device();                                 // LS_OK or LS_EARCH / LS_ECUDA
 int sm_count();                                     // SMs of the current device
+struct QuantEpilogue {              // optional MXFP4 output of act(C), per batch
+    uint8_t *packed[2];
+    uint8_t *sf[2];
+    int act;                        // 0 none, 1 GELU (erf form)
+};
+int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
+               const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
+               int64_t N, int64_t K, void *stream, int *err, const QuantEpilogue *qe);
 int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
                 const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
                 int64_t N, int64_t K, void *stream, int *err);

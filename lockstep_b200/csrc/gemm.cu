@@ -56,7 +56,52 @@ struct GemmParams {
     int splits;                    // split-K factor of the single-CTA kernel (1 = off)
     int kt_per_split;              // k-tiles per split
     float *partial;                // [splits, M, N] fp32 partial sums when splits > 1
+    // fused quantizing epilogue (the consumer of C is another MXFP4 GEMM): MXFP4 of act(C)
+    uint8_t *q_packed[2];          // [M, N/2] packed codes, or NULL
+    uint8_t *q_sf[2];              // scale-factor bytes of a [M, N] operand
+    int act;                       // 0 none, 1 GELU (erf form)
+    int store_c;                   // 0: C itself is not written (only its quantized form)
 };
+
+// MXFP4 of one row's 32 consecutive outputs (exactly one scale block), as the next GEMM
+// reads it.  The values quantized are the ones a separate pass would see: the
+// accumulator rounded to the output type, the activation applied in fp32 and rounded
+// to the output type again.
+__device__ __forceinline__ void quant_chunk(const GemmParams &p, int b, int row, int col0, const uint32_t (&r)[32])
+{
+    if (row >= p.M || col0 >= p.N) return;
+    float v[32];
+    uint32_t amax = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        float x = __uint_as_float(r[i]);
+        if (p.out_bf16) x = __bfloat162float(__float2bfloat16_rn(x));
+        if (p.act == 1) {
+            x = (x * 0.5f) * (1.0f + erff(x * 0.70710678118654752440f));
+            if (p.out_bf16) x = __bfloat162float(__float2bfloat16_rn(x));
+        }
+        v[i] = x;
+        amax = max(amax, __float_as_uint(x) & 0x7FFFFFFFu);
+    }
+    const uint32_t e8 = block_e8m0(amax);
+    const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+    uint32_t pk[4];
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        float t[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) t[i] = v[8 * h + i] * inv;
+        if (amax < kBitsInf) {
+            pk[h] = cvt_ref_e2m1x8(t);
+        } else {
+            pk[h] = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) pk[h] |= e2m1_code<false>(t[i]) << (4 * i);
+        }
+    }
+    *reinterpret_cast<uint4 *>(p.q_packed[b] + int64_t(row) * (p.N / 2) + col0 / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    p.q_sf[b][sf_offset(uint32_t(row), uint32_t(col0 / 32), uint32_t(p.N / 128))] = uint8_t(e8);
+}
 
 __device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bool bf16, int row, int col0,
                                             const uint32_t (&r)[32])
@@ -269,7 +314,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_free_bar);
                 }
-                store_chunk(p, dst, dst_bf16, row, nt * BN + 32 * c, r);
+                if (p.store_c || p.splits > 1) store_chunk(p, dst, dst_bf16, row, nt * BN + 32 * c, r);
+                if (p.q_packed[b]) quant_chunk(p, b, row, nt * BN + 32 * c, r);
             }
         }
     }
@@ -507,7 +553,8 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
                 }
-                store_chunk(p, p.c[my_batch], p.out_bf16, row, nt * C::BN + 32 * c, r);
+                if (p.store_c) store_chunk(p, p.c[my_batch], p.out_bf16, row, nt * C::BN + 32 * c, r);
+                if (p.q_packed[my_batch]) quant_chunk(p, my_batch, row, nt * C::BN + 32 * c, r);
             }
         }
     }
@@ -677,18 +724,34 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
                 const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
                 int64_t N, int64_t K, void *stream, int *err)
 {
+    return gemm_fused(nbatch, a0, a1, w, sfa0, sfa1, sfb, c0, c1, out_dtype, M, N, K, stream, err, nullptr);
+}
+
+int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
+               const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
+               int64_t N, int64_t K, void *stream, int *err, const QuantEpilogue *qe)
+{
     if (int rc = check_device()) return rc;
     if (M < 0 || N < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a multiple of 128", (long long)K);
     if (out_dtype != LS_F32 && out_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported output dtype %d", out_dtype);
     if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(LS_EINVAL, "dimension too large");
     if (M == 0 || N == 0) return LS_OK;
     if (K == 0) return fail(LS_EINVAL, "K must be positive");
-    const void *ptrs[] = {a0, w, sfa0, sfb, c0};
+    const bool fused = qe && qe->packed[0];
+    const void *ptrs[] = {a0, w, sfa0, sfb};
     for (const void *q : ptrs)
         if (!q) return fail(LS_EINVAL, "null pointer");
-    if (nbatch == 2 && (!a1 || !sfa1 || !c1)) return fail(LS_EINVAL, "null pointer (second batch)");
+    if (!c0 && !fused) return fail(LS_EINVAL, "null output");
+    if (nbatch == 2 && (!a1 || !sfa1 || (!c1 && !fused))) return fail(LS_EINVAL, "null pointer (second batch)");
+    if (fused) {
+        if (N % 128 != 0) return fail(LS_EINVAL, "quantizing epilogue needs N %% 128 == 0 (N=%lld)", (long long)N);
+        if (!qe->sf[0] || (nbatch == 2 && (!qe->packed[1] || !qe->sf[1]))) return fail(LS_EINVAL, "null quantized output");
+        if (qe->act != 0 && qe->act != 1) return fail(LS_EINVAL, "unknown activation %d", qe->act);
+        if (!aligned16(qe->packed[0]) || (nbatch == 2 && !aligned16(qe->packed[1])))
+            return fail(LS_EALIGN, "quantized outputs must be 16-byte aligned");
+    }
     if (!aligned16(a0) || !aligned16(w) || !aligned16(sfa0) || !aligned16(sfb) || !aligned16(c0) ||
-        (nbatch == 2 && (!aligned16(a1) || !aligned16(sfa1) || !aligned16(c1))))
+        (nbatch == 2 && (!aligned16(a1) || !aligned16(sfa1) || !aligned16(c1))))    // NULL counts as aligned
         return fail(LS_EALIGN, "GEMM operands, scale buffers and outputs must be 16-byte aligned");
     const bool caller_err = err != nullptr;
     if (!err) err = error_word();
@@ -712,12 +775,18 @@ int gemm_common(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t 
     p.splits = 1;
     p.kt_per_split = int((K / 2 + BKB - 1) / BKB);
     p.partial = nullptr;
+    p.store_c = c0 != nullptr;
+    p.act = fused ? qe->act : 0;
+    for (int b = 0; b < 2; b++) {
+        p.q_packed[b] = fused ? qe->packed[nbatch == 2 ? b : 0] : nullptr;
+        p.q_sf[b] = fused ? qe->sf[nbatch == 2 ? b : 0] : nullptr;
+    }
     if (pair) return launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
     // Few tiles and a long K (decode-like shapes): split K over otherwise idle SMs.  Not on the
     // allocation-free path (caller-supplied error word), which must not touch an allocator.
     const int tiles = int(((M + BM - 1) / BM) * ((N + bn - 1) / bn)) * nbatch;
     const int k_tiles = p.kt_per_split;
-    if (!caller_err && M <= 32 && tiles * 2 <= sm_count() && k_tiles >= 4) {      // partial traffic grows with M
+    if (!caller_err && !fused && M <= 32 && tiles * 2 <= sm_count() && k_tiles >= 4) {      // partial traffic grows with M
         int s = sm_count() / tiles;
         if (s > k_tiles / 2) s = k_tiles / 2;
         if (s > 16) s = 16;
@@ -776,4 +845,13 @@ extern "C" int ls_gemm_set_variant(int variant)
     if (variant < 0 || variant > 2) return fail(LS_EINVAL, "variant must be 0, 1 or 2");
     g_gemm_variant = variant;
     return LS_OK;
+}
+
+extern "C" int ls_mxfp4_gemm_quant(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                                   void *c, int out_dtype, int act, uint8_t *q_packed, uint8_t *q_sf, int64_t M,
+                                   int64_t N, int64_t K, void *stream)
+{
+    if (!q_packed || !q_sf) return fail(LS_EINVAL, "null quantized output");
+    QuantEpilogue qe{{q_packed, nullptr}, {q_sf, nullptr}, act};
+    return gemm_fused(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream, nullptr, &qe);
 }

@@ -67,20 +67,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
     return v;
 }
 
-// One thread per CTA polls; returns after the flags of all `world` ranks reached `epoch`.
+// Thread s of every CTA polls rank s's flag; returns after all `world` flags reached `epoch`
+// (or after poll_limit polls, recording the time-out).
 __device__ __forceinline__ void wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch,
                                            uint32_t poll_limit)
 {
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < world; s++) {
-            uint32_t polls = 0;
-            while (int32_t(ld_acquire_sys(flags + s) - epoch) < 0) {
-                if (++polls > poll_limit) {
-                    atomicExch(&h->status, 1u);
-                    break;
-                }
-                __nanosleep(100);
+    if (int(threadIdx.x) < world) {
+        uint32_t polls = 0;
+        while (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
+            if (++polls > poll_limit) {
+                atomicExch(&h->status, 1u);
+                break;
             }
+            __nanosleep(100);
         }
     }
     __syncthreads();
@@ -178,32 +177,33 @@ wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res
     const uint32_t stride = gridDim.x * kThreads;
     const int lane = threadIdx.x & 31;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);      // a multiple of 32: warps never straddle shards
-    for (int o = 0; o < geo.world; o++) {
+    const uint32_t groups = uint32_t(geo.padded / 8);
+    // one flat loop over all groups; the owner index advances with the position
+    uint32_t g8 = blockIdx.x * kThreads + threadIdx.x;
+    uint32_t o = g8 / g_per_shard, in_shard = g8 - o * g_per_shard;
+    for (; g8 < groups; g8 += stride, in_shard += stride) {
+        while (in_shard >= g_per_shard) in_shard -= g_per_shard, o++;
         uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
-        uint8_t *slot_e = slot + geo.shard / 2;
-        const int64_t first = int64_t(o) * geo.shard;          // first element of the shard
-        for (uint32_t in_shard = blockIdx.x * kThreads + threadIdx.x; in_shard - lane < g_per_shard; in_shard += stride) {
-            const int64_t i0 = first + int64_t(in_shard) * 8;
-            float v[8], dq[8];
-            load8(g, i0, n, v);
-            if (res) {
-                float r[8];
-                load8(res, i0, geo.padded, r);
+        const int64_t i0 = int64_t(g8) * 8;
+        float v[8], dq[8];
+        load8(g, i0, n, v);
+        if (res) {
+            float r[8];
+            load8(res, i0, geo.padded, r);
 #pragma unroll
-                for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
-            }
-            uint32_t e8;
-            const uint32_t pk = encode8(v, e8, dq);
-            if (res) {
-                float r[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], dq[i]);
-                store8(res, i0, geo.padded, r);
-            }
-            reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
-            const uint2 ex = gather_exponents(e8);
-            if (lane == 0) *reinterpret_cast<uint2 *>(slot_e + in_shard / 4) = ex;
+            for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
         }
+        uint32_t e8;
+        const uint32_t pk = encode8(v, e8, dq);
+        if (res) {
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], dq[i]);
+            store8(res, i0, geo.padded, r);
+        }
+        reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
+        const uint2 ex = gather_exponents(e8);
+        if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + in_shard / 4) = ex;
     }
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
     signal_done(mine, &mine->counter[0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
@@ -345,10 +345,10 @@ wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, 
     }
 }
 
-int grid_for(int64_t groups)
+int grid_for(int64_t groups, int ctas_per_sm = 8)
 {
     int64_t want = (groups + kThreads - 1) / kThreads;
-    int64_t cap = int64_t(sm_count()) * 8;
+    int64_t cap = int64_t(sm_count()) * ctas_per_sm;           // one resident wave: flags are polled once per CTA
     return int(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
@@ -460,7 +460,7 @@ extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, 
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
     w->epoch++;
-    wire_send_kernel<<<grid_for(w->g.padded / 8), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    wire_send_kernel<<<grid_for(w->g.padded / 8, 5), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         g, numel, res, w->g, w->peers, w->epoch);
     LS_LAUNCH_CHECK("wire_send");
     return LS_OK;
@@ -470,7 +470,7 @@ extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
 {
     Wire *w = as_wire(h);
     if (!w || !w->mapped) return fail(LS_ESTATE, "wire not ready");
-    const int grid = grid_for(w->g.shard / 8);
+    const int grid = grid_for(w->g.shard / 8, 4);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (w->g.world) {
     case 1: wire_reduce_kernel<1><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;

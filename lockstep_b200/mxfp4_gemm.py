@@ -48,6 +48,26 @@ def mxfp4_gemm_packed(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloat16):
     return c
 
 
+def mxfp4_gemm_packed_quant(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloat16, act=None, want_c=True):
+    """(extension) mxfp4_gemm_packed whose epilogue also quantizes act(C) to MXFP4
+    for a following GEMM (act: None or "gelu").  Returns (C or None, packed
+    [M, N // 2], scale-factor bytes of a [M, N] operand).  N % 128 == 0."""
+    need_cuda(a_pk, bt_pk, a_scale, b_scale)
+    M, Kh = a_pk.shape
+    N, Kh2 = bt_pk.shape
+    K = Kh * 2
+    assert Kh == Kh2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
+    assert N % 128 == 0, "N must be a multiple of 128 for the quantized output"
+    a_pk, bt_pk = a_pk.contiguous(), bt_pk.contiguous()
+    sfa, sfb = _sf(a_scale, M, K), _sf(b_scale, N, K)
+    c = torch.empty((M, N), device=a_pk.device, dtype=out_dtype) if want_c else None
+    q = torch.empty((M, N // 2), device=a_pk.device, dtype=torch.uint8)
+    q_sf = torch.empty(fp4.sf_bytes(M, N), device=a_pk.device, dtype=torch.uint8)
+    check(lib().ls_mxfp4_gemm_quant(ptr(a_pk), ptr(bt_pk), ptr(sfa), ptr(sfb), ptr(c), _lib.dtype_code(out_dtype),
+                                    {None: 0, "gelu": 1}[act], ptr(q), ptr(q_sf), M, N, K, stream()))
+    return c, q, q_sf
+
+
 _E4M3_TO_CODE = None
 
 

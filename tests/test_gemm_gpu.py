@@ -134,6 +134,57 @@ def test_skinny_shapes_split_k(mods, M, N, K):
     assert torch.equal(mg.mxfp4_gemm_packed(pa, pw, sfa, sfw), mg.mxfp4_gemm_packed(pa, pw, sfa, sfw))   # deterministic
 
 
+@pytest.mark.parametrize("M,N,K,dt", [(256, 512, 384, torch.bfloat16), (130, 256, 256, torch.bfloat16),
+                                      (4096, 1024, 1024, torch.bfloat16), (64, 128, 128, torch.float32)])
+def test_quantizing_epilogue_equals_separate_pass(mods, M, N, K, dt):
+    fp4, mg, _ = mods
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    pa, sfa = fp4.quantize_mxfp4_packed(a)
+    pw, sfw = fp4.quantize_mxfp4_packed(w)
+    plain = mg.mxfp4_gemm_packed(pa, pw, sfa, sfw, out_dtype=dt)
+
+    def valid_sf(t):                        # rows past M in the last 128-row tile are padding
+        rows = np.arange(M)
+        return t.cpu().numpy().reshape(-1, N // 128, 32, 4, 4)[rows // 128, :, rows % 32, (rows % 128) // 32]
+
+    c, q, q_sf = mg.mxfp4_gemm_packed_quant(pa, pw, sfa, sfw, out_dtype=dt)
+    mg.gemm_status()
+    assert torch.equal(c, plain)
+    want_q, want_sf = fp4.quantize_mxfp4_packed(plain)
+    assert torch.equal(q, want_q) and np.array_equal(valid_sf(q_sf), valid_sf(want_sf))
+
+    c2, q2, q2_sf = mg.mxfp4_gemm_packed_quant(pa, pw, sfa, sfw, out_dtype=dt, act="gelu", want_c=False)
+    mg.gemm_status()
+    assert c2 is None
+    want_q, want_sf = fp4.quantize_mxfp4_packed(torch.nn.functional.gelu(plain))
+    differ = (q2 != want_q).float().mean().item()       # erf of this library vs torch's kernel: same formula
+    assert differ <= 1e-4, differ
+    if differ == 0:
+        assert np.array_equal(valid_sf(q2_sf), valid_sf(want_sf))
+
+
+def test_fused_mlp_chain(mods):
+    # fc -> GELU -> quantize -> out with the activations never leaving MXFP4 between the GEMMs
+    fp4, mg, _ = mods
+    T, D = 512, 256
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    w1 = (torch.randn(4 * D, D, device="cuda", generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(D, 4 * D, device="cuda", generator=g) * 0.05).bfloat16()
+    px, sx = fp4.quantize_mxfp4_packed(x)
+    p1, s1 = fp4.quantize_mxfp4_packed(w1)
+    p2, s2 = fp4.quantize_mxfp4_packed(w2)
+    h = mg.mxfp4_gemm_packed(px, p1, sx, s1)
+    ph, sh = fp4.quantize_mxfp4_packed(torch.nn.functional.gelu(h))
+    y_ref = mg.mxfp4_gemm_packed(ph, p2, sh, s2)
+    _, qh, qsf = mg.mxfp4_gemm_packed_quant(px, p1, sx, s1, act="gelu", want_c=False)
+    y = mg.mxfp4_gemm_packed(qh, p2, qsf, s2)
+    mg.gemm_status()
+    _check(y, y_ref, "fused mlp")
+
+
 def test_fp8_entry(mods):
     fp4, mg, _ = mods
     M, N, K = 128, 256, 256
