@@ -174,6 +174,17 @@ int ls_wire_finish(void *handle, float *g, int64_t numel, void *stream);
 int ls_wire_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, int reverse,
                       void *stream);
 
+/* The reference's integer wires (wire.py:104-138: int16, int8, int8 with error
+ * feedback) on the same transport: a shared grid per chunk of 64 from the
+ * maximum over ranks, exact int32 sum at the owner, owner re-encodes, gather.
+ * bits = 8 or 16.  Set-up as for the MXFP4 wire (handles, map).  One step is
+ * four launches; ls_wire_int_phase runs one of them (0 publish chunk maxima,
+ * 1 quantize and send, 2 owner, 3 decode) for callers that interleave ranks in
+ * one process.  res [padded] / ores [padded / world]: residuals or NULL. */
+int ls_wire_create_int(int rank, int world, int64_t padded, int bits, void **handle);
+int ls_wire_int_phase(void *handle, int phase, float *g, int64_t numel, float *res, float *ores, void *stream);
+int ls_wire_int_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, void *stream);
+
 /* How many times (about 100 ns apart, default 2^22 = ~0.5 s) a kernel polls a
  * peer's flag before it gives up, records a time-out in the status word and
  * carries on with whatever its buffers hold; the context stays usable. */

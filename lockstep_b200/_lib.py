@@ -41,6 +41,9 @@ _SIGS = {
     "ls_wire_reduce": (c_int, [c_vp, c_vp, c_int, c_vp]),
     "ls_wire_finish": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "ls_wire_allreduce": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_int, c_vp]),
+    "ls_wire_create_int": (c_int, [c_int, c_int, c_i64, c_int, ctypes.POINTER(c_vp)]),
+    "ls_wire_int_phase": (c_int, [c_vp, c_int, c_vp, c_i64, c_vp, c_vp, c_vp]),
+    "ls_wire_int_allreduce": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "ls_wire_status": (c_int, [c_vp, c_vp]),
     "ls_wire_set_poll_limit": (c_int, [c_vp, c_i64]),
     "ls_wire_debug_slots": (c_int, [c_vp, c_int, c_vp, ctypes.POINTER(c_i64), c_vp]),

@@ -33,6 +33,8 @@ struct Header {                 // start of every rank's arena
     uint32_t ag_flag[kMaxWorld];    // epoch of the last completed reduce of owner o
     uint32_t counter[2];            // CTA completion counters (send, reduce)
     uint32_t status;                // non-zero: a wait ran out
+    uint32_t mx_flag[kMaxWorld];    // integer wires: epoch of rank s's last published chunk maxima
+    uint32_t counter_mx;
 };
 constexpr size_t kHeaderBytes = 256;
 
@@ -44,6 +46,8 @@ struct WireGeom {
     int64_t slot_bytes;             // packed + exponent bytes of one shard, 256-aligned
     int64_t rs_off, ag_off;         // byte offsets of the slot arrays in an arena
     uint32_t poll_limit;            // polls before a wait on a peer's flag gives up
+    int bits;                       // 0: MXFP4 payload; 8 / 16: integer payload (wire.py's int8 / int16)
+    int64_t mx_off;                 // integer wires: [world][padded / 64] fp32 chunk maxima of every rank
 };
 
 struct Wire {
@@ -292,7 +296,8 @@ wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t
 // One thread decodes 4 values (two packed bytes) per step and writes one 16-byte
 // word, so every load and store of a warp is one contiguous segment.  POW2: the
 // world size is a power of two, so dividing by it is an exact multiplication that
-// folds into the block scale.
+// folds into the block scale.  Otherwise the value is multiplied by fp32(1 / world),
+// which is how torch divides a tensor by a scalar (wire.py:138 `.div_(world)`).
 template <bool POW2>
 __global__ void __launch_bounds__(kThreads)
 wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
@@ -332,7 +337,7 @@ wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, 
                 float t[4];
                 e2m1x4_values(pk[u], t);
 #pragma unroll
-                for (int i = 0; i < 4; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
+                for (int i = 0; i < 4; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fmul_rn(__fmul_rn(t[i], sc), rw);
                 const int64_t i0 = int64_t(q) * 4;
                 if (vec && i0 + 4 <= ns) {
                     *reinterpret_cast<float4 *>(gs + i0) = make_float4(t[0], t[1], t[2], t[3]);
@@ -342,6 +347,208 @@ wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, 
                 }
             }
         }
+    }
+}
+
+// ======================================================================================
+// Integer wires of the reference (wire.py:104-138): one fp32 scale per chunk of 64, shared
+// by all ranks (maximum over ranks), exact int32 sum at the owner, owner re-encodes with its
+// own grid, gather.  Same transport as above; every fp32 operation is the one torch runs,
+// explicitly rounded (division by IEEE divide, rounding to nearest even integer).
+// One thread owns 8 consecutive elements; 8 adjacent lanes share a chunk.
+// ======================================================================================
+constexpr int kChunk = 64;
+
+__device__ __forceinline__ float chunk_max8(const float (&v)[8])
+{
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) m = max(m, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+    return __uint_as_float(m);
+}
+// torch evaluates `lim / m` (Python scalar over tensor) as m.reciprocal() * lim: two roundings
+__device__ __forceinline__ float grid_scale(float m, float lim) { return m > 0.0f ? __fmul_rn(__frcp_rn(m), lim) : 1.0f; }
+__device__ __forceinline__ int quant_int(float x, float s, int lim)
+{
+    return max(-lim, min(lim, __float2int_rn(__fmul_rn(x, s))));       // torch.round: half to even
+}
+template <int BITS>
+__device__ __forceinline__ void store_q8(uint8_t *slot, uint32_t g8, const int (&q)[8])
+{
+    if (BITS == 8) {
+        uint2 w;
+        w.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | (uint32_t(q[3] & 0xFF) << 24);
+        w.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | (uint32_t(q[7] & 0xFF) << 24);
+        reinterpret_cast<uint2 *>(slot)[g8] = w;
+    } else {
+        uint4 w;
+        w.x = (q[0] & 0xFFFF) | (uint32_t(q[1] & 0xFFFF) << 16), w.y = (q[2] & 0xFFFF) | (uint32_t(q[3] & 0xFFFF) << 16);
+        w.z = (q[4] & 0xFFFF) | (uint32_t(q[5] & 0xFFFF) << 16), w.w = (q[6] & 0xFFFF) | (uint32_t(q[7] & 0xFFFF) << 16);
+        reinterpret_cast<uint4 *>(slot)[g8] = w;
+    }
+}
+template <int BITS>
+__device__ __forceinline__ void load_q8(const uint8_t *slot, uint32_t g8, int (&q)[8])
+{
+    if (BITS == 8) {
+        const uint2 w = reinterpret_cast<const uint2 *>(slot)[g8];
+#pragma unroll
+        for (int i = 0; i < 4; i++) q[i] = int(int8_t(w.x >> (8 * i))), q[4 + i] = int(int8_t(w.y >> (8 * i)));
+    } else {
+        const uint4 w = reinterpret_cast<const uint4 *>(slot)[g8];
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) q[2 * i] = int(int16_t(u[i] & 0xFFFF)), q[2 * i + 1] = int(int16_t(u[i] >> 16));
+    }
+}
+// maximum over ranks of the published chunk maxima (chunk index c of the padded buffer)
+__device__ __forceinline__ float shared_max(const uint8_t *my, const WireGeom &geo, int64_t c)
+{
+    const float *mx = reinterpret_cast<const float *>(my + geo.mx_off);
+    const int64_t chunks = geo.padded / kChunk;
+    float m = 0.0f;
+    for (int s = 0; s < geo.world; s++) m = fmaxf(m, mx[s * chunks + c]);
+    return m;
+}
+
+// phase 0: publish this rank's chunk maxima of v = g + res to every rank
+__global__ void __launch_bounds__(kThreads)
+wire_int_max_kernel(const float *__restrict__ g, int64_t n, const float *__restrict__ res, WireGeom geo, Peers peers,
+                    uint32_t epoch)
+{
+    const uint32_t groups = uint32_t(geo.padded / 8), stride = gridDim.x * kThreads;
+    const int64_t chunks = geo.padded / kChunk;
+    for (uint32_t g8 = blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
+        float v[8];
+        load8(g, int64_t(g8) * 8, n, v);
+        if (res) {
+            float r[8];
+            load8(res, int64_t(g8) * 8, geo.padded, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
+        }
+        const float m = chunk_max8(v);
+        if ((threadIdx.x & 7) == 0)
+            for (int p = 0; p < geo.world; p++)
+                reinterpret_cast<float *>(peers.arena[p] + geo.mx_off)[geo.rank * chunks + g8 / 8] = m;
+    }
+    Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
+    signal_done(mine, &mine->counter_mx, peers, geo.world, geo.rank, offsetof(Header, mx_flag), epoch);
+}
+
+// phase 1: quantize on the shared grid, update the sender residual, push to the owners
+template <int BITS>
+__global__ void __launch_bounds__(kThreads)
+wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, WireGeom geo, Peers peers,
+                     uint32_t epoch)
+{
+    constexpr int LIM = (1 << (BITS - 1)) - 1;
+    uint8_t *my = peers.arena[geo.rank];
+    Header *mine = reinterpret_cast<Header *>(my);
+    wait_flags(mine, mine->mx_flag, geo.world, epoch, geo.poll_limit);
+    const uint32_t groups = uint32_t(geo.padded / 8), stride = gridDim.x * kThreads;
+    const uint32_t g_per_shard = uint32_t(geo.shard / 8);
+    uint32_t g8 = blockIdx.x * kThreads + threadIdx.x;
+    uint32_t o = g8 / g_per_shard, in_shard = g8 - o * g_per_shard;
+    for (; g8 < groups; g8 += stride, in_shard += stride) {
+        while (in_shard >= g_per_shard) in_shard -= g_per_shard, o++;
+        float v[8];
+        load8(g, int64_t(g8) * 8, n, v);
+        if (res) {
+            float r[8];
+            load8(res, int64_t(g8) * 8, geo.padded, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
+        }
+        const float s = grid_scale(shared_max(my, geo, g8 / 8), float(LIM));
+        int q[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) q[i] = quant_int(v[i], s, LIM);
+        if (res) {
+            float r[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], __fdiv_rn(float(q[i]), s));
+            store8(res, int64_t(g8) * 8, geo.padded, r);
+        }
+        store_q8<BITS>(peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes, in_shard, q);
+    }
+    signal_done(mine, &mine->counter[0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
+}
+
+// phase 2: exact integer sum at the owner, owner grid, owner residual, push to everyone
+template <int BITS>
+__global__ void __launch_bounds__(kThreads)
+wire_int_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t epoch)
+{
+    constexpr int LIM = (1 << (BITS - 1)) - 1;
+    uint8_t *my = peers.arena[geo.rank];
+    Header *mine = reinterpret_cast<Header *>(my);
+    wait_flags(mine, mine->rs_flag, geo.world, epoch, geo.poll_limit);
+    const uint32_t groups = uint32_t(geo.shard / 8), stride = gridDim.x * kThreads;
+    const int64_t first_chunk = int64_t(geo.rank) * (geo.shard / kChunk);
+    const int64_t payload = geo.shard * (BITS / 8);
+    for (uint32_t g8 = blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
+        int sum[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) sum[i] = 0;
+        for (int t = 0; t < geo.world; t++) {
+            int q[8];
+            load_q8<BITS>(my + geo.rs_off + int64_t(t) * geo.slot_bytes, g8, q);
+#pragma unroll
+            for (int i = 0; i < 8; i++) sum[i] += q[i];
+        }
+        const float s = grid_scale(shared_max(my, geo, first_chunk + g8 / 8), float(LIM));
+        float val[8], r[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) val[i] = __fdiv_rn(float(sum[i]), s);
+        if (ores) {
+            load8(ores, int64_t(g8) * 8, geo.shard, r);
+#pragma unroll
+            for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
+        }
+        const float s2 = grid_scale(chunk_max8(val), float(LIM));
+        int q2[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) q2[i] = quant_int(val[i], s2, LIM);
+        if (ores) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(val[i], __fdiv_rn(float(q2[i]), s2));
+            store8(ores, int64_t(g8) * 8, geo.shard, r);
+        }
+        for (int p = 0; p < geo.world; p++) {
+            uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
+            store_q8<BITS>(slot, g8, q2);
+            if ((threadIdx.x & 7) == 0) reinterpret_cast<float *>(slot + payload)[g8 / 8] = s2;
+        }
+    }
+    signal_done(mine, &mine->counter[1], peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
+}
+
+// phase 3: decode the gathered shards, divide by the world size
+template <int BITS>
+__global__ void __launch_bounds__(kThreads)
+wire_int_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
+{
+    uint8_t *my = peers.arena[geo.rank];
+    Header *mine = reinterpret_cast<Header *>(my);
+    wait_flags(mine, mine->ag_flag, geo.world, epoch, geo.poll_limit);
+    const uint32_t groups = uint32_t((n + 7) / 8), stride = gridDim.x * kThreads;
+    const uint32_t g_per_shard = uint32_t(geo.shard / 8);
+    const int64_t payload = geo.shard * (BITS / 8);
+    const float rw = 1.0f / float(geo.world);
+    for (uint32_t g8 = blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
+        const uint32_t o = g8 / g_per_shard, in_shard = g8 - o * g_per_shard;
+        const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
+        int q[8];
+        load_q8<BITS>(slot, in_shard, q);
+        const float s2 = reinterpret_cast<const float *>(slot + payload)[in_shard / 8];
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __fmul_rn(__fdiv_rn(float(q[i]), s2), rw);     // torch divides by a scalar as x * (1 / w)
+        store8(g, int64_t(g8) * 8, n, v);
     }
 }
 
@@ -358,6 +565,7 @@ int check_call(Wire *w, const float *g, int64_t numel)
 {
     if (!w) return fail(LS_EINVAL, "null wire handle");
     if (!w->mapped) return fail(LS_ESTATE, "wire peers are not mapped yet");
+    if (w->g.bits) return fail(LS_ESTATE, "this handle carries an integer wire");
     if (!g || numel <= 0 || numel > w->g.padded) return fail(LS_EINVAL, "numel %lld does not fit the wire (padded %lld)", (long long)numel, (long long)w->g.padded);
     return LS_OK;
 }
@@ -369,7 +577,17 @@ using namespace ls;
 
 extern "C" int64_t ls_wire_handle_bytes(void) { return int64_t(sizeof(cudaIpcMemHandle_t)); }
 
+static int wire_create(int rank, int world, int64_t padded, int bits, void **out);
 extern "C" int ls_wire_create(int rank, int world, int64_t padded, void **out)
+{
+    return wire_create(rank, world, padded, 0, out);
+}
+extern "C" int ls_wire_create_int(int rank, int world, int64_t padded, int bits, void **out)
+{
+    if (bits != 8 && bits != 16) return fail(LS_EINVAL, "integer wire has 8 or 16 bits, got %d", bits);
+    return wire_create(rank, world, padded, bits, out);
+}
+static int wire_create(int rank, int world, int64_t padded, int bits, void **out)
 {
     if (int rc = check_device()) return rc;
     if (!out) return fail(LS_EINVAL, "null output");
@@ -379,12 +597,14 @@ extern "C" int ls_wire_create(int rank, int world, int64_t padded, void **out)
     Wire *w = new (std::nothrow) Wire();
     if (!w) return fail(LS_ECUDA, "out of host memory");
     w->g.rank = rank, w->g.world = world, w->g.padded = padded, w->g.shard = padded / world;
-    int64_t raw = w->g.shard / 2 + w->g.shard / 32;
+    int64_t raw = bits ? w->g.shard * (bits / 8) + (w->g.shard / kChunk) * 4 : w->g.shard / 2 + w->g.shard / 32;
     w->g.slot_bytes = (raw + 255) / 256 * 256;
     w->g.rs_off = int64_t(kHeaderBytes);
     w->g.ag_off = w->g.rs_off + w->g.slot_bytes * world;
     w->g.poll_limit = kPollLimit;
-    w->arena_bytes = size_t(w->g.ag_off + w->g.slot_bytes * world);
+    w->g.bits = bits;
+    w->g.mx_off = w->g.ag_off + w->g.slot_bytes * world;
+    w->arena_bytes = size_t(w->g.mx_off + (bits ? int64_t(world) * (padded / kChunk) * 4 : 0));
     w->mapped = false;
     w->epoch = 0;
     for (int i = 0; i < kMaxWorld; i++) w->opened[i] = false, w->peers.arena[i] = nullptr;
@@ -501,6 +721,46 @@ extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, f
     if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
     if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
     return ls_wire_finish(h, g, numel, stream);
+}
+
+// Integer wires: phase 0 publish maxima, 1 send, 2 reduce, 3 finish.
+extern "C" int ls_wire_int_phase(void *h, int phase, float *g, int64_t numel, float *res, float *ores, void *stream)
+{
+    Wire *w = as_wire(h);
+    if (!w || !w->mapped || !w->g.bits) return fail(LS_ESTATE, "not a ready integer wire");
+    if ((phase == 0 || phase == 1 || phase == 3) && (!g || numel <= 0 || numel > w->g.padded))
+        return fail(LS_EINVAL, "numel %lld does not fit the wire", (long long)numel);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool b8 = w->g.bits == 8;
+    switch (phase) {
+    case 0:
+        w->epoch++;
+        wire_int_max_kernel<<<grid_for(w->g.padded / 8), kThreads, 0, st>>>(g, numel, res, w->g, w->peers, w->epoch);
+        break;
+    case 1:
+        if (b8) wire_int_send_kernel<8><<<grid_for(w->g.padded / 8, 5), kThreads, 0, st>>>(g, numel, res, w->g, w->peers, w->epoch);
+        else wire_int_send_kernel<16><<<grid_for(w->g.padded / 8, 5), kThreads, 0, st>>>(g, numel, res, w->g, w->peers, w->epoch);
+        break;
+    case 2:
+        if (b8) wire_int_reduce_kernel<8><<<grid_for(w->g.shard / 8, 4), kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch);
+        else wire_int_reduce_kernel<16><<<grid_for(w->g.shard / 8, 4), kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch);
+        break;
+    case 3:
+        if (b8) wire_int_finish_kernel<8><<<grid_for((numel + 7) / 8), kThreads, 0, st>>>(g, numel, w->g, w->peers, w->epoch);
+        else wire_int_finish_kernel<16><<<grid_for((numel + 7) / 8), kThreads, 0, st>>>(g, numel, w->g, w->peers, w->epoch);
+        break;
+    default:
+        return fail(LS_EINVAL, "phase must be 0..3");
+    }
+    LS_LAUNCH_CHECK("wire_int_phase");
+    return LS_OK;
+}
+
+extern "C" int ls_wire_int_allreduce(void *h, float *g, int64_t numel, float *res, float *ores, void *stream)
+{
+    for (int phase = 0; phase < 4; phase++)
+        if (int rc = ls_wire_int_phase(h, phase, g, numel, res, ores, stream)) return rc;
+    return LS_OK;
 }
 
 extern "C" int ls_wire_set_poll_limit(void *h, int64_t polls)

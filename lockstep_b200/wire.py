@@ -98,11 +98,15 @@ class Wire:
         self._h = None
         self._kpadded = -(-numel // (world * _KUNIT)) * world * _KUNIT
 
-    # ---- MXFP4 transport -----------------------------------------------------
+    # ---- peer-store transport (MXFP4 and integer payloads) ---------------------
     def _handle(self, device):
         if self._h is None:
             h = ctypes.c_void_p()
-            check(lib().ls_wire_create(self.rank, self.world, self._kpadded, ctypes.byref(h)))
+            if self.fp4:
+                check(lib().ls_wire_create(self.rank, self.world, self._kpadded, ctypes.byref(h)))
+            else:
+                bits = 16 if self.dtype == torch.int16 else 8
+                check(lib().ls_wire_create_int(self.rank, self.world, self._kpadded, bits, ctypes.byref(h)))
             self._h = h
             if self.world > 1:
                 nb = int(lib().ls_wire_handle_bytes())
@@ -170,42 +174,18 @@ class Wire:
         return self._integer(g, reverse)
 
     def _integer(self, g, reverse):
-        """The reference's integer wires, same operations in the same order
-        (wire.py:104-138), on the GPU."""
-        world, lim = self.world, self.lim
-        v = torch.zeros(self.padded, device=g.device)
-        v[:self.n] = g
-        if self.ef:
-            if self.res is None:
-                self.res = torch.zeros_like(v)
-            v += self.res
-        c = v.view(-1, CHUNK)
-        m = c.abs().amax(1)
-        if world > 1:
-            dist.all_reduce(m, op=dist.ReduceOp.MAX)
-        s = torch.where(m > 0, lim / m, torch.ones_like(m))
-        q = torch.round(c * s[:, None]).clamp_(-lim, lim)
-        if self.ef:
-            self.res = v - (q / s[:, None]).view(-1)
-        own = c.shape[0] // world
-        parts = _all_to_all(q.to(self.dtype), world).view(world, own, CHUNK)
-        if reverse:
-            parts = parts.flip(0)
-        val = parts.to(torch.int32).sum(0).float()
-        lo = self.rank * own
-        val /= s[lo:lo + own, None]
-        if self.ef:
-            if self.ores is None:
-                self.ores = torch.zeros_like(val)
-            val += self.ores
-        m2 = val.abs().amax(1)
-        s2 = torch.where(m2 > 0, lim / m2, torch.ones_like(m2))
-        q2 = torch.round(val * s2[:, None]).clamp_(-lim, lim)
-        if self.ef:
-            self.ores = val - q2 / s2[:, None]
-        q2 = _all_gather(q2.to(self.dtype), world).view(-1, CHUNK)
-        s2 = _all_gather(s2, world)
-        return g.copy_((q2.float() / s2[:, None]).view(-1)[:self.n]).div_(world)
+        """The reference's integer wires (wire.py:104-138) as four kernels on the
+        peer-store transport: shared grid from the maximum over ranks, exact
+        int32 sum at the owner, owner grid, gather.  `reverse` has no effect:
+        integer sums do not depend on the order (tests/test_wire.py:58-59)."""
+        need_cuda(g)
+        assert g.dtype == torch.float32 and g.is_contiguous() and g.numel() == self.n
+        h = self._handle(g.device)
+        if self.ef and self.res is None:
+            self.res = torch.zeros(self._kpadded, device=g.device)
+            self.ores = torch.zeros(self._kpadded // self.world, device=g.device)
+        check(lib().ls_wire_int_allreduce(h, ptr(g), self.n, ptr(self.res), ptr(self.ores), stream()))
+        return g
 
 
 class LocalWireGroup:
@@ -214,13 +194,16 @@ class LocalWireGroup:
     stream, so no kernel ever waits for another.  Exercises exactly the kernels,
     addressing and flags of the multi-GPU path; used by the single-GPU tests."""
 
-    def __init__(self, world, numel, ef=False):
-        self.world, self.n, self.ef = world, numel, ef
+    def __init__(self, world, numel, ef=False, bits=0):
+        self.world, self.n, self.ef, self.bits = world, numel, ef, bits
         self.kpadded = -(-numel // (world * _KUNIT)) * world * _KUNIT
         self.handles = []
         for r in range(world):
             h = ctypes.c_void_p()
-            check(lib().ls_wire_create(r, world, self.kpadded, ctypes.byref(h)))
+            if bits:
+                check(lib().ls_wire_create_int(r, world, self.kpadded, bits, ctypes.byref(h)))
+            else:
+                check(lib().ls_wire_create(r, world, self.kpadded, ctypes.byref(h)))
             self.handles.append(h)
         arr = (ctypes.c_void_p * world)(*[h.value for h in self.handles])
         for h in self.handles:
@@ -231,6 +214,13 @@ class LocalWireGroup:
 
     def step(self, gs, reverse=False):
         L = lib()
+        if self.bits:
+            for phase in range(4):
+                for r, h in enumerate(self.handles):
+                    check(L.ls_wire_int_phase(h, phase, ptr(gs[r]), self.n, ptr(self.res[r]), ptr(self.ores[r]), stream()))
+            for h in self.handles:
+                check(L.ls_wire_status(h, None))
+            return gs
         for r, h in enumerate(self.handles):
             check(L.ls_wire_send(h, ptr(gs[r]), self.n, ptr(self.res[r]), stream()))
         for r, h in enumerate(self.handles):

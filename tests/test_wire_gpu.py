@@ -127,12 +127,35 @@ def test_error_feedback_delivers_small_gradients(wire):
 
 @pytest.mark.parametrize("method", ["int16", "int8", "int8ef"])
 def test_integer_wire_golden(wire, golden, method):
+    # outputs of the real reference Wire over three steps: bit for bit
     gd = golden(f"wire_{method}_w1")
     g = torch.from_numpy(gd["g"]).cuda()
     w = wire.Wire(method, g.numel())
     for s in range(3):
         out = w(g.clone() * (1 + 0.5 * s))
-        assert torch.allclose(out.cpu(), torch.from_numpy(gd["outs"][s]), rtol=1e-6, atol=1e-7), (method, s)
+        assert np.array_equal(out.cpu().numpy(), gd["outs"][s]), (method, s)
+    w.status()
+    w.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("bits,ef", [(16, False), (8, False), (8, True)])
+def test_integer_wire_ranks_vs_oracle(wire, world, bits, ef):
+    from oracle import ref_port
+    n = 5000 + 333 * world
+    lim = 2 ** (bits - 1) - 1
+    grp = wire.LocalWireGroup(world, n, ef, bits=bits)
+    padded = ref_port.padded_len(n, world)
+    res = [torch.zeros(padded) for _ in range(world)] if ef else None
+    ores = [torch.zeros(padded // 64 // world, 64) for _ in range(world)] if ef else None
+    for step in range(3):
+        grads = [torch.randn(n, generator=torch.Generator().manual_seed(17 * step + r)) * (1 + r) for r in range(world)]
+        want = ref_port.wire_int_step(grads, lim, res, ores)[0]
+        gs = [g.clone().cuda() for g in grads]
+        grp.step(gs)
+        for r in range(world):
+            assert torch.equal(gs[r].cpu(), want), (step, r)
+    grp.close()
 
 
 def test_ranks_come_from_torchrun_then_slurm(wire, monkeypatch):
