@@ -137,6 +137,8 @@ class Wire:
             check(lib().ls_wire_status(self._h, None))
 
     def close(self):
+        """Frees the receive arena.  Collective when world > 1: every rank must call
+        it (it waits for all ranks first, because peers store into this memory)."""
         if self._h is not None:
             if self.world > 1 and dist.is_initialized():
                 torch.cuda.synchronize()
@@ -145,8 +147,11 @@ class Wire:
             self._h = None
 
     def __del__(self):
+        # With peers, memory they may still store into is never freed behind their back:
+        # an unclosed multi-rank wire keeps its arena until the process ends.
         try:
-            self.close()
+            if self.world == 1:
+                self.close()
         except Exception:
             pass
 
