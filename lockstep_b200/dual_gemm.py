@@ -49,10 +49,11 @@ def dual_mxfp4_packed(a1_pk, a2_pk, bt_pk, a1_scale, a2_scale, b_scale, out_dtyp
     a1_pk, a2_pk, bt_pk = a1_pk.contiguous(), a2_pk.contiguous(), bt_pk.contiguous()
     sfa1, sfa2 = mxfp4_gemm._sf(a1_scale, M, K), mxfp4_gemm._sf(a2_scale, M, K)
     sfb = mxfp4_gemm._sf(b_scale, N, K)
-    c = torch.empty((2, M, N), device=a1_pk.device, dtype=out_dtype)
+    c1 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)      # two allocations: both 16-byte aligned
+    c2 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)
     check(lib().ls_mxfp4_gemm_dual(ptr(a1_pk), ptr(a2_pk), ptr(bt_pk), ptr(sfa1), ptr(sfa2), ptr(sfb),
-                                   ptr(c[0]), ptr(c[1]), _lib.dtype_code(out_dtype), M, N, K, stream()))
-    return c[0], c[1]
+                                   ptr(c1), ptr(c2), _lib.dtype_code(out_dtype), M, N, K, stream()))
+    return c1, c2
 
 
 def dual_mxfp4(x1, x2, w_pk, w_sf, out_dtype=torch.bfloat16):
