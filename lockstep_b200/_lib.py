@@ -86,6 +86,16 @@ def need_cuda(*tensors):
                                f"{t.device.type} tensor (there is no CPU fallback)")
 
 
+def aligned(t, n=16):
+    """t as a contiguous tensor whose storage pointer is a multiple of n bytes
+    (a contiguous slice of a larger tensor may start anywhere; the kernels read
+    and write vector words)."""
+    if t is None:
+        return None
+    t = t.contiguous()
+    return t.clone() if t.data_ptr() % n else t
+
+
 def ptr(t):
     return None if t is None else c_vp(t.data_ptr())
 

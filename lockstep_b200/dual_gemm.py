@@ -19,7 +19,7 @@ import math
 import torch
 
 from . import _lib, fp4, mxfp4_gemm
-from ._lib import check, lib, need_cuda, ptr, stream
+from ._lib import aligned, check, lib, need_cuda, ptr, stream
 
 CFG = dict(BLOCK_M=128, BLOCK_N=256, BLOCK_K=256, num_stages=4, num_warps=6)
 
@@ -46,7 +46,7 @@ def dual_mxfp4_packed(a1_pk, a2_pk, bt_pk, a1_scale, a2_scale, b_scale, out_dtyp
     N, Kh2 = bt_pk.shape
     K = Kh * 2
     assert a2_pk.shape == a1_pk.shape and Kh == Kh2 and K % 128 == 0
-    a1_pk, a2_pk, bt_pk = a1_pk.contiguous(), a2_pk.contiguous(), bt_pk.contiguous()
+    a1_pk, a2_pk, bt_pk = aligned(a1_pk), aligned(a2_pk), aligned(bt_pk)
     sfa1, sfa2 = mxfp4_gemm._sf(a1_scale, M, K), mxfp4_gemm._sf(a2_scale, M, K)
     sfb = mxfp4_gemm._sf(b_scale, N, K)
     c1 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)      # two allocations: both 16-byte aligned

@@ -12,7 +12,7 @@ Additions that the reference does not have are marked "(extension)".
 import torch
 
 from . import _lib
-from ._lib import check, lib, need_cuda, ptr, stream
+from ._lib import aligned, check, lib, need_cuda, ptr, stream
 
 # ---------------------------------------------------------------- E2M1 tables
 _E2M1_MAG = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
@@ -38,7 +38,7 @@ def _round_to_e2m1(q: torch.Tensor, rounding: str = "ref") -> torch.Tensor:
     between two grid points keeps the smaller magnitude; rounding="rne"
     (extension) sends it to the even code instead."""
     need_cuda(q)
-    q = q.float().contiguous()
+    q = aligned(q.float())
     codes = torch.empty(q.shape, dtype=torch.uint8, device=q.device)
     check(lib().ls_round_e2m1(ptr(q), q.numel(), _ROUNDING[rounding], ptr(codes), stream()))
     return codes
@@ -49,9 +49,7 @@ def _as_rows(x, block):
     assert K % block == 0, f"K={K} must be a multiple of block={block}"
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.float()
-    x = x.contiguous()
-    if x.data_ptr() % 32:                      # the kernels read 32-byte words
-        x = x.clone()
+    x = aligned(x, 32)                         # the kernels read 32-byte words
     return x, lead, K, (x.numel() // K if K else 0)
 
 
@@ -94,7 +92,7 @@ def quantize_mxfp4_packed_t(x: torch.Tensor, rounding: str = "ref", want_scale: 
     assert x.dim() == 2 and x.shape[0] % 128 == 0, "rows must be a multiple of 128"
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.float()
-    x = x.contiguous()
+    x = aligned(x)
     R, C = x.shape
     packed = torch.empty((C, R // 2), dtype=torch.uint8, device=x.device)
     sf = torch.empty(sf_bytes(C, R), dtype=torch.uint8, device=x.device)
@@ -113,7 +111,7 @@ def scales_to_sf(scale: torch.Tensor) -> torch.Tensor:
     """(extension) fp32 power-of-two scales [rows, K // 32] -> scale-factor
     layout bytes.  Raises if a scale is not a power of two."""
     need_cuda(scale)
-    scale = scale.float().contiguous()
+    scale = aligned(scale.float())
     rows, kb = scale.shape
     assert kb % 4 == 0, "K must be a multiple of 128"
     sf = torch.empty(sf_bytes(rows, kb * 32), dtype=torch.uint8, device=scale.device)
@@ -127,8 +125,8 @@ def dequantize_mxfp4(codes: torch.Tensor, scale: torch.Tensor, block: int = 32):
     need_cuda(codes, scale)
     *lead, K = codes.shape
     assert K % block == 0
-    codes = codes.contiguous()
-    scale = scale.float().contiguous()
+    codes = aligned(codes)
+    scale = aligned(scale.float())
     out = torch.empty((*lead, K), dtype=torch.float32, device=codes.device)
     rows = codes.numel() // K if K else 0
     check(lib().ls_dequantize_mxfp4(ptr(codes), 0, ptr(scale), None, rows, K, block, ptr(out), 0, stream()))
@@ -149,7 +147,7 @@ def pack_fp4(codes: torch.Tensor) -> torch.Tensor:
     """[..., K] codes -> [..., K // 2] bytes, even index in the low nibble (fp4.py:91-94)."""
     assert codes.shape[-1] % 2 == 0
     need_cuda(codes)
-    codes = codes.contiguous()
+    codes = aligned(codes)
     out = torch.empty((*codes.shape[:-1], codes.shape[-1] // 2), dtype=torch.uint8, device=codes.device)
     check(lib().ls_pack_fp4(ptr(codes), ptr(out), codes.numel(), stream()))
     return out
@@ -158,7 +156,7 @@ def pack_fp4(codes: torch.Tensor) -> torch.Tensor:
 def unpack_fp4(packed: torch.Tensor) -> torch.Tensor:
     """Inverse of pack_fp4 (fp4.py:97-99)."""
     need_cuda(packed)
-    packed = packed.contiguous()
+    packed = aligned(packed)
     out = torch.empty((*packed.shape[:-1], packed.shape[-1] * 2), dtype=torch.uint8, device=packed.device)
     check(lib().ls_unpack_fp4(ptr(packed), ptr(out), packed.numel(), stream()))
     return out

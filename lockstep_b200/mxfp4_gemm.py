@@ -14,7 +14,7 @@ or, to skip a conversion pass, as the uint8 scale-factor buffer that
 import torch
 
 from . import _lib, fp4
-from ._lib import check, lib, need_cuda, ptr, stream
+from ._lib import aligned, check, lib, need_cuda, ptr, stream
 
 # The reference exports its Triton launch config under this name
 # (mxfp4_gemm.py:23); here it documents the fixed tile shape of the kernel.
@@ -25,7 +25,7 @@ def _sf(scale, rows, K):
     """fp32 [rows, K//32] scales -> scale-factor bytes; uint8 buffers pass through."""
     if scale.dtype == torch.uint8:
         assert scale.numel() == fp4.sf_bytes(rows, K), "scale-factor buffer has the wrong size"
-        return scale.contiguous()
+        return aligned(scale)
     assert scale.shape == (rows, K // 32), f"scale shape {tuple(scale.shape)} != {(rows, K // 32)}"
     sf, _bad = fp4.scales_to_sf(scale)
     return sf
@@ -40,7 +40,7 @@ def mxfp4_gemm_packed(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloat16):
     N, Kh2 = bt_pk.shape
     K = Kh * 2
     assert Kh == Kh2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
-    a_pk, bt_pk = a_pk.contiguous(), bt_pk.contiguous()
+    a_pk, bt_pk = aligned(a_pk), aligned(bt_pk)
     sfa, sfb = _sf(a_scale, M, K), _sf(b_scale, N, K)
     c = torch.empty((M, N), device=a_pk.device, dtype=out_dtype)
     check(lib().ls_mxfp4_gemm(ptr(a_pk), ptr(bt_pk), ptr(sfa), ptr(sfb), ptr(c), _lib.dtype_code(out_dtype),
@@ -58,7 +58,7 @@ def mxfp4_gemm_packed_quant(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloa
     K = Kh * 2
     assert Kh == Kh2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
     assert N % 128 == 0, "N must be a multiple of 128 for the quantized output"
-    a_pk, bt_pk = a_pk.contiguous(), bt_pk.contiguous()
+    a_pk, bt_pk = aligned(a_pk), aligned(bt_pk)
     sfa, sfb = _sf(a_scale, M, K), _sf(b_scale, N, K)
     c = torch.empty((M, N), device=a_pk.device, dtype=out_dtype) if want_c else None
     q = torch.empty((M, N // 2), device=a_pk.device, dtype=torch.uint8)

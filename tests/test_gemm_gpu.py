@@ -185,6 +185,24 @@ def test_fused_mlp_chain(mods):
     _check(y, y_ref, "fused mlp")
 
 
+def test_unaligned_views_are_accepted(mods):
+    # contiguous slices that start at odd byte offsets: the host layer re-aligns them
+    fp4, mg, dg = mods
+    g = torch.Generator(device="cuda").manual_seed(1)
+    big = torch.randn(129 * 256 + 3, device="cuda", generator=g).bfloat16()
+    x = big[3:3 + 129 * 256].view(129, 256)                  # 6 bytes into the allocation
+    w = (torch.randn(72, 256, device="cuda", generator=g) * 0.02).bfloat16()
+    want = mg.mxfp4_gemm_packed(*sum((list(fp4.quantize_mxfp4_packed(t.clone())) for t in (x, w)), [])[::2],
+                                *sum((list(fp4.quantize_mxfp4_packed(t.clone())) for t in (x, w)), [])[1::2])
+    pa, sa = fp4.quantize_mxfp4_packed(x)
+    pw, sw = fp4.quantize_mxfp4_packed(w)
+    pa_off = torch.cat([torch.zeros(1, dtype=torch.uint8, device="cuda"), pa.flatten()])[1:].view_as(pa)
+    got = mg.mxfp4_gemm_packed(pa_off, pw, sa, sw)
+    assert torch.equal(got, want)
+    codes = fp4.unpack_fp4(pa_off)
+    assert torch.equal(fp4.pack_fp4(codes), pa)
+
+
 def test_fp8_entry(mods):
     fp4, mg, _ = mods
     M, N, K = 128, 256, 256
