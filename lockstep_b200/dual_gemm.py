@@ -36,11 +36,12 @@ def unpack_dual(acc: torch.Tensor, s: int):
     return acc - c2 * w, c2
 
 
-def dual_mxfp4_packed(a1_pk, a2_pk, bt_pk, a1_scale, a2_scale, b_scale, out_dtype=torch.bfloat16):
+def dual_mxfp4_packed(a1_pk, a2_pk, bt_pk, a1_scale, a2_scale, b_scale, out_dtype=torch.bfloat16, out=None):
     """Two activation batches against one MXFP4 weight in one launch.
 
     a1_pk, a2_pk [M, K//2] uint8; bt_pk [N, K//2] uint8; scales as in
-    mxfp4_gemm.mxfp4_gemm_packed.  Returns (C1, C2), each [M, N]."""
+    mxfp4_gemm.mxfp4_gemm_packed.  Returns (C1, C2), each [M, N]; `out` may
+    give the two output tensors (contiguous, 16-byte aligned)."""
     need_cuda(a1_pk, a2_pk, bt_pk)
     M, Kh = a1_pk.shape
     N, Kh2 = bt_pk.shape
@@ -49,8 +50,13 @@ def dual_mxfp4_packed(a1_pk, a2_pk, bt_pk, a1_scale, a2_scale, b_scale, out_dtyp
     a1_pk, a2_pk, bt_pk = aligned(a1_pk), aligned(a2_pk), aligned(bt_pk)
     sfa1, sfa2 = mxfp4_gemm._sf(a1_scale, M, K), mxfp4_gemm._sf(a2_scale, M, K)
     sfb = mxfp4_gemm._sf(b_scale, N, K)
-    c1 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)      # two allocations: both 16-byte aligned
-    c2 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)
+    if out is not None:
+        c1, c2 = out
+        assert c1.shape == (M, N) and c2.shape == (M, N) and c1.dtype == out_dtype and c2.dtype == out_dtype
+        assert c1.is_contiguous() and c2.is_contiguous()
+    else:
+        c1 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)  # two allocations: both 16-byte aligned
+        c2 = torch.empty((M, N), device=a1_pk.device, dtype=out_dtype)
     check(lib().ls_mxfp4_gemm_dual(ptr(a1_pk), ptr(a2_pk), ptr(bt_pk), ptr(sfa1), ptr(sfa2), ptr(sfb),
                                    ptr(c1), ptr(c2), _lib.dtype_code(out_dtype), M, N, K, stream()))
     return c1, c2
@@ -62,7 +68,11 @@ def dual_mxfp4(x1, x2, w_pk, w_sf, out_dtype=torch.bfloat16):
 
     When the two batches are the two halves of one allocation (as the
     reference's train_step.py:97-103 lays its microbatches out) and the batch
-    height is a multiple of 128, both are quantized by a single launch."""
+    height is a multiple of 128, both are quantized by a single launch.
+    (Splitting the rows to run the second half's quantizer under the first
+    half's GEMM was tried and lost: 236 us against 210 us per step at
+    2 x 4096 x 8192 -- two shorter persistent GEMM launches cost more than the
+    overlap hides.)"""
     M, K = x1.shape
     adjacent = (x1.is_contiguous() and x2.is_contiguous() and x1.dtype == x2.dtype and x1.shape == x2.shape
                 and M % 128 == 0 and x2.data_ptr() == x1.data_ptr() + x1.numel() * x1.element_size()
