@@ -58,26 +58,6 @@ def init():
     return rank, world, device
 
 
-def _as_bytes(x):
-    return x.view(torch.uint8) if x.dtype == torch.int16 else x
-
-
-def _all_to_all(x, world):
-    if world == 1:
-        return x
-    out = torch.empty_like(x)
-    dist.all_to_all_single(_as_bytes(out), _as_bytes(x))
-    return out
-
-
-def _all_gather(x, world):
-    if world == 1:
-        return x
-    out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(_as_bytes(out), _as_bytes(x))
-    return out
-
-
 class Wire:
     """Averages a flat fp32 gradient across ranks, in place, with one method."""
 
@@ -252,49 +232,51 @@ class LocalWireGroup:
 
 
 def bench(out, numel, iters):
-    """Time and error of each wire on one gradient-sized buffer (wire.py:141-185)."""
+    """Microbenchmark in the manner of wire.py:141-185: every wire on one
+    gradient-sized buffer, median time over `iters` calls and relative error
+    against an fp64 all-reduce; rank 0 prints the rows and writes <out>/wire.csv."""
     import csv
     import statistics
     import time
     from pathlib import Path
     rank, world, dev = init()
-    gen = torch.Generator(device=dev).manual_seed(1)
-    signal = torch.randn(numel, device=dev, generator=gen)
-    gen.manual_seed(100 + rank)
-    g0 = signal / world + 3 * torch.randn(numel, device=dev, generator=gen) / world ** 0.5
-    ref = g0.double()
+    common = torch.randn(numel, device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    noise = torch.randn(numel, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank))
+    grad = common / world + 3 * noise / world ** 0.5            # shared signal + per-rank noise
+    exact = grad.double()
     if world > 1:
-        dist.all_reduce(ref)
-    ref /= world
-    rows = []
-    for method in ("fp32", "bf16", "int16", "int8", "mxfp4"):
-        t0 = time.perf_counter()
+        dist.all_reduce(exact)
+    exact /= world
+    table = []
+    for method in ("fp32", "bf16", "int16", "int8", "int8ef", "mxfp4", "mxfp4ef"):
+        began = time.perf_counter()
         w = Wire(method, numel, world, rank)
-        res = w(g0.clone())
-        times = []
+        first = w(grad.clone())
+        err = ((first.double() - exact).norm() / exact.norm()).item()
+        samples = []
         for _ in range(iters):
-            x = g0.clone()
+            buf = grad.clone()
             if world > 1:
                 dist.barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            w(x)
-            b.record()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            w(buf)
+            t1.record()
             torch.cuda.synchronize()
-            times.append(a.elapsed_time(b))
-        ms = statistics.median(times)
-        rows.append(dict(method=method, gpus=world, B_per_el=round(w.bytes_per_el, 4), ms=round(ms, 3),
-                         grad_GBps=round(numel * 4 / ms / 1e6, 1),
-                         rel_err=f"{((res.double() - ref).norm() / ref.norm()).item():.3e}",
-                         seconds=round(time.perf_counter() - t0, 1)))
+            samples.append(t0.elapsed_time(t1))
+        w.status()
         w.close()
+        ms = statistics.median(samples)
+        table.append({"method": method, "gpus": world, "B_per_el": round(w.bytes_per_el, 4), "ms": round(ms, 3),
+                      "grad_GBps": round(numel * 4 / ms / 1e6, 1), "rel_err": f"{err:.3e}",
+                      "seconds": round(time.perf_counter() - began, 1)})
         if rank == 0:
-            print(rows[-1], flush=True)
+            print(table[-1], flush=True)
     if rank == 0:
         Path(out).mkdir(parents=True, exist_ok=True)
         with open(Path(out) / "wire.csv", "w", newline="") as f:
-            wr = csv.DictWriter(f, fieldnames=list(rows[0]))
+            wr = csv.DictWriter(f, fieldnames=list(table[0]))
             wr.writeheader()
-            wr.writerows(rows)
+            wr.writerows(table)
     if world > 1:
         dist.destroy_process_group()
