@@ -22,7 +22,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/lockstep")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF))
 import fp4            # noqa: E402  (the reference's)
 import fp4_linear     # noqa: E402
