@@ -200,3 +200,15 @@ def test_dual_slot_split():
         c2 = torch.tensor([-144.0 * k, 144.0 * k, -7.0], dtype=torch.float64)
         g1, g2 = ref_port.unpack_dual(c1 + c2 * 2.0 ** s, s)
         assert torch.equal(g1, c1) and torch.equal(g2, c2)
+
+
+@pytest.mark.parametrize("world", [3, 5, 6, 7])
+def test_c_oracle_equals_torch_port_for_odd_worlds(world):
+    """The final division by the world size: torch divides a tensor by a scalar as
+    x * (1 / world) (wire.py:138 `.div_(world)`); not exact unless world is a power
+    of two, so the C restatement must do the same."""
+    rng = np.random.default_rng(world)
+    gs = [(rng.standard_t(3, 3000) * 1e-3).astype(np.float32) for _ in range(world)]
+    out_c, _, _ = cref.wire_step(gs)
+    out_t = ref_port.wire_mxfp4_step([torch.from_numpy(g) for g in gs])[0].numpy()
+    assert np.array_equal(out_c, out_t)
