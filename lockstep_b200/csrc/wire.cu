@@ -296,8 +296,7 @@ wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t
 // One thread decodes 4 values (two packed bytes) per step and writes one 16-byte
 // word, so every load and store of a warp is one contiguous segment.  POW2: the
 // world size is a power of two, so dividing by it is an exact multiplication that
-// folds into the block scale.  Otherwise the value is multiplied by fp32(1 / world),
-// which is how torch divides a tensor by a scalar (wire.py:138 `.div_(world)`).
+// folds into the block scale.  Otherwise an IEEE division (wire.py:138 `.div_(world)`).
 template <bool POW2>
 __global__ void __launch_bounds__(kThreads)
 wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
@@ -337,7 +336,7 @@ wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, 
                 float t[4];
                 e2m1x4_values(pk[u], t);
 #pragma unroll
-                for (int i = 0; i < 4; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fmul_rn(__fmul_rn(t[i], sc), rw);
+                for (int i = 0; i < 4; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
                 const int64_t i0 = int64_t(q) * 4;
                 if (vec && i0 + 4 <= ns) {
                     *reinterpret_cast<float4 *>(gs + i0) = make_float4(t[0], t[1], t[2], t[3]);
@@ -538,7 +537,7 @@ wire_int_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers pee
     const uint32_t groups = uint32_t((n + 7) / 8), stride = gridDim.x * kThreads;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);
     const int64_t payload = geo.shard * (BITS / 8);
-    const float rw = 1.0f / float(geo.world);
+    const float w = float(geo.world);
     for (uint32_t g8 = blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
         const uint32_t o = g8 / g_per_shard, in_shard = g8 - o * g_per_shard;
         const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
@@ -547,7 +546,7 @@ wire_int_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers pee
         const float s2 = reinterpret_cast<const float *>(slot + payload)[in_shard / 8];
         float v[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = __fmul_rn(__fdiv_rn(float(q[i]), s2), rw);     // torch divides by a scalar as x * (1 / w)
+        for (int i = 0; i < 8; i++) v[i] = __fdiv_rn(__fdiv_rn(float(q[i]), s2), w);
         store8(g, int64_t(g8) * 8, n, v);
     }
 }

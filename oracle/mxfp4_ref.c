@@ -214,14 +214,14 @@ void ref_wire_owner(const uint8_t *const *slots_p, const uint8_t *const *slots_e
 /* Receiver: g[:n] = decode(all shards) / world. */
 void ref_wire_decode(const uint8_t *packed, const uint8_t *e8m0, int64_t n, int world, float *g)
 {
-    /* wire.py:138 `.div_(world)`: torch divides a tensor by a scalar as x * (1 / world) */
-    float rw = 1.0f / (float)world;
+    /* wire.py:138 `.div_(world)`: an IEEE division (what torch's CPU kernel does) */
+    float w = (float)world;
 #pragma omp parallel for schedule(static)
     for (int64_t k = 0; k < n; k++) {
         uint8_t byte = packed[k / 2];
         uint8_t c = (k & 1) ? byte >> 4 : byte & 0x0F;
         volatile float d = code_value(c) * e8m0_value(e8m0[k / 32]);
-        g[k] = d * rw;
+        g[k] = d / w;
     }
 }
 
