@@ -201,6 +201,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--e2e-chunks", type=int, default=2, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--no-wire", action="store_true", help="skip the all-reduce leg")
     ap.add_argument("--no-train", action="store_true", help="skip the FP4-linear training-step leg")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
@@ -302,7 +303,7 @@ def main():
     hx = xs.cpu().pin_memory()
     hc = torch.empty((2, m, N), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
-    chunks = 8 if m % (8 * 128) == 0 else 1
+    chunks = args.e2e_chunks if m % (args.e2e_chunks * 128) == 0 else 1
     cm = m // chunks
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     dx = [torch.empty((2, cm, K), dtype=torch.bfloat16, device=dev) for _ in range(2)]

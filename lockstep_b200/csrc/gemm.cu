@@ -16,6 +16,7 @@
 // epilogue drains the shared columns first and only then lets the next tile's
 // MMAs start.
 #include <cuda.h>
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -103,35 +104,79 @@ __device__ __forceinline__ void quant_chunk(const GemmParams &p, int b, int row,
     p.q_sf[b][sf_offset(uint32_t(row), uint32_t(col0 / 32), uint32_t(p.N / 128))] = uint8_t(e8);
 }
 
-__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bool bf16, int row, int col0,
+// 4 x 4 transpose of 16-byte items inside each group of four lanes: afterwards item k of
+// lane 4g + j is what lane 4g + k held as item j.
+__device__ __forceinline__ void transpose4(uint4 (&it)[4], int lane)
+{
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
+        const bool up = (lane >> b) & 1;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (i & (1 << b)) continue;
+            const int hi = i | (1 << b);
+            uint4 send = up ? it[i] : it[hi], recv;
+            recv.x = __shfl_xor_sync(0xFFFFFFFFu, send.x, 1 << b);
+            recv.y = __shfl_xor_sync(0xFFFFFFFFu, send.y, 1 << b);
+            recv.z = __shfl_xor_sync(0xFFFFFFFFu, send.z, 1 << b);
+            recv.w = __shfl_xor_sync(0xFFFFFFFFu, send.w, 1 << b);
+            if (up) it[i] = recv;
+            else it[hi] = recv;
+        }
+    }
+}
+
+// Stores one accumulator chunk: lane l of the warp holds the 32 consecutive outputs
+// (columns col0 .. col0 + 31) of row row0 + l.  Called by the whole warp.  Storing each
+// lane's own row would touch 32 rows per instruction (one 16-byte piece each); the
+// pieces are transposed inside groups of four lanes first, so that four adjacent lanes
+// write 64 contiguous bytes of one row and an instruction touches 8 rows.
+__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bool bf16, int row0, int lane, int col0,
                                             const uint32_t (&r)[32])
 {
-    if (row >= p.M || col0 >= p.N) return;
+    if (row0 >= p.M || col0 >= p.N) return;                       // uniform over the warp
+    const int row = row0 + lane;
+    const int trow = row0 + (lane & ~3), tq = lane & 3;            // first row / piece of this lane after a transpose
     if (bf16) {
-        __nv_bfloat16 *dst = static_cast<__nv_bfloat16 *>(cbase) + int64_t(row) * p.N + col0;
+        __nv_bfloat16 *base = static_cast<__nv_bfloat16 *>(cbase);
         if (col0 + 32 <= p.N && (p.N & 7) == 0) {
+            uint4 it[4];
 #pragma unroll
             for (int v = 0; v < 4; v++) {
-                uint4 o;
-                uint32_t *ow = &o.x;
+                uint32_t *ow = &it[v].x;
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2 * j]),
                                                              __uint_as_float(r[8 * v + 2 * j + 1]));
                     ow[j] = *reinterpret_cast<uint32_t *>(&h);
                 }
-                reinterpret_cast<uint4 *>(dst)[v] = o;
             }
-        } else {
+            transpose4(it, lane);
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (trow + k < p.M)
+                    *reinterpret_cast<uint4 *>(base + int64_t(trow + k) * p.N + col0 + 8 * tq) = it[k];
+        } else if (row < p.M) {
+            __nv_bfloat16 *dst = base + int64_t(row) * p.N + col0;
             for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
         }
     } else {
-        float *dst = static_cast<float *>(cbase) + int64_t(row) * p.N + col0;
+        float *base = static_cast<float *>(cbase);
         if (col0 + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
-            for (int v = 0; v < 8; v++)
-                reinterpret_cast<uint4 *>(dst)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-        } else {
+            for (int h = 0; h < 2; h++) {
+                uint4 it[4];
+#pragma unroll
+                for (int v = 0; v < 4; v++)
+                    it[v] = make_uint4(r[16 * h + 4 * v], r[16 * h + 4 * v + 1], r[16 * h + 4 * v + 2], r[16 * h + 4 * v + 3]);
+                transpose4(it, lane);
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    if (trow + k < p.M)
+                        *reinterpret_cast<uint4 *>(base + int64_t(trow + k) * p.N + col0 + 16 * h + 4 * tq) = it[k];
+            }
+        } else if (row < p.M) {
+            float *dst = base + int64_t(row) * p.N + col0;
             for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __uint_as_float(r[j]);
         }
     }
@@ -304,18 +349,26 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             constexpr int CH = BN / 32;
             // first chunk: the columns shared with the other accumulator
             const int first = (C::OVL && !(lt & 1)) ? CH - 1 : 0;
-            for (int i = 0; i < CH; i++) {
-                const int c = (first + i) % CH;
-                uint32_t r[32];
-                ptx::tmem_ld32(acc + 32 * c, r);
-                ptx::tmem_ld_wait();
-                if (i == 0) {
+            // two register sets: the load of the next chunk is in flight while this one is stored
+            auto emit = [&](int c, const uint32_t (&r)[32]) {
+                if (p.store_c || p.splits > 1) store_chunk(p, dst, dst_bf16, row - lane, lane, nt * BN + 32 * c, r);
+                if (p.q_packed[b]) quant_chunk(p, b, row, nt * BN + 32 * c, r);
+            };
+            uint32_t ra[32], rb[32];
+            ptx::tmem_ld32(acc + 32 * first, ra);
+#pragma unroll
+            for (int i = 0; i < CH; i += 2) {
+                ptx::tmem_ld_wait(ra);
+                ptx::tmem_ld32(acc + 32 * ((first + i + 1) % CH), rb);
+                if (i == 0) {                               // first chunk drained: the next tile may start
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_free_bar);
                 }
-                if (p.store_c || p.splits > 1) store_chunk(p, dst, dst_bf16, row, nt * BN + 32 * c, r);
-                if (p.q_packed[b]) quant_chunk(p, b, row, nt * BN + 32 * c, r);
+                emit((first + i) % CH, ra);
+                ptx::tmem_ld_wait(rb);
+                if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * ((first + i + 2) % CH), ra);
+                emit((first + i + 1) % CH, rb);
             }
         }
     }
@@ -431,9 +484,11 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + C::BN - 1) / C::BN;
     const int mp_tiles = p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2;   // row-tile pairs
-    const int total = mp_tiles * n_tiles;
+    const int total = mp_tiles * n_tiles * p.splits;       // work items: (pair tile, K split)
     const int k_tiles = (p.K / 2 + BKB - 1) / BKB;
     const int k_atoms = p.K / 128;
+    auto kt_begin = [&](int t) { return (t % p.splits) * p.kt_per_split; };
+    auto kt_end = [&](int t) { return min(k_tiles, (t % p.splits + 1) * p.kt_per_split); };
     // this CTA's batch and row tile inside pair-tile index mp
     const int my_batch = p.nbatch == 2 ? int(cta) : 0;
     auto my_mtile = [&](int mp) { return p.nbatch == 2 ? mp : 2 * mp + int(cta); };
@@ -475,9 +530,10 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             uint32_t ph = 0;
             bool ok = true;
             for (int t = pair; t < total && ok; t += npairs) {
-                const int mp = t % mp_tiles, nt = t / mp_tiles;
+                const int tt = t / p.splits;
+                const int mp = tt % mp_tiles, nt = tt / mp_tiles;
                 const int mt = my_mtile(mp);
-                for (int kt = 0; kt < k_tiles; kt++) {
+                for (int kt = kt_begin(t), kte = kt_end(t); kt < kte; kt++) {
                     if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag))) break;
                     const uint32_t st = smem_base + s * C::STAGE_BYTES;
                     const uint32_t bar = ptx::map_to_cta(full_bar(s), 0);
@@ -511,17 +567,18 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                 if (lt > 0 && !(ok = ptx::mbar_wait(acc_free_bar, (lt - 1) & 1, abort_flag))) break;
                 ptx::tc_fence_after();
                 const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0);
-                for (int kt = 0; kt < k_tiles; kt++) {
+                const int kt0 = kt_begin(t), kt1 = kt_end(t);
+                for (int kt = kt0; kt < kt1; kt++) {
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
                     ptx::tc_fence_after();
                     const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);
                     const uint32_t sfa_t = tmem_base + C::SF_COL, sfb_t = sfa_t + 8;
                     if (2 * kt + 2 <= k_atoms)
                         issue_stage<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                             sfb_t, idesc, kt == 0, false, false);
+                                             sfb_t, idesc, kt == kt0, false, false);
                     else
                         issue_stage<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                             sfb_t, idesc, kt == 0, false, false);
+                                             sfb_t, idesc, kt == kt0, false, false);
                     ptx::tc_commit_pair(empty_bar(s), 3);      // frees the stage in both CTAs
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
@@ -534,8 +591,13 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
         int lt = 0;
         bool ok = true;
         for (int t = pair; t < total && ok; t += npairs, lt++) {
-            const int mp = t % mp_tiles, nt = t / mp_tiles;
+            const int ks = t % p.splits, tt = t / p.splits;
+            const int mp = tt % mp_tiles, nt = tt / mp_tiles;
             const int mt = my_mtile(mp);
+            // split-K: fp32 partial sums into the scratch slab of (batch, split)
+            void *dst = p.splits > 1 ? static_cast<void *>(p.partial + int64_t(my_batch * p.splits + ks) * p.M * p.N)
+                                     : p.c[my_batch];
+            const bool dst_bf16 = p.splits > 1 ? false : bool(p.out_bf16);
             if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
@@ -543,18 +605,27 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             constexpr int CH = C::BN / 32;
             constexpr int SHARED = C::OVL / 32;             // chunks shared with the other accumulator
             const int first = !(lt & 1) ? CH - SHARED : 0;
-            for (int i = 0; i < CH; i++) {
-                const int c = (first + i) % CH;
-                uint32_t r[32];
-                ptx::tmem_ld32(acc + 32 * c, r);
-                ptx::tmem_ld_wait();
-                if (i == SHARED - 1) {                      // shared columns drained: next tile may start
+            static_assert(SHARED == 1 && CH % 2 == 0, "the drain order below assumes one shared chunk");
+            // two register sets: the load of the next chunk is in flight while this one is stored
+            auto emit = [&](int c, const uint32_t (&r)[32]) {
+                if (p.store_c || p.splits > 1) store_chunk(p, dst, dst_bf16, row - lane, lane, nt * C::BN + 32 * c, r);
+                if (p.q_packed[my_batch]) quant_chunk(p, my_batch, row, nt * C::BN + 32 * c, r);
+            };
+            uint32_t ra[32], rb[32];
+            ptx::tmem_ld32(acc + 32 * first, ra);
+#pragma unroll
+            for (int i = 0; i < CH; i += 2) {
+                ptx::tmem_ld_wait(ra);
+                ptx::tmem_ld32(acc + 32 * ((first + i + 1) % CH), rb);
+                if (i == 0) {                               // shared columns drained: the next tile may start
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
                 }
-                if (p.store_c) store_chunk(p, p.c[my_batch], p.out_bf16, row, nt * C::BN + 32 * c, r);
-                if (p.q_packed[my_batch]) quant_chunk(p, my_batch, row, nt * C::BN + 32 * c, r);
+                emit((first + i) % CH, ra);
+                ptx::tmem_ld_wait(rb);
+                if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * ((first + i + 2) % CH), ra);
+                emit((first + i + 1) % CH, rb);
             }
         }
     }
@@ -672,7 +743,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
         resident_pairs[dev] = n;
     }
     int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + C::BN - 1) / C::BN;
-    int pairs = (p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2) * n_tiles;
+    int pairs = (p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2) * n_tiles * p.splits;
     int max_pairs = resident_pairs[dev];
     int grid = 2 * (pairs < max_pairs ? pairs : max_pairs);
     mxfp4_gemm_pair_kernel<<<grid, kGemmThreads, C::SMEM, st>>>(ta0, ta1, tb, tsa0, tsa1, tsb, p);
@@ -681,6 +752,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
 }
 
 int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
+int g_gemm_splits = 0;           // 0 = choose by shape, n = split K n ways where splitting is allowed
 
 // Per-device scratch for split-K partial sums; grows on demand and is kept.
 float *splitk_scratch(size_t bytes)
@@ -781,23 +853,39 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
         p.q_packed[b] = fused ? qe->packed[nbatch == 2 ? b : 0] : nullptr;
         p.q_sf[b] = fused ? qe->sf[nbatch == 2 ? b : 0] : nullptr;
     }
-    if (pair) return launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream));
-    // Few tiles and a long K (decode-like shapes): split K over otherwise idle SMs.  Not on the
-    // allocation-free path (caller-supplied error word), which must not touch an allocator.
-    const int tiles = int(((M + BM - 1) / BM) * ((N + bn - 1) / bn)) * nbatch;
+    // Few output tiles and a long K (decode-like shapes, weight gradients): split K over
+    // otherwise idle SMs into fp32 partial slabs that a second kernel sums in ascending
+    // order.  Not on the allocation-free path (caller-supplied error word), which must
+    // not touch an allocator, and not with the quantizing epilogue.
     const int k_tiles = p.kt_per_split;
-    if (!caller_err && !fused && M <= 32 && tiles * 2 <= sm_count() && k_tiles >= 4) {      // partial traffic grows with M
-        int s = sm_count() / tiles;
-        if (s > k_tiles / 2) s = k_tiles / 2;
-        if (s > 16) s = 16;
-        if (s > 1) {
-            p.kt_per_split = (k_tiles + s - 1) / s;
-            p.splits = (k_tiles + p.kt_per_split - 1) / p.kt_per_split;
-            p.partial = splitk_scratch(size_t(p.splits) * nbatch * M * N * sizeof(float));
-            if (!p.partial) return fail(LS_ECUDA, "could not allocate split-K scratch");
+    const int tiles = pair ? int((nbatch == 2 ? (M + BM - 1) / BM : (M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn))
+                           : int(((M + BM - 1) / BM) * ((N + bn - 1) / bn)) * nbatch;
+    const int slots = pair ? sm_count() / 2 : sm_count();       // work items that run at once
+    int s = 1;
+    if (!caller_err && !fused) {
+        if (g_gemm_splits > 0) {
+            s = g_gemm_splits;
+        } else if (pair) {
+            // at least 8 k-tiles (K = 2048) per split keep the pipeline fill small against the work
+            if (tiles * 2 <= slots && k_tiles >= 16) s = std::min(slots / tiles, k_tiles / 8);
+        } else if (M <= 32 && tiles * 2 <= slots && k_tiles >= 4) {                 // partial traffic grows with M
+            s = std::min(slots / tiles, k_tiles / 2);
         }
+        s = std::max(1, std::min(std::min(s, 16), k_tiles));
     }
-    if (int rc = launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
+    if (s > 1) {
+        p.kt_per_split = (k_tiles + s - 1) / s;
+        p.splits = (k_tiles + p.kt_per_split - 1) / p.kt_per_split;
+    }
+    if (p.splits > 1) {
+        p.partial = splitk_scratch(size_t(p.splits) * nbatch * M * N * sizeof(float));
+        if (!p.partial) return fail(LS_ECUDA, "could not allocate split-K scratch");
+    }
+    if (pair) {
+        if (int rc = launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
+    } else {
+        if (int rc = launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
+    }
     if (p.splits > 1) {
         for (int b = 0; b < nbatch; b++) {
             const int64_t mn = M * N;
@@ -844,6 +932,13 @@ extern "C" int ls_gemm_set_variant(int variant)
 {
     if (variant < 0 || variant > 2) return fail(LS_EINVAL, "variant must be 0, 1 or 2");
     g_gemm_variant = variant;
+    return LS_OK;
+}
+
+extern "C" int ls_gemm_set_splits(int splits)
+{
+    if (splits < 0 || splits > 16) return fail(LS_EINVAL, "splits must be 0 (choose by shape) or 1..16");
+    g_gemm_splits = splits;
     return LS_OK;
 }
 

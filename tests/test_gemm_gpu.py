@@ -134,6 +134,40 @@ def test_skinny_shapes_split_k(mods, M, N, K):
     assert torch.equal(mg.mxfp4_gemm_packed(pa, pw, sfa, sfw), mg.mxfp4_gemm_packed(pa, pw, sfa, sfw))   # deterministic
 
 
+@pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2),
+                                                  (2, 300, 520, 4096, 5), (2, 1024, 1024, 16384, 0)])
+def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
+    # power-of-two scales on an integer grid: every partial sum is exact, so a split
+    # product must equal the unsplit one bit for bit, on both kernels and both batches
+    fp4, mg, dg = mods
+    from lockstep_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(K + splits)
+    ac = torch.randint(0, 16, (2, M, K), dtype=torch.uint8, device="cuda", generator=g)
+    bc = torch.randint(0, 16, (N, K), dtype=torch.uint8, device="cuda", generator=g)
+    sa = torch.exp2(torch.randint(-2, 3, (2, M, K // 32), device="cuda", generator=g).float())
+    sb = torch.exp2(torch.randint(-2, 3, (N, K // 32), device="cuda", generator=g).float())
+    pa, pb = fp4.pack_fp4(ac), fp4.pack_fp4(bc)
+    want = [fp4.dequantize_mxfp4(ac[i], sa[i]).double() @ fp4.dequantize_mxfp4(bc, sb).double().t() for i in range(2)]
+    try:
+        assert L.ls_gemm_set_variant(variant) == 0 and L.ls_gemm_set_splits(splits) == 0
+        c = mg.mxfp4_gemm_packed(pa[0], pb, sa[0], sb, out_dtype=torch.float32)
+        guard = torch.full((4, N), 777.0, device="cuda")
+        c1, c2 = dg.dual_mxfp4_packed(pa[0], pa[1], pb, sa[0], sa[1], sb, out_dtype=torch.float32)
+        cb = mg.mxfp4_gemm_packed(pa[1], pb, sa[1], sb)
+        mg.gemm_status()
+    finally:
+        L.ls_gemm_set_variant(0), L.ls_gemm_set_splits(0)
+    if K <= 4096:
+        assert torch.equal(c.double(), want[0]) and torch.equal(c1.double(), want[0]) and torch.equal(c2.double(), want[1])
+        assert torch.equal(cb, want[1].float().bfloat16())
+    else:       # sums may pass 2^24 units: fp32 rounding of the partial sums is allowed
+        for got, ref in ((c, want[0]), (c1, want[0]), (c2, want[1]), (cb, want[1])):
+            _check(got, ref.float().to(got.dtype), f"{M}x{N}x{K} splits {splits}")
+    assert (guard == 777.0).all()
+    assert L.ls_gemm_set_splits(17) < 0 and L.ls_gemm_set_splits(-1) < 0
+
+
 @pytest.mark.parametrize("M,N,K,dt", [(256, 512, 384, torch.bfloat16), (130, 256, 256, torch.bfloat16),
                                       (4096, 1024, 1024, torch.bfloat16), (64, 128, 128, torch.float32)])
 def test_quantizing_epilogue_equals_separate_pass(mods, M, N, K, dt):
