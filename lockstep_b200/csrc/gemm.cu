@@ -68,7 +68,27 @@ struct GemmParams {
 // reads it.  The values quantized are the ones a separate pass would see: the
 // accumulator rounded to the output type, the activation applied in fp32 and rounded
 // to the output type again.
-__device__ __forceinline__ void quant_chunk(const GemmParams &p, int b, int row, int col0, const uint32_t (&r)[32])
+// What an epilogue thread needs from the kernel parameters, read once into registers.
+// (Indexing the parameter arrays with a run-time batch index makes the compiler keep a
+// copy of the whole parameter struct in local memory and read it back on every use.)
+struct Epi {
+    int M, N;
+    bool out_bf16, store_c;
+    int act;
+    uint8_t *q_packed, *q_sf;      // of this thread's batch
+};
+__device__ __forceinline__ Epi make_epi(const GemmParams &p, int b)
+{
+    Epi e;
+    e.M = p.M, e.N = p.N;
+    e.out_bf16 = p.out_bf16 != 0, e.store_c = p.store_c != 0;
+    e.act = p.act;
+    e.q_packed = b ? p.q_packed[1] : p.q_packed[0];
+    e.q_sf = b ? p.q_sf[1] : p.q_sf[0];
+    return e;
+}
+
+__device__ __forceinline__ void quant_chunk(const Epi &p, int row, int col0, const uint32_t (&r)[32])
 {
     if (row >= p.M || col0 >= p.N) return;
     float v[32];
@@ -100,8 +120,8 @@ __device__ __forceinline__ void quant_chunk(const GemmParams &p, int b, int row,
             for (int i = 0; i < 8; i++) pk[h] |= e2m1_code<false>(t[i]) << (4 * i);
         }
     }
-    *reinterpret_cast<uint4 *>(p.q_packed[b] + int64_t(row) * (p.N / 2) + col0 / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-    p.q_sf[b][sf_offset(uint32_t(row), uint32_t(col0 / 32), uint32_t(p.N / 128))] = uint8_t(e8);
+    *reinterpret_cast<uint4 *>(p.q_packed + int64_t(row) * (p.N / 2) + col0 / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    p.q_sf[sf_offset(uint32_t(row), uint32_t(col0 / 32), uint32_t(p.N / 128))] = uint8_t(e8);
 }
 
 // 4 x 4 transpose of 16-byte items inside each group of four lanes: afterwards item k of
@@ -131,7 +151,7 @@ __device__ __forceinline__ void transpose4(uint4 (&it)[4], int lane)
 // lane's own row would touch 32 rows per instruction (one 16-byte piece each); the
 // pieces are transposed inside groups of four lanes first, so that four adjacent lanes
 // write 64 contiguous bytes of one row and an instruction touches 8 rows.
-__device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bool bf16, int row0, int lane, int col0,
+__device__ __forceinline__ void store_chunk(const Epi &p, void *cbase, bool bf16, int row0, int lane, int col0,
                                             const uint32_t (&r)[32])
 {
     if (row0 >= p.M || col0 >= p.N) return;                       // uniform over the warp
@@ -158,7 +178,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bo
                     *reinterpret_cast<uint4 *>(base + int64_t(trow + k) * p.N + col0 + 8 * tq) = it[k];
         } else if (row < p.M) {
             __nv_bfloat16 *dst = base + int64_t(row) * p.N + col0;
-            for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+#pragma unroll                                     // unrolled with predicates: r[] must stay in registers
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
         }
     } else {
         float *base = static_cast<float *>(cbase);
@@ -177,7 +199,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams &p, void *cbase, bo
             }
         } else if (row < p.M) {
             float *dst = base + int64_t(row) * p.N + col0;
-            for (int j = 0; j < 32 && col0 + j < p.N; j++) dst[j] = __uint_as_float(r[j]);
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+                if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
         }
     }
 }
@@ -274,7 +298,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 const int b = tt % p.nbatch, rest = tt / p.nbatch;
                 const int mt = rest % m_tiles, nt = rest / m_tiles;
                 const CUtensorMap *tma = b ? &tm_a1 : &tm_a0;
-                const uint8_t *sfa = p.sfa[b] + int64_t(mt) * k_atoms * 512;
+                const uint8_t *sfa = (b ? p.sfa[1] : p.sfa[0]) + int64_t(mt) * k_atoms * 512;
                 for (int kt = kt_begin(ks); kt < kt_end(ks); kt++, it++) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
@@ -333,6 +357,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     } else {
         // ------------------------------------------------------------ epilogue
         const int q = warp & 3;                        // tensor-memory lane quarter of this warp
+        const int splits = p.splits;
         int lt = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
@@ -340,8 +365,10 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             const int b = tt % p.nbatch, rest = tt / p.nbatch;
             const int mt = rest % m_tiles, nt = rest / m_tiles;
             // split-K: fp32 partial sums into the scratch slab of (batch, split)
-            void *dst = p.splits > 1 ? static_cast<void *>(p.partial + int64_t(b * p.splits + ks) * p.M * p.N) : p.c[b];
-            const bool dst_bf16 = p.splits > 1 ? false : bool(p.out_bf16);
+            const Epi ep = make_epi(p, b);
+            void *dst = p.splits > 1 ? static_cast<void *>(p.partial + int64_t(b * p.splits + ks) * p.M * p.N)
+                                     : (b ? p.c[1] : p.c[0]);
+            const bool dst_bf16 = p.splits > 1 ? false : ep.out_bf16;
             if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
@@ -351,8 +378,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             const int first = (C::OVL && !(lt & 1)) ? CH - 1 : 0;
             // two register sets: the load of the next chunk is in flight while this one is stored
             auto emit = [&](int c, const uint32_t (&r)[32]) {
-                if (p.store_c || p.splits > 1) store_chunk(p, dst, dst_bf16, row - lane, lane, nt * BN + 32 * c, r);
-                if (p.q_packed[b]) quant_chunk(p, b, row, nt * BN + 32 * c, r);
+                if (ep.store_c || splits > 1) store_chunk(ep, dst, dst_bf16, row - lane, lane, nt * BN + 32 * c, r);
+                if (ep.q_packed) quant_chunk(ep, row, nt * BN + 32 * c, r);
             };
             uint32_t ra[32], rb[32];
             ptx::tmem_ld32(acc + 32 * first, ra);
@@ -588,16 +615,18 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue (both CTAs)
         const int q = warp & 3;
+        const Epi ep = make_epi(p, my_batch);
+        const int splits = p.splits;
         int lt = 0;
         bool ok = true;
         for (int t = pair; t < total && ok; t += npairs, lt++) {
-            const int ks = t % p.splits, tt = t / p.splits;
+            const int ks = t % splits, tt = t / splits;
             const int mp = tt % mp_tiles, nt = tt / mp_tiles;
             const int mt = my_mtile(mp);
             // split-K: fp32 partial sums into the scratch slab of (batch, split)
-            void *dst = p.splits > 1 ? static_cast<void *>(p.partial + int64_t(my_batch * p.splits + ks) * p.M * p.N)
-                                     : p.c[my_batch];
-            const bool dst_bf16 = p.splits > 1 ? false : bool(p.out_bf16);
+            void *dst = splits > 1 ? static_cast<void *>(p.partial + int64_t(my_batch * splits + ks) * ep.M * ep.N)
+                                   : (my_batch ? p.c[1] : p.c[0]);
+            const bool dst_bf16 = splits > 1 ? false : ep.out_bf16;
             if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
@@ -608,8 +637,8 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             static_assert(SHARED == 1 && CH % 2 == 0, "the drain order below assumes one shared chunk");
             // two register sets: the load of the next chunk is in flight while this one is stored
             auto emit = [&](int c, const uint32_t (&r)[32]) {
-                if (p.store_c || p.splits > 1) store_chunk(p, dst, dst_bf16, row - lane, lane, nt * C::BN + 32 * c, r);
-                if (p.q_packed[my_batch]) quant_chunk(p, my_batch, row, nt * C::BN + 32 * c, r);
+                if (ep.store_c || splits > 1) store_chunk(ep, dst, dst_bf16, row - lane, lane, nt * C::BN + 32 * c, r);
+                if (ep.q_packed) quant_chunk(ep, row, nt * C::BN + 32 * c, r);
             };
             uint32_t ra[32], rb[32];
             ptx::tmem_ld32(acc + 32 * first, ra);
@@ -866,8 +895,9 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
         if (g_gemm_splits > 0) {
             s = g_gemm_splits;
         } else if (pair) {
-            // at least 8 k-tiles (K = 2048) per split keep the pipeline fill small against the work
-            if (tiles * 2 <= slots && k_tiles >= 16) s = std::min(slots / tiles, k_tiles / 8);
+            // Pays only with a quarter of the CTA pairs busy and a long K (weight gradients
+            // of small layers): the partial slabs and the second kernel cost about 10 us.
+            if (tiles * 4 <= slots && k_tiles >= 32) s = std::min(slots / tiles, k_tiles / 8);
         } else if (M <= 32 && tiles * 2 <= slots && k_tiles >= 4) {                 // partial traffic grows with M
             s = std::min(slots / tiles, k_tiles / 2);
         }

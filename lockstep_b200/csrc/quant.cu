@@ -243,31 +243,38 @@ __global__ void __launch_bounds__(kThreads)
 quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__restrict__ packed,
                   float *__restrict__ scale, uint8_t *__restrict__ sf)
 {
-    constexpr int STRIDE = kTC + (sizeof(T) == 2 ? 2 : 1);      // elements; keeps rows on different banks
-    __shared__ T tile[kTR * STRIDE];
-    const int64_t r0 = int64_t(blockIdx.y) * kTR, c0 = int64_t(blockIdx.x) * kTC;
-    constexpr int VEC = 16 / sizeof(T);                          // elements per 16-byte load
+    // The tile sits in shared memory as rows of 16-byte chunks, each group of 32 rows
+    // rotated by two more chunks: the column reads below (4 row groups x 8 columns per
+    // warp) then fall on different banks without padding, and the row writes stay
+    // 16-byte vectors.
+    constexpr int VEC = 16 / sizeof(T);                          // elements per 16-byte chunk
     constexpr int CHUNKS = kTC / VEC;                            // per tile row
-    const bool vec_ok = (C % VEC) == 0;
+    __shared__ uint4 tile4[kTR * CHUNKS];
+    const T *tile = reinterpret_cast<const T *>(tile4);
+    const int64_t r0 = int64_t(blockIdx.y) * kTR, c0 = int64_t(blockIdx.x) * kTC;
+    const bool vec_ok = (C % VEC) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+#pragma unroll
     for (int i = threadIdx.x; i < kTR * CHUNKS; i += kThreads) {
-        const int r = i / CHUNKS, cc = (i % CHUNKS) * VEC;
-        T v[VEC];
+        const int r = i / CHUNKS, ch = i % CHUNKS, cc = ch * VEC;
+        uint4 v;
         if (vec_ok && c0 + cc + VEC <= C) {
-            *reinterpret_cast<uint4 *>(v) = ld_stream(reinterpret_cast<const uint4 *>(x + (r0 + r) * C + c0 + cc));
+            v = ld_stream(reinterpret_cast<const uint4 *>(x + (r0 + r) * C + c0 + cc));
         } else {
+            alignas(16) T e[VEC];
 #pragma unroll
-            for (int k = 0; k < VEC; k++) v[k] = c0 + cc + k < C ? x[(r0 + r) * C + c0 + cc + k] : T(0.0f);
+            for (int k = 0; k < VEC; k++) e[k] = c0 + cc + k < C ? x[(r0 + r) * C + c0 + cc + k] : T(0.0f);
+            v = *reinterpret_cast<uint4 *>(e);
         }
-#pragma unroll
-        for (int k = 0; k < VEC; k++) tile[r * STRIDE + cc + k] = v[k];
+        tile4[r * CHUNKS + ((ch + 2 * (r >> 5)) & (CHUNKS - 1))] = v;
     }
     __syncthreads();
     const int rb = threadIdx.x & 3, c = threadIdx.x >> 2;        // 4 blocks of 32 per column, 64 columns
+    const int pos = (c + 2 * VEC * rb) & (kTC - 1);              // this column inside the rotated rows of group rb
     float q[32];
     uint32_t amax = 0;
 #pragma unroll
     for (int i = 0; i < 32; i++) {
-        q[i] = float(tile[(rb * 32 + i) * STRIDE + c]);
+        q[i] = float(tile[(rb * 32 + i) * kTC + pos]);
         amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
     }
     const uint32_t e8 = block_e8m0(amax);
