@@ -10,7 +10,8 @@
 //               into a ring of shared-memory stages
 //   warp 1      MMA issuer: scale tiles shared -> tensor memory, then four
 //               K=64 MMAs per stage; commits free the stage / publish the tile
-//   warps 2-5   epilogue: tensor memory -> registers -> global
+//   warps 2-5   epilogue: tensor memory -> registers -> global (warps 2-9 in the
+//               CTA-pair kernel)
 // Two accumulator buffers alternate between tiles.  With 256-column tiles they
 // overlap by 32 columns (2 x 256 + scales would not fit in 512 columns): the
 // epilogue drains the shared columns first and only then lets the next tile's
@@ -27,7 +28,8 @@ namespace {
 
 constexpr int BM = 128;            // rows of A per tile (= tensor-memory lanes)
 constexpr int BKB = 128;           // bytes of K per stage row = 256 E2M1 = one swizzle row
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;      // single-CTA kernel: producer, MMA issuer, 4 epilogue warps
+constexpr int kPairThreads = 320;      // CTA-pair kernel: producer, MMA issuer, 8 epilogue warps
 constexpr int kTmemCols = 512;
 
 template <int BN>
@@ -457,7 +459,7 @@ splitk_reduce_kernel(const float *__restrict__ partial, void *__restrict__ out, 
 // Roles per CTA: warp 0 lane: TMA producer for this CTA's stage halves (every
 // load of either CTA completes on CTA 0's barrier).  Warp 1 lane of CTA 0: the
 // MMA issuer for the pair (warp 1 of CTA 1 only takes part in the tensor-memory
-// allocation).  Warps 2-5: epilogue.
+// allocation).  Warps 2-9: epilogue, two warps per quarter of the rows.
 struct PairCfg {
     static constexpr int BN = 256;                         // tile columns (128 rows of W per CTA)
     static constexpr int STAGES = 6;
@@ -486,7 +488,7 @@ __device__ __forceinline__ uint32_t cluster_ctarank()
     return r;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfa0,
                        const __grid_constant__ CUtensorMap tm_sfa1, const __grid_constant__ CUtensorMap tm_sfb,
@@ -526,7 +528,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             ptx::mbar_init(empty_bar(s), 1);
         }
         ptx::mbar_init(acc_full_bar, 1);
-        ptx::mbar_init(acc_free_bar, 8);                    // 4 epilogue warps of each CTA
+        ptx::mbar_init(acc_free_bar, 16);                   // 8 epilogue warps of each CTA
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -614,7 +616,11 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue (both CTAs)
-        const int q = warp & 3;
+        // Eight warps: warp w reads the tensor-memory lanes of quarter w % 4 (the hardware
+        // ties a warp to that quarter) and one half of the tile's columns, four chunks of
+        // 32.  The stores of a 128 x 256 tile keep one warp busy for longer than a short-K
+        // tile takes on the tensor cores, so two warps share each row quarter.
+        const int q = warp & 3, half = (warp - 2) >> 2;
         const Epi ep = make_epi(p, my_batch);
         const int splits = p.splits;
         int lt = 0;
@@ -631,30 +637,37 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             ptx::tc_fence_after();
             const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
             const int row = mt * BM + 32 * q + lane;
-            constexpr int CH = C::BN / 32;
-            constexpr int SHARED = C::OVL / 32;             // chunks shared with the other accumulator
-            const int first = !(lt & 1) ? CH - SHARED : 0;
-            static_assert(SHARED == 1 && CH % 2 == 0, "the drain order below assumes one shared chunk");
-            // two register sets: the load of the next chunk is in flight while this one is stored
+            constexpr int CH = C::BN / 32 / 2;              // chunks per warp
+            static_assert(C::OVL == 32 && CH == 4, "the drain order below assumes one shared chunk per tile");
+            // The 32 columns shared with the other accumulator are chunk 7 of accumulator 0
+            // and chunk 0 of accumulator 1.  The warps that own them read them first and
+            // then release the next tile; the other warps release it at once: being here,
+            // they have finished every load of the tiles before this one.
+            const bool owner = (lt & 1) ? half == 0 : half == 1;
+            const int start = (owner && !(lt & 1)) ? CH - 1 : 0;
+            auto chunk = [&](int i) { return CH * half + ((start + i) & (CH - 1)); };
+            auto release_next_tile = [&]() {
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
+            };
+            if (!owner) release_next_tile();
             auto emit = [&](int c, const uint32_t (&r)[32]) {
                 if (ep.store_c || splits > 1) store_chunk(ep, dst, dst_bf16, row - lane, lane, nt * C::BN + 32 * c, r);
                 if (ep.q_packed) quant_chunk(ep, row, nt * C::BN + 32 * c, r);
             };
+            // two register sets: the load of the next chunk is in flight while this one is stored
             uint32_t ra[32], rb[32];
-            ptx::tmem_ld32(acc + 32 * first, ra);
+            ptx::tmem_ld32(acc + 32 * chunk(0), ra);
 #pragma unroll
             for (int i = 0; i < CH; i += 2) {
                 ptx::tmem_ld_wait(ra);
-                ptx::tmem_ld32(acc + 32 * ((first + i + 1) % CH), rb);
-                if (i == 0) {                               // shared columns drained: the next tile may start
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
-                }
-                emit((first + i) % CH, ra);
+                ptx::tmem_ld32(acc + 32 * chunk(i + 1), rb);
+                if (i == 0 && owner) release_next_tile();   // shared columns drained
+                emit(chunk(i), ra);
                 ptx::tmem_ld_wait(rb);
-                if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * ((first + i + 2) % CH), ra);
-                emit((first + i + 1) % CH, rb);
+                if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * chunk(i + 2), ra);
+                emit(chunk(i + 1), rb);
             }
         }
     }
@@ -760,7 +773,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
         // resident at once (fewer than SMs / 2 when a TPC has a single SM enabled).
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(unsigned(sm_count() & ~1), 1, 1);
-        cfg.blockDim = dim3(kGemmThreads, 1, 1);
+        cfg.blockDim = dim3(kPairThreads, 1, 1);
         cfg.dynamicSmemBytes = C::SMEM;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
@@ -775,7 +788,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     int pairs = (p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2) * n_tiles * p.splits;
     int max_pairs = resident_pairs[dev];
     int grid = 2 * (pairs < max_pairs ? pairs : max_pairs);
-    mxfp4_gemm_pair_kernel<<<grid, kGemmThreads, C::SMEM, st>>>(ta0, ta1, tb, tsa0, tsa1, tsb, p);
+    mxfp4_gemm_pair_kernel<<<grid, kPairThreads, C::SMEM, st>>>(ta0, ta1, tb, tsa0, tsa1, tsb, p);
     LS_LAUNCH_CHECK("mxfp4_gemm_pair");
     return LS_OK;
 }
