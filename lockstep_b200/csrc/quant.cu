@@ -233,79 +233,116 @@ quantize_f32_kernel(const uint8_t *__restrict__ x, uint32_t n8, QuantOut o)
 
 // ---- transposed quantizer -------------------------------------------------------
 // x [R, C] row-major -> MXFP4 of x^T [C, R], blocks of 32 running down a column of x
-// (what a GEMM that contracts over R needs).  A CTA stages a 128 x 64 tile in shared
-// memory with coalesced row reads, then each thread walks one column segment of 32
-// values, so the packed output of a column is written in 64-byte pieces.
-constexpr int kTR = 128, kTC = 64;
+// (what a GEMM that contracts over R needs).  A CTA walks tiles of 128 rows x 256 bytes:
+// the rows are copied to shared memory with 16-byte asynchronous copies (the next tile
+// is in flight while this one is quantized), then each thread walks one column segment
+// of 32 values, so the packed output of a column is written in 64-byte pieces.
+constexpr int kTR = 128;                  // tile rows = 4 blocks of 32
+constexpr int kTRowBytes = 256;           // bytes of each row in a tile
+constexpr int kTSmem = 2 * kTR * kTRowBytes;
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(smem))),
+                 "l"(__cvta_generic_to_global(gmem))
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename T, bool RNE>
 __global__ void __launch_bounds__(kThreads)
 quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__restrict__ packed,
                   float *__restrict__ scale, uint8_t *__restrict__ sf)
 {
-    // The tile sits in shared memory as rows of 16-byte chunks, each group of 32 rows
+    // A tile sits in shared memory as rows of 16-byte chunks, each group of 32 rows
     // rotated by two more chunks: the column reads below (4 row groups x 8 columns per
     // warp) then fall on different banks without padding, and the row writes stay
     // 16-byte vectors.
     constexpr int VEC = 16 / sizeof(T);                          // elements per 16-byte chunk
-    constexpr int CHUNKS = kTC / VEC;                            // per tile row
-    __shared__ uint4 tile4[kTR * CHUNKS];
-    const T *tile = reinterpret_cast<const T *>(tile4);
-    const int64_t r0 = int64_t(blockIdx.y) * kTR, c0 = int64_t(blockIdx.x) * kTC;
-    const bool vec_ok = (C % VEC) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    constexpr int TC = kTRowBytes / sizeof(T);                   // tile columns
+    constexpr int CHUNKS = TC / VEC;                             // per tile row
+    extern __shared__ uint4 tile_smem[];                         // two tiles
+    const int64_t tiles_x = (C + TC - 1) / TC, tiles = tiles_x * (R / kTR);
+    const bool vec_ok = (C % VEC) == 0;
+
+    auto stage = [&](int64_t t, uint4 *buf) {                    // tile t -> buf, asynchronously where it can be
+        const int64_t r0 = (t / tiles_x) * kTR, c0 = (t % tiles_x) * TC;
 #pragma unroll
-    for (int i = threadIdx.x; i < kTR * CHUNKS; i += kThreads) {
-        const int r = i / CHUNKS, ch = i % CHUNKS, cc = ch * VEC;
-        uint4 v;
-        if (vec_ok && c0 + cc + VEC <= C) {
-            v = ld_stream(reinterpret_cast<const uint4 *>(x + (r0 + r) * C + c0 + cc));
-        } else {
-            alignas(16) T e[VEC];
+        for (int i = threadIdx.x; i < kTR * CHUNKS; i += kThreads) {
+            const int r = i / CHUNKS, ch = i % CHUNKS, cc = ch * VEC;
+            uint4 *dst = buf + r * CHUNKS + ((ch + 2 * (r >> 5)) & (CHUNKS - 1));
+            const T *src = x + (r0 + r) * C + c0 + cc;
+            if (vec_ok && c0 + cc + VEC <= C) {
+                cp_async16(dst, src);
+            } else {                                             // ragged right edge, or rows not 16-byte aligned
+                alignas(16) T e[VEC];
 #pragma unroll
-            for (int k = 0; k < VEC; k++) e[k] = c0 + cc + k < C ? x[(r0 + r) * C + c0 + cc + k] : T(0.0f);
-            v = *reinterpret_cast<uint4 *>(e);
-        }
-        tile4[r * CHUNKS + ((ch + 2 * (r >> 5)) & (CHUNKS - 1))] = v;
-    }
-    __syncthreads();
-    const int rb = threadIdx.x & 3, c = threadIdx.x >> 2;        // 4 blocks of 32 per column, 64 columns
-    const int pos = (c + 2 * VEC * rb) & (kTC - 1);              // this column inside the rotated rows of group rb
-    float q[32];
-    uint32_t amax = 0;
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-        q[i] = float(tile[(rb * 32 + i) * kTC + pos]);
-        amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
-    }
-    const uint32_t e8 = block_e8m0(amax);
-    const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
-    uint32_t pk[4];
-#pragma unroll
-    for (int h = 0; h < 4; h++) {
-        float t[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) t[i] = q[8 * h + i] * inv;
-        if (amax < kBitsInf) pk[h] = RNE ? cvt_e2m1x8(t) : cvt_ref_e2m1x8(t);
-        else pk[h] = codes8<RNE>(t);
-    }
-    const int64_t col = c0 + c;
-    // exponent bytes of this column's 4 blocks (lanes rb = 0..3) -> one word at lane rb = 0
-    uint32_t w = e8;
-    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 1) << 8;
-    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 2) << 16;
-    w |= __shfl_down_sync(0xFFFFFFFFu, e8, 3) << 24;
-    if (col < C) {
-        if (packed) *reinterpret_cast<uint4 *>(packed + col * (R / 2) + (r0 + rb * 32) / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        if (rb == 0) {
-            const int64_t kb = r0 / 32;                          // first of 4 blocks: one scale tile
-            if (scale) {
-                uint4 sc;
-                sc.x = scale_bits(w & 0xFFu), sc.y = scale_bits((w >> 8) & 0xFFu);
-                sc.z = scale_bits((w >> 16) & 0xFFu), sc.w = scale_bits(w >> 24);
-                *reinterpret_cast<uint4 *>(scale + col * (R / 32) + kb) = sc;
+                for (int k = 0; k < VEC; k++) e[k] = c0 + cc + k < C ? src[k] : T(0.0f);
+                *dst = *reinterpret_cast<uint4 *>(e);
             }
-            if (sf) *reinterpret_cast<uint32_t *>(sf + sf_offset(uint32_t(col), uint32_t(kb), uint32_t(R / 128))) = w;
         }
+        cp_async_commit();
+    };
+
+    int b = 0;
+    if (int64_t(blockIdx.x) < tiles) stage(blockIdx.x, tile_smem);
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x, b ^= 1) {
+        const int64_t next = t + gridDim.x;
+        if (next < tiles) {
+            stage(next, tile_smem + (b ^ 1) * kTR * CHUNKS);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const T *tile = reinterpret_cast<const T *>(tile_smem + b * kTR * CHUNKS);
+        const int64_t r0 = (t / tiles_x) * kTR, c0 = (t % tiles_x) * TC;
+#pragma unroll
+        for (int item = threadIdx.x; item < 4 * TC; item += kThreads) {
+            const int rb = item & 3, c = item >> 2;              // 4 blocks of 32 per column
+            const int pos = (c + 2 * VEC * rb) & (TC - 1);       // this column inside the rotated rows of group rb
+            float q[32];
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                q[i] = float(tile[(rb * 32 + i) * TC + pos]);
+                amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
+            }
+            const uint32_t e8 = block_e8m0(amax);
+            const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+            uint32_t pk[4];
+#pragma unroll
+            for (int h = 0; h < 4; h++) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = q[8 * h + i] * inv;
+                if (amax < kBitsInf) pk[h] = RNE ? cvt_e2m1x8(v) : cvt_ref_e2m1x8(v);
+                else pk[h] = codes8<RNE>(v);
+            }
+            const int64_t col = c0 + c;
+            // exponent bytes of this column's 4 blocks (lanes rb = 0..3) -> one word at lane rb = 0
+            uint32_t w = e8;
+            w |= __shfl_down_sync(0xFFFFFFFFu, e8, 1) << 8;
+            w |= __shfl_down_sync(0xFFFFFFFFu, e8, 2) << 16;
+            w |= __shfl_down_sync(0xFFFFFFFFu, e8, 3) << 24;
+            if (col < C) {
+                if (packed)
+                    *reinterpret_cast<uint4 *>(packed + col * (R / 2) + (r0 + rb * 32) / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                if (rb == 0) {
+                    const int64_t kb = r0 / 32;                  // first of 4 blocks: one scale tile
+                    if (scale) {
+                        uint4 sc;
+                        sc.x = scale_bits(w & 0xFFu), sc.y = scale_bits((w >> 8) & 0xFFu);
+                        sc.z = scale_bits((w >> 16) & 0xFFu), sc.w = scale_bits(w >> 24);
+                        *reinterpret_cast<uint4 *>(scale + col * (R / 32) + kb) = sc;
+                    }
+                    if (sf) *reinterpret_cast<uint32_t *>(sf + sf_offset(uint32_t(col), uint32_t(kb), uint32_t(R / 128))) = w;
+                }
+            }
+        }
+        __syncthreads();                                         // this buffer is refilled by the next iteration's copies
     }
 }
 
@@ -612,19 +649,39 @@ extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_
     if (!x || (!packed && !scale && !sf)) return fail(LS_EINVAL, "null pointer");
     if (!aligned16(x) || !aligned16(packed) || !aligned16(scale) || (reinterpret_cast<uintptr_t>(sf) & 3))
         return fail(LS_EALIGN, "x, packed and scale must be 16-byte aligned, sf 4-byte");
-    if (C >= (int64_t(1) << 31) || R / 128 > 65535) return fail(LS_EINVAL, "shape too large");
-    dim3 grid(unsigned((C + kTC - 1) / kTC), unsigned(R / kTR));
+    if (C >= (int64_t(1) << 31) || R >= (int64_t(1) << 31)) return fail(LS_EINVAL, "shape too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool rne = rounding == LS_ROUND_RNE;
+    {
+        static bool attr_set[64] = {};                           // the kernels need 64 KB of dynamic shared memory
+        int dev = 0;
+        LS_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64) return fail(LS_ECUDA, "device index %d out of range", dev);
+        if (!attr_set[dev]) {
+            LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
+            LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
+            LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
+            LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
+            attr_set[dev] = true;
+        }
+    }
+    auto launch = [&](auto kernel, auto xp, int tile_cols) -> int {
+        const int64_t tiles = ((C + tile_cols - 1) / tile_cols) * (R / kTR);
+        const int64_t cap = int64_t(sm_count()) * 3;             // three resident CTAs per SM (64 KB each)
+        kernel<<<unsigned(tiles < cap ? tiles : cap), kThreads, kTSmem, st>>>(xp, R, C, packed, scale, sf);
+        return LS_OK;
+    };
+    int rc;
     if (x_dtype == LS_BF16) {
         auto xp = static_cast<const __nv_bfloat16 *>(x);
-        if (rne) quantize_t_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
-        else quantize_t_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
+        rc = rne ? launch(quantize_t_kernel<__nv_bfloat16, true>, xp, kTRowBytes / 2)
+                 : launch(quantize_t_kernel<__nv_bfloat16, false>, xp, kTRowBytes / 2);
     } else {
         auto xp = static_cast<const float *>(x);
-        if (rne) quantize_t_kernel<float, true><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
-        else quantize_t_kernel<float, false><<<grid, kThreads, 0, st>>>(xp, R, C, packed, scale, sf);
+        rc = rne ? launch(quantize_t_kernel<float, true>, xp, kTRowBytes / 4)
+                 : launch(quantize_t_kernel<float, false>, xp, kTRowBytes / 4);
     }
+    if (rc) return rc;
     LS_LAUNCH_CHECK("quantize_mxfp4_t");
     return LS_OK;
 }

@@ -175,7 +175,7 @@ __device__ __forceinline__ void store8(float *p, int64_t i0, int64_t n, const fl
 
 // ---- phase 1: sender ---------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
-wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, WireGeom geo, Peers peers,
+wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
                  uint32_t epoch)
 {
     const uint32_t stride = gridDim.x * kThreads;
@@ -218,7 +218,7 @@ wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res
 // senders' slots are issued together before the first decode.  WORLD = 0: any size.
 template <int WORLD>
 __global__ void __launch_bounds__(kThreads)
-wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t epoch, int reverse)
+wire_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch, int reverse)
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
@@ -299,7 +299,7 @@ wire_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t
 // folds into the block scale.  Otherwise an IEEE division (wire.py:138 `.div_(world)`).
 template <bool POW2>
 __global__ void __launch_bounds__(kThreads)
-wire_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
+wire_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch)
 {
     constexpr int U = 4;                                        // independent quads in flight per thread
     uint8_t *my = peers.arena[geo.rank];
@@ -415,7 +415,7 @@ __device__ __forceinline__ float shared_max(const uint8_t *my, const WireGeom &g
 
 // phase 0: publish this rank's chunk maxima of v = g + res to every rank
 __global__ void __launch_bounds__(kThreads)
-wire_int_max_kernel(const float *__restrict__ g, int64_t n, const float *__restrict__ res, WireGeom geo, Peers peers,
+wire_int_max_kernel(const float *__restrict__ g, int64_t n, const float *__restrict__ res, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
                     uint32_t epoch)
 {
     const uint32_t groups = uint32_t(geo.padded / 8), stride = gridDim.x * kThreads;
@@ -441,7 +441,7 @@ wire_int_max_kernel(const float *__restrict__ g, int64_t n, const float *__restr
 // phase 1: quantize on the shared grid, update the sender residual, push to the owners
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
-wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, WireGeom geo, Peers peers,
+wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
                      uint32_t epoch)
 {
     constexpr int LIM = (1 << (BITS - 1)) - 1;
@@ -480,7 +480,7 @@ wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__
 // phase 2: exact integer sum at the owner, owner grid, owner residual, push to everyone
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
-wire_int_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint32_t epoch)
+wire_int_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch)
 {
     constexpr int LIM = (1 << (BITS - 1)) - 1;
     uint8_t *my = peers.arena[geo.rank];
@@ -529,7 +529,7 @@ wire_int_reduce_kernel(float *__restrict__ ores, WireGeom geo, Peers peers, uint
 // phase 3: decode the gathered shards, divide by the world size
 template <int BITS>
 __global__ void __launch_bounds__(kThreads)
-wire_int_finish_kernel(float *__restrict__ g, int64_t n, WireGeom geo, Peers peers, uint32_t epoch)
+wire_int_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch)
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);

@@ -207,7 +207,7 @@ def test_quantize_random_vs_c_oracle(fp4, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("R,C", [(128, 64), (256, 100), (384, 1000), (1024, 4096)])
+@pytest.mark.parametrize("R,C", [(128, 64), (256, 100), (384, 1000), (1024, 4096), (2048, 4100), (4096, 2048)])
 def test_transposed_quantizer_equals_quantizer_of_transpose(fp4, dtype, R, C, golden):
     g = torch.Generator().manual_seed(R + C)
     x = torch.randn(R, C, generator=g) * torch.exp2(torch.randint(-20, 20, (1, C), generator=g).float())
