@@ -193,6 +193,43 @@ def run_sweep(args):
     mxfp4_gemm.gemm_status()
 
 
+def run_shape(m, n, k, out_f32, steps):
+    """One shape of the single MXFP4 GEMM: `steps` launches replayed from a CUDA graph
+    (device time rather than launch overhead), timed with CUDA events after a 256 MiB
+    write that flushes L2."""
+    from lockstep_b200 import fp4, mxfp4_gemm
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    w = (torch.randn(n, k, device=dev, generator=g) * 0.02).bfloat16()
+    a = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    w_pk, w_sf = fp4.quantize_mxfp4_packed(w)
+    a_pk, a_sf = fp4.quantize_mxfp4_packed(a)
+    dt = torch.float32 if out_f32 else torch.bfloat16
+    for _ in range(3):
+        mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf, dt)
+    graph = torch.cuda.CUDAGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        for _ in range(steps):
+            c = mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf, dt)
+    graph.replay()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    best = float("inf")
+    for _ in range(3):
+        flush.fill_(1)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        graph.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        best = min(best, t0.elapsed_time(t1) / steps)
+    del graph, c
+    mxfp4_gemm.gemm_status()
+    print(json.dumps({"shape": [m, n, k], "out": "f32" if out_f32 else "bf16", "steps": steps, "us": best * 1e3,
+                      "tflops": 2 * m * n * k / best / 1e9,
+                      "out_gbs": m * n * (4 if out_f32 else 2) / best / 1e6}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,15 +243,20 @@ def main():
     ap.add_argument("--no-train", action="store_true", help="skip the FP4-linear training-step leg")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
     ap.add_argument("--sweep", action="store_true", help="shape sweep of the single GEMM instead of the benchmark step")
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time one shape of the single GEMM instead")
+    ap.add_argument("--out-f32", action="store_true", help="with --shape: fp32 output instead of bf16")
     args = ap.parse_args()
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
 
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.sweep:
+    if args.sweep or args.shape:
         if rank == 0:
-            run_sweep(args)
+            if args.shape:
+                run_shape(*args.shape, args.out_f32, min(args.steps, 50))
+            else:
+                run_sweep(args)
         return
 
     import torch.distributed as dist

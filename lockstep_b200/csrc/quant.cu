@@ -299,47 +299,85 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
         __syncthreads();
         const T *tile = reinterpret_cast<const T *>(tile_smem + b * kTR * CHUNKS);
         const int64_t r0 = (t / tiles_x) * kTR, c0 = (t % tiles_x) * TC;
-#pragma unroll
-        for (int item = threadIdx.x; item < 4 * TC; item += kThreads) {
-            const int rb = item & 3, c = item >> 2;              // 4 blocks of 32 per column
-            const int pos = (c + 2 * VEC * rb) & (TC - 1);       // this column inside the rotated rows of group rb
-            float q[32];
-            uint32_t amax = 0;
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-                q[i] = float(tile[(rb * 32 + i) * TC + pos]);
-                amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
-            }
-            const uint32_t e8 = block_e8m0(amax);
-            const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
-            uint32_t pk[4];
-#pragma unroll
-            for (int h = 0; h < 4; h++) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) v[i] = q[8 * h + i] * inv;
-                if (amax < kBitsInf) pk[h] = RNE ? cvt_e2m1x8(v) : cvt_ref_e2m1x8(v);
-                else pk[h] = codes8<RNE>(v);
-            }
-            const int64_t col = c0 + c;
+        auto emit = [&](int64_t col, int rb, uint32_t e8, const uint32_t (&pk)[4]) {
             // exponent bytes of this column's 4 blocks (lanes rb = 0..3) -> one word at lane rb = 0
             uint32_t w = e8;
             w |= __shfl_down_sync(0xFFFFFFFFu, e8, 1) << 8;
             w |= __shfl_down_sync(0xFFFFFFFFu, e8, 2) << 16;
             w |= __shfl_down_sync(0xFFFFFFFFu, e8, 3) << 24;
-            if (col < C) {
-                if (packed)
-                    *reinterpret_cast<uint4 *>(packed + col * (R / 2) + (r0 + rb * 32) / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                if (rb == 0) {
-                    const int64_t kb = r0 / 32;                  // first of 4 blocks: one scale tile
-                    if (scale) {
-                        uint4 sc;
-                        sc.x = scale_bits(w & 0xFFu), sc.y = scale_bits((w >> 8) & 0xFFu);
-                        sc.z = scale_bits((w >> 16) & 0xFFu), sc.w = scale_bits(w >> 24);
-                        *reinterpret_cast<uint4 *>(scale + col * (R / 32) + kb) = sc;
-                    }
-                    if (sf) *reinterpret_cast<uint32_t *>(sf + sf_offset(uint32_t(col), uint32_t(kb), uint32_t(R / 128))) = w;
+            if (col >= C) return;
+            if (packed)
+                *reinterpret_cast<uint4 *>(packed + col * (R / 2) + (r0 + rb * 32) / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (rb == 0) {
+                const int64_t kb = r0 / 32;                      // first of 4 blocks: one scale tile
+                if (scale) {
+                    uint4 sc;
+                    sc.x = scale_bits(w & 0xFFu), sc.y = scale_bits((w >> 8) & 0xFFu);
+                    sc.z = scale_bits((w >> 16) & 0xFFu), sc.w = scale_bits(w >> 24);
+                    *reinterpret_cast<uint4 *>(scale + col * (R / 32) + kb) = sc;
                 }
+                if (sf) *reinterpret_cast<uint32_t *>(sf + sf_offset(uint32_t(col), uint32_t(kb), uint32_t(R / 128))) = w;
+            }
+        };
+        if constexpr (sizeof(T) == 2) {
+            // bf16: a thread takes two adjacent columns (one 32-bit word per row) of one row
+            // group.  Maxima run on packed pairs; the reference's rounding of halfway values
+            // comes from a reciprocal scale shortened by 2^-12 (the product is exact) and the
+            // hardware's round-to-nearest-even conversion, as in the row-wise kernel.
+            static_assert(sizeof(T) != 2 || 4 * (TC / 2) == kThreads, "one item per thread");
+            const uint32_t *tile32 = reinterpret_cast<const uint32_t *>(tile);
+            const int rb = threadIdx.x & 3, cp = threadIdx.x >> 2;
+            const int posw = (cp + 2 * VEC / 2 * rb) & (TC / 2 - 1);   // word of this column pair in the rotated rows
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) w[i] = tile32[(rb * 32 + i) * (TC / 2) + posw];
+            __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
+#pragma unroll
+            for (int i = 1; i < 32; i++) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+            const uint32_t mb = *reinterpret_cast<uint32_t *>(&m);
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                const uint32_t amax = hi ? (mb & 0xFFFF0000u) : (mb << 16);       // as fp32 bits
+                const uint32_t e8 = block_e8m0(amax);
+                const bool finite = amax < kBitsInf;
+                const float cmul = __uint_as_float(e8 == 255u      ? 0x7FC00000u
+                                                   : (RNE || !finite) ? inv_scale_bits(e8)
+                                                                      : (((253u - e8) << 23) | 0x7FF000u));
+                uint32_t pk[4];
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        v[i] = __uint_as_float(hi ? (w[8 * h + i] & 0xFFFF0000u) : (w[8 * h + i] << 16)) * cmul;
+                    pk[h] = finite ? cvt_e2m1x8(v) : codes8<RNE>(v);
+                }
+                emit(c0 + 2 * cp + hi, rb, e8, pk);
+            }
+        } else {
+#pragma unroll
+            for (int item = threadIdx.x; item < 4 * TC; item += kThreads) {
+                const int rb = item & 3, c = item >> 2;              // 4 blocks of 32 per column
+                const int pos = (c + 2 * VEC * rb) & (TC - 1);       // this column inside the rotated rows of group rb
+                float q[32];
+                uint32_t amax = 0;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    q[i] = float(tile[(rb * 32 + i) * TC + pos]);
+                    amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
+                }
+                const uint32_t e8 = block_e8m0(amax);
+                const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
+                uint32_t pk[4];
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = q[8 * h + i] * inv;
+                    if (amax < kBitsInf) pk[h] = RNE ? cvt_e2m1x8(v) : cvt_ref_e2m1x8(v);
+                    else pk[h] = codes8<RNE>(v);
+                }
+                emit(c0 + c, rb, e8, pk);
             }
         }
         __syncthreads();                                         // this buffer is refilled by the next iteration's copies
