@@ -148,6 +148,27 @@ __device__ __forceinline__ void transpose4(uint4 (&it)[4], int lane)
     }
 }
 
+// Ragged edge of the output (N not a multiple of the vector width, or the last columns of
+// a tile): element-wise stores from a private copy of the chunk.  Kept out of line, and fed
+// from a copy, so that neither its loop nor its run-time index touches the epilogue's
+// accumulator registers (a run-time index into them would move them to local memory) or
+// its code size (a tile's epilogue runs once per tile; short tiles pay for every
+// instruction fetched).
+__device__ __noinline__ void store_tail_impl(void *dst, bool bf16, int n, const uint32_t *v)
+{
+    if (bf16)
+        for (int j = 0; j < n; j++) static_cast<__nv_bfloat16 *>(dst)[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+    else
+        for (int j = 0; j < n; j++) static_cast<float *>(dst)[j] = __uint_as_float(v[j]);
+}
+__device__ __forceinline__ void store_tail(void *dst, bool bf16, int n, const uint32_t (&r)[32])
+{
+    uint32_t v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = r[j];
+    store_tail_impl(dst, bf16, n, v);
+}
+
 // Stores one accumulator chunk: lane l of the warp holds the 32 consecutive outputs
 // (columns col0 .. col0 + 31) of row row0 + l.  Called by the whole warp.  Storing each
 // lane's own row would touch 32 rows per instruction (one 16-byte piece each); the
@@ -179,10 +200,7 @@ __device__ __forceinline__ void store_chunk(const Epi &p, void *cbase, bool bf16
                 if (trow + k < p.M)
                     *reinterpret_cast<uint4 *>(base + int64_t(trow + k) * p.N + col0 + 8 * tq) = it[k];
         } else if (row < p.M) {
-            __nv_bfloat16 *dst = base + int64_t(row) * p.N + col0;
-#pragma unroll                                     // unrolled with predicates: r[] must stay in registers
-            for (int j = 0; j < 32; j++)
-                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            store_tail(base + int64_t(row) * p.N + col0, true, min(32, p.N - col0), r);
         }
     } else {
         float *base = static_cast<float *>(cbase);
@@ -200,10 +218,7 @@ __device__ __forceinline__ void store_chunk(const Epi &p, void *cbase, bool bf16
                         *reinterpret_cast<uint4 *>(base + int64_t(trow + k) * p.N + col0 + 16 * h + 4 * tq) = it[k];
             }
         } else if (row < p.M) {
-            float *dst = base + int64_t(row) * p.N + col0;
-#pragma unroll
-            for (int j = 0; j < 32; j++)
-                if (col0 + j < p.N) dst[j] = __uint_as_float(r[j]);
+            store_tail(base + int64_t(row) * p.N + col0, false, min(32, p.N - col0), r);
         }
     }
 }
@@ -385,7 +400,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             };
             uint32_t ra[32], rb[32];
             ptx::tmem_ld32(acc + 32 * first, ra);
-#pragma unroll
+#pragma unroll 1                                    // code size: the body already holds two chunks
             for (int i = 0; i < CH; i += 2) {
                 ptx::tmem_ld_wait(ra);
                 ptx::tmem_ld32(acc + 32 * ((first + i + 1) % CH), rb);
@@ -659,7 +674,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             // two register sets: the load of the next chunk is in flight while this one is stored
             uint32_t ra[32], rb[32];
             ptx::tmem_ld32(acc + 32 * chunk(0), ra);
-#pragma unroll
+#pragma unroll 1                                    // code size: the body already holds two chunks
             for (int i = 0; i < CH; i += 2) {
                 ptx::tmem_ld_wait(ra);
                 ptx::tmem_ld32(acc + 32 * chunk(i + 1), rb);

@@ -25,8 +25,7 @@ class Block(nn.Module):
 
     def forward(self, x):
         b, t, c = x.shape
-        qkv = self.qkv(self.ln1(x)).view(b, t, 3, self.heads, c // self.heads)
-        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        q, k, v = (z.view(b, t, self.heads, -1).transpose(1, 2) for z in self.qkv(self.ln1(x)).split(c, 2))
         att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.proj(att.transpose(1, 2).reshape(b, t, c))
         return x + self.out(F.gelu(self.fc(self.ln2(x))))
