@@ -107,7 +107,11 @@ int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint8_t *sf, in
  *   a_pk   [M, K/2] packed E2M1, K-contiguous          bt_pk  [N, K/2] likewise
  *   sfa    scale bytes of A in the scale-factor layout  sfb    likewise for W
  *   c      [M, N] row-major, LS_BF16 (round to nearest even) or LS_F32
- * K % 128 == 0; M and N are free.  All buffers 16-byte aligned. */
+ * K % 128 == 0; M and N are free.  All buffers 16-byte aligned.
+ * Entry points may be called from several host threads.  A product that the
+ * library splits along K (few output tiles, long K; see ls_gemm_set_splits)
+ * puts its partial sums in one scratch buffer per device: such calls must not
+ * overlap in time on one device. */
 int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
                   void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 

@@ -48,6 +48,20 @@ int check_device()
     return LS_OK;
 }
 
+int current_device(int *dev)
+{
+    cudaError_t e = cudaGetDevice(dev);
+    if (e != cudaSuccess) return fail(LS_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (*dev < 0 || *dev >= 64) return fail(LS_EINVAL, "device index %d out of range", *dev);
+    return LS_OK;
+}
+
+std::mutex &state_mutex()
+{
+    static std::mutex mu;
+    return mu;
+}
+
 int sm_count()
 {
     DevInfo d;

@@ -4,6 +4,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <mutex>
 #include <stdint.h>
 
 #include "../../include/lockstep_b200.h"
@@ -14,6 +15,8 @@ namespace ls {
 int fail(int code, const char *fmt, ...);          // records the message, returns code
 int check_device();                                 // LS_OK or LS_EARCH / LS_ECUDA
 int sm_count();                                     // SMs of the current device
+int current_device(int *dev);                       // index of the current device, checked against the per-device tables (64 entries)
+std::mutex &state_mutex();                          // guards the library's per-device tables (attributes set, scratch, error words)
 struct QuantEpilogue {              // optional MXFP4 output of act(C), per batch
     uint8_t *packed[2];
     uint8_t *sf[2];

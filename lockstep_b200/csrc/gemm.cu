@@ -742,10 +742,13 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
     using C = Cfg<BN>;
     static bool attr_set[64] = {};
     int dev = 0;
-    LS_CUDA(cudaGetDevice(&dev));
-    if (!attr_set[dev]) {
-        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        attr_set[dev] = true;
+    if (int rc = current_device(&dev)) return rc;
+    {
+        std::lock_guard<std::mutex> lk(state_mutex());
+        if (!attr_set[dev]) {
+            LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+            attr_set[dev] = true;
+        }
     }
     int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.nbatch * p.splits;
     int grid = tiles < sm_count() ? tiles : sm_count();
@@ -781,7 +784,8 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     using C = PairCfg;
     static int resident_pairs[64] = {};
     int dev = 0;
-    LS_CUDA(cudaGetDevice(&dev));
+    if (int rc = current_device(&dev)) return rc;
+    std::unique_lock<std::mutex> lk(state_mutex());
     if (!resident_pairs[dev]) {
         LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         // The kernel is persistent: the grid must not exceed the CTA pairs that can be
@@ -799,9 +803,10 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
         if (n < 1) return fail(LS_ECUDA, "no CTA pair of the GEMM kernel fits on this device");
         resident_pairs[dev] = n;
     }
+    const int max_pairs = resident_pairs[dev];
+    lk.unlock();
     int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + C::BN - 1) / C::BN;
     int pairs = (p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2) * n_tiles * p.splits;
-    int max_pairs = resident_pairs[dev];
     int grid = 2 * (pairs < max_pairs ? pairs : max_pairs);
     mxfp4_gemm_pair_kernel<<<grid, kPairThreads, C::SMEM, st>>>(ta0, ta1, tb, tsa0, tsa1, tsb, p);
     LS_LAUNCH_CHECK("mxfp4_gemm_pair");
@@ -811,13 +816,16 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
 int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
 int g_gemm_splits = 0;           // 0 = choose by shape, n = split K n ways where splitting is allowed
 
-// Per-device scratch for split-K partial sums; grows on demand and is kept.
+// Per-device scratch for split-K partial sums; grows on demand and is kept.  One buffer
+// per device: K-split GEMMs of one device must not overlap in time (streams or threads),
+// and a larger request re-allocates after a device synchronisation.
 float *splitk_scratch(size_t bytes)
 {
     static float *buf[64] = {};
     static size_t cap[64] = {};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (current_device(&dev)) return nullptr;
+    std::lock_guard<std::mutex> lk(state_mutex());
     if (cap[dev] < bytes) {
         if (buf[dev]) {
             cudaDeviceSynchronize();
@@ -838,7 +846,8 @@ int *error_word()
     // one device int per device, allocated on first use and kept for the process
     static int *words[64] = {};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (current_device(&dev)) return nullptr;
+    std::lock_guard<std::mutex> lk(state_mutex());
     if (!words[dev]) {
         if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
         cudaMemset(words[dev], 0, sizeof(int));

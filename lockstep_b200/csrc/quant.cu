@@ -693,8 +693,8 @@ extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_
     {
         static bool attr_set[64] = {};                           // the kernels need 64 KB of dynamic shared memory
         int dev = 0;
-        LS_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64) return fail(LS_ECUDA, "device index %d out of range", dev);
+        if (int rc = current_device(&dev)) return rc;
+        std::lock_guard<std::mutex> lk(state_mutex());
         if (!attr_set[dev]) {
             LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
             LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
