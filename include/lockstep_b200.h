@@ -198,6 +198,16 @@ int ls_wire_create_int(int rank, int world, int64_t padded, int bits, void **han
 int ls_wire_int_phase(void *handle, int phase, float *g, int64_t numel, float *res, float *ores, void *stream);
 int ls_wire_int_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, void *stream);
 
+/* ls_wire_allreduce cuts a call into pieces (the same sub-range of every
+ * owner's shard) whose three phases run on the caller's stream and on two
+ * streams owned by the handle, joined back into the caller's stream before the
+ * call's work counts as done there: the exchange of one piece overlaps the
+ * memory passes of the others.  Results and wire bytes do not depend on the
+ * number of pieces.  0 or 1 = one piece (default: on one and two GPUs the
+ * concurrent phases cost more HBM time than the hidden latency saves),
+ * 2..8 = that many where the shard divides.  No reference counterpart. */
+int ls_wire_set_chunks(void *handle, int chunks);
+
 /* How many times (about 100 ns apart, default 2^22 = ~0.5 s) a kernel polls a
  * peer's flag before it gives up, records a time-out in the status word and
  * carries on with whatever its buffers hold; the context stays usable. */

@@ -47,6 +47,7 @@ _SIGS = {
     "ls_wire_int_allreduce": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "ls_wire_status": (c_int, [c_vp, c_vp]),
     "ls_wire_set_poll_limit": (c_int, [c_vp, c_i64]),
+    "ls_wire_set_chunks": (c_int, [c_vp, c_int]),
     "ls_wire_debug_slots": (c_int, [c_vp, c_int, c_vp, ctypes.POINTER(c_i64), c_vp]),
     "ls_scales_to_sf": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
 }

@@ -28,15 +28,25 @@ constexpr int kMaxWorld = 8;
 constexpr int kThreads = 256;
 constexpr uint32_t kPollLimit = 1u << 22;     // default polls (x ~100 ns sleep each) before a wait gives up
 
+constexpr int kMaxChunks = 8;   // pieces an all-reduce call may be cut into (each with its own flags)
 struct Header {                 // start of every rank's arena
-    uint32_t rs_flag[kMaxWorld];    // epoch of the last completed send from rank s
-    uint32_t ag_flag[kMaxWorld];    // epoch of the last completed reduce of owner o
-    uint32_t counter[2];            // CTA completion counters (send, reduce)
+    uint32_t rs_flag[kMaxChunks][kMaxWorld];    // epoch of the last completed send of chunk c from rank s
+    uint32_t ag_flag[kMaxChunks][kMaxWorld];    // epoch of the last completed reduce of chunk c by owner o
+    uint32_t counter[kMaxChunks][2];            // CTA completion counters (send, reduce)
     uint32_t status;                // non-zero: a wait ran out
     uint32_t mx_flag[kMaxWorld];    // integer wires: epoch of rank s's last published chunk maxima
     uint32_t counter_mx;
 };
-constexpr size_t kHeaderBytes = 256;
+constexpr size_t kHeaderBytes = 1024;
+static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
+
+// A piece of one all-reduce: the same sub-range [first, first + count) (in groups of 8
+// elements) of every owner's shard.  Pieces of one call run as separate launches on three
+// streams, so that one piece's exchange overlaps the memory passes of the others.
+struct Chunk {
+    int index;
+    uint32_t first, count;      // multiples of 32: a warp never straddles a piece
+};
 
 struct Peers { uint8_t *arena[kMaxWorld]; };
 
@@ -58,6 +68,12 @@ struct Wire {
     Peers peers;
     bool mapped, opened[kMaxWorld];
     uint32_t epoch;
+    // pipelined all-reduce: pieces of a call run on the caller's stream (send) and on two
+    // streams of the wire (owner phase, decode), chained by events
+    int chunks;                     // 0 = choose by size and world, n = cut every call into n pieces
+    cudaStream_t s_reduce, s_finish;
+    cudaEvent_t ev_start, ev_done, ev_sent[kMaxChunks], ev_reduced[kMaxChunks];
+    bool pipe_ready;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
@@ -176,17 +192,18 @@ __device__ __forceinline__ void store8(float *p, int64_t i0, int64_t n, const fl
 // ---- phase 1: sender ---------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
-                 uint32_t epoch)
+                 uint32_t epoch, Chunk ch)
 {
     const uint32_t stride = gridDim.x * kThreads;
     const int lane = threadIdx.x & 31;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);      // a multiple of 32: warps never straddle shards
-    const uint32_t groups = uint32_t(geo.padded / 8);
-    // one flat loop over all groups; the owner index advances with the position
-    uint32_t g8 = blockIdx.x * kThreads + threadIdx.x;
-    uint32_t o = g8 / g_per_shard, in_shard = g8 - o * g_per_shard;
-    for (; g8 < groups; g8 += stride, in_shard += stride) {
-        while (in_shard >= g_per_shard) in_shard -= g_per_shard, o++;
+    const uint32_t total = uint32_t(geo.world) * ch.count;
+    // one flat loop over the piece's groups of all owners; the owner index advances with the position
+    uint32_t j = blockIdx.x * kThreads + threadIdx.x;
+    uint32_t o = j / ch.count, k = j - o * ch.count;
+    for (; j < total; j += stride, k += stride) {
+        while (k >= ch.count) k -= ch.count, o++;
+        const uint32_t in_shard = ch.first + k, g8 = o * g_per_shard + in_shard;
         uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
         const int64_t i0 = int64_t(g8) * 8;
         float v[8], dq[8];
@@ -210,7 +227,8 @@ wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res
         if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + in_shard / 4) = ex;
     }
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
-    signal_done(mine, &mine->counter[0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
+    signal_done(mine, &mine->counter[ch.index][0], peers, geo.world, geo.rank,
+                offsetof(Header, rs_flag) + ch.index * sizeof(mine->rs_flag[0]), epoch);
 }
 
 // ---- phase 2: owner ------------------------------------------------------------------
@@ -218,18 +236,19 @@ wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res
 // senders' slots are issued together before the first decode.  WORLD = 0: any size.
 template <int WORLD>
 __global__ void __launch_bounds__(kThreads)
-wire_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch, int reverse)
+wire_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch, int reverse,
+                   Chunk ch)
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
     const int world = WORLD ? WORLD : geo.world;
-    wait_flags(mine, mine->rs_flag, world, epoch, geo.poll_limit);
-    const uint32_t groups = uint32_t(geo.shard / 8);           // a multiple of 32
+    wait_flags(mine, mine->rs_flag[ch.index], world, epoch, geo.poll_limit);
+    const uint32_t groups = ch.first + ch.count;               // end of this piece inside the shard
     const uint32_t stride = gridDim.x * kThreads;
     const int lane = threadIdx.x & 31;
     const uint8_t *rs = my + geo.rs_off;
     const int64_t exp_off = geo.shard / 2;
-    for (uint32_t g8 = blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
+    for (uint32_t g8 = ch.first + blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
         float val[8], dq[8], r[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) val[i] = 0.0f;
@@ -289,7 +308,8 @@ wire_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom ge
             if (lane == 0) *reinterpret_cast<uint2 *>(slot + exp_off + g8 / 4) = ex;
         }
     }
-    signal_done(mine, &mine->counter[1], peers, world, geo.rank, offsetof(Header, ag_flag), epoch);
+    signal_done(mine, &mine->counter[ch.index][1], peers, world, geo.rank,
+                offsetof(Header, ag_flag) + ch.index * sizeof(mine->ag_flag[0]), epoch);
 }
 
 // ---- phase 3: everyone ---------------------------------------------------------------
@@ -299,14 +319,15 @@ wire_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom ge
 // folds into the block scale.  Otherwise an IEEE division (wire.py:138 `.div_(world)`).
 template <bool POW2>
 __global__ void __launch_bounds__(kThreads)
-wire_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch)
+wire_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch,
+                   Chunk ch)
 {
     constexpr int U = 4;                                        // independent quads in flight per thread
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->ag_flag, geo.world, epoch, geo.poll_limit);
+    wait_flags(mine, mine->ag_flag[ch.index], geo.world, epoch, geo.poll_limit);
     const uint32_t stride = gridDim.x * kThreads;
-    const uint32_t q_per_shard = uint32_t(geo.shard / 4);
+    const uint32_t q_first = 2 * ch.first, q_end = 2 * (ch.first + ch.count);   // this piece in quads of 4 elements
     const float w = float(geo.world), rw = 1.0f / w;
     const bool vec = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
     for (int o = 0; o < geo.world; o++) {
@@ -315,10 +336,10 @@ wire_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__ Wir
         const int64_t first = int64_t(o) * geo.shard;
         if (first >= n) break;
         const int64_t left = (n - first + 3) / 4;
-        const uint32_t count = left < int64_t(q_per_shard) ? uint32_t(left) : q_per_shard;
+        const uint32_t count = left < int64_t(q_end) ? uint32_t(left) : q_end;
         float *gs = g + first;
         const int64_t ns = n - first;                           // elements of g in this shard and beyond
-        for (uint32_t q0 = blockIdx.x * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
+        for (uint32_t q0 = q_first + blockIdx.x * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
             uint32_t pk[U], e8[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
@@ -474,7 +495,7 @@ wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__
         }
         store_q8<BITS>(peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes, in_shard, q);
     }
-    signal_done(mine, &mine->counter[0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
+    signal_done(mine, &mine->counter[0][0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
 }
 
 // phase 2: exact integer sum at the owner, owner grid, owner residual, push to everyone
@@ -485,7 +506,7 @@ wire_int_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeo
     constexpr int LIM = (1 << (BITS - 1)) - 1;
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->rs_flag, geo.world, epoch, geo.poll_limit);
+    wait_flags(mine, mine->rs_flag[0], geo.world, epoch, geo.poll_limit);
     const uint32_t groups = uint32_t(geo.shard / 8), stride = gridDim.x * kThreads;
     const int64_t first_chunk = int64_t(geo.rank) * (geo.shard / kChunk);
     const int64_t payload = geo.shard * (BITS / 8);
@@ -523,7 +544,7 @@ wire_int_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeo
             if ((threadIdx.x & 7) == 0) reinterpret_cast<float *>(slot + payload)[g8 / 8] = s2;
         }
     }
-    signal_done(mine, &mine->counter[1], peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
+    signal_done(mine, &mine->counter[0][1], peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
 }
 
 // phase 3: decode the gathered shards, divide by the world size
@@ -533,7 +554,7 @@ wire_int_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->ag_flag, geo.world, epoch, geo.poll_limit);
+    wait_flags(mine, mine->ag_flag[0], geo.world, epoch, geo.poll_limit);
     const uint32_t groups = uint32_t((n + 7) / 8), stride = gridDim.x * kThreads;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);
     const int64_t payload = geo.shard * (BITS / 8);
@@ -606,6 +627,8 @@ static int wire_create(int rank, int world, int64_t padded, int bits, void **out
     w->arena_bytes = size_t(w->g.mx_off + (bits ? int64_t(world) * (padded / kChunk) * 4 : 0));
     w->mapped = false;
     w->epoch = 0;
+    w->chunks = 0;
+    w->pipe_ready = false;
     for (int i = 0; i < kMaxWorld; i++) w->opened[i] = false, w->peers.arena[i] = nullptr;
     cudaError_t e = cudaGetDevice(&w->dev);
     if (e == cudaSuccess) e = cudaMalloc(&w->arena, w->arena_bytes);
@@ -628,6 +651,11 @@ extern "C" int ls_wire_destroy(void *h)
     cudaDeviceSynchronize();
     for (int i = 0; i < kMaxWorld; i++)
         if (w->opened[i]) cudaIpcCloseMemHandle(w->peers.arena[i]);
+    if (w->pipe_ready) {
+        cudaStreamDestroy(w->s_reduce), cudaStreamDestroy(w->s_finish);
+        cudaEventDestroy(w->ev_start), cudaEventDestroy(w->ev_done);
+        for (int c = 0; c < kMaxChunks; c++) cudaEventDestroy(w->ev_sent[c]), cudaEventDestroy(w->ev_reduced[c]);
+    }
     cudaFree(w->arena);
     delete w;
     return LS_OK;
@@ -674,52 +702,135 @@ extern "C" int ls_wire_map_local(void *h, void *const *wires)
     return LS_OK;
 }
 
+namespace {
+Chunk whole_shard(const Wire *w) { return Chunk{0, 0u, uint32_t(w->g.shard / 8)}; }
+
+int launch_send(Wire *w, const float *g, int64_t numel, float *res, Chunk ch, int ctas_per_sm, cudaStream_t st)
+{
+    wire_send_kernel<<<grid_for(int64_t(w->g.world) * ch.count, ctas_per_sm), kThreads, 0, st>>>(g, numel, res, w->g, w->peers,
+                                                                                               w->epoch, ch);
+    LS_LAUNCH_CHECK("wire_send");
+    return LS_OK;
+}
+
+int launch_reduce(Wire *w, float *ores, int reverse, Chunk ch, int ctas_per_sm, cudaStream_t st)
+{
+    const int grid = grid_for(ch.count, ctas_per_sm);
+    switch (w->g.world) {
+    case 1: wire_reduce_kernel<1><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
+    case 2: wire_reduce_kernel<2><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
+    case 4: wire_reduce_kernel<4><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
+    case 8: wire_reduce_kernel<8><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
+    default: wire_reduce_kernel<0><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
+    }
+    LS_LAUNCH_CHECK("wire_reduce");
+    return LS_OK;
+}
+
+int launch_finish(Wire *w, float *g, int64_t numel, Chunk ch, int ctas_per_sm, cudaStream_t st)
+{
+    const bool pow2 = (w->g.world & (w->g.world - 1)) == 0;
+    const int grid = grid_for((int64_t(w->g.world) * ch.count + 1) / 2, ctas_per_sm);    // four quads per thread and step
+    if (pow2) wire_finish_kernel<true><<<grid, kThreads, 0, st>>>(g, numel, w->g, w->peers, w->epoch, ch);
+    else wire_finish_kernel<false><<<grid, kThreads, 0, st>>>(g, numel, w->g, w->peers, w->epoch, ch);
+    LS_LAUNCH_CHECK("wire_finish");
+    return LS_OK;
+}
+
+int pipe_setup(Wire *w)
+{
+    if (w->pipe_ready) return LS_OK;
+    LS_CUDA(cudaStreamCreateWithFlags(&w->s_reduce, cudaStreamNonBlocking));
+    LS_CUDA(cudaStreamCreateWithFlags(&w->s_finish, cudaStreamNonBlocking));
+    LS_CUDA(cudaEventCreateWithFlags(&w->ev_start, cudaEventDisableTiming));
+    LS_CUDA(cudaEventCreateWithFlags(&w->ev_done, cudaEventDisableTiming));
+    for (int c = 0; c < kMaxChunks; c++) {
+        LS_CUDA(cudaEventCreateWithFlags(&w->ev_sent[c], cudaEventDisableTiming));
+        LS_CUDA(cudaEventCreateWithFlags(&w->ev_reduced[c], cudaEventDisableTiming));
+    }
+    w->pipe_ready = true;
+    return LS_OK;
+}
+
+// Pieces per call.  One unless the caller asks for more: on 1 and 2 GPUs the three phases
+// of concurrent pieces compete for HBM (64 Mi elements, error feedback on: 312 -> 356 us
+// alone, 284 -> 349 us with one peer at four pieces), which costs more than the hidden
+// exchange latency saves.
+int pieces_of(const Wire *w)
+{
+    const int64_t groups = w->g.shard / 8;
+    int c = w->chunks > 0 ? w->chunks : 1;
+    while (c > 1 && groups % (int64_t(c) * 32) != 0) c--;
+    return c;
+}
+}  // namespace
+
 extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, void *stream)
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
     w->epoch++;
-    wire_send_kernel<<<grid_for(w->g.padded / 8, 5), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        g, numel, res, w->g, w->peers, w->epoch);
-    LS_LAUNCH_CHECK("wire_send");
-    return LS_OK;
+    return launch_send(w, g, numel, res, whole_shard(w), 5, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
 {
     Wire *w = as_wire(h);
     if (!w || !w->mapped) return fail(LS_ESTATE, "wire not ready");
-    const int grid = grid_for(w->g.shard / 8, 4);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    switch (w->g.world) {
-    case 1: wire_reduce_kernel<1><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
-    case 2: wire_reduce_kernel<2><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
-    case 4: wire_reduce_kernel<4><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
-    case 8: wire_reduce_kernel<8><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
-    default: wire_reduce_kernel<0><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse); break;
-    }
-    LS_LAUNCH_CHECK("wire_reduce");
-    return LS_OK;
+    return launch_reduce(w, ores, reverse, whole_shard(w), 4, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ls_wire_finish(void *h, float *g, int64_t numel, void *stream)
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
-    const bool pow2 = (w->g.world & (w->g.world - 1)) == 0;
-    const int grid = grid_for((numel + 15) / 16);        // four quads per thread and step
-    if (pow2) wire_finish_kernel<true><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(g, numel, w->g, w->peers, w->epoch);
-    else wire_finish_kernel<false><<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(g, numel, w->g, w->peers, w->epoch);
-    LS_LAUNCH_CHECK("wire_finish");
+    return launch_finish(w, g, numel, whole_shard(w), 8, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ls_wire_set_chunks(void *h, int chunks)
+{
+    Wire *w = as_wire(h);
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    if (chunks < 0 || chunks > kMaxChunks) return fail(LS_EINVAL, "chunks must be 0 (choose) or 1..%d", kMaxChunks);
+    w->chunks = chunks;
     return LS_OK;
 }
 
 extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, float *ores, int reverse,
                                  void *stream)
 {
-    if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
-    if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
-    return ls_wire_finish(h, g, numel, stream);
+    Wire *w = as_wire(h);
+    if (int rc = check_call(w, g, numel)) return rc;
+    const int pieces = pieces_of(w);
+    if (pieces == 1) {
+        if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
+        if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
+        return ls_wire_finish(h, g, numel, stream);
+    }
+    // Send pieces follow each other on the caller's stream; the owner phase of piece c
+    // runs on a second stream once piece c is sent, its decode on a third once it is
+    // reduced here.  The grids leave room for the three kernels to be resident together:
+    // a kernel that waits for its peers must not keep the others off the SMs.
+    if (int rc = pipe_setup(w)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    w->epoch++;
+    const uint32_t per = uint32_t(w->g.shard / 8 / pieces);
+    LS_CUDA(cudaEventRecord(w->ev_start, st));
+    LS_CUDA(cudaStreamWaitEvent(w->s_reduce, w->ev_start, 0));     // residuals and g are ready when the caller's stream says so
+    LS_CUDA(cudaStreamWaitEvent(w->s_finish, w->ev_start, 0));
+    for (int c = 0; c < pieces; c++) {
+        const Chunk ch{c, uint32_t(c) * per, per};
+        if (int rc = launch_send(w, g, numel, res, ch, 3, st)) return rc;
+        LS_CUDA(cudaEventRecord(w->ev_sent[c], st));
+        LS_CUDA(cudaStreamWaitEvent(w->s_reduce, w->ev_sent[c], 0));
+        if (int rc = launch_reduce(w, ores, reverse, ch, 2, w->s_reduce)) return rc;
+        LS_CUDA(cudaEventRecord(w->ev_reduced[c], w->s_reduce));
+        LS_CUDA(cudaStreamWaitEvent(w->s_finish, w->ev_reduced[c], 0));
+        if (int rc = launch_finish(w, g, numel, ch, 2, w->s_finish)) return rc;
+    }
+    LS_CUDA(cudaEventRecord(w->ev_done, w->s_finish));
+    LS_CUDA(cudaStreamWaitEvent(st, w->ev_done, 0));
+    return LS_OK;
 }
 
 // Integer wires: phase 0 publish maxima, 1 send, 2 reduce, 3 finish.

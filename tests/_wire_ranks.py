@@ -16,6 +16,7 @@ sys.path.insert(0, str(ROOT))
 os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
 from lockstep_b200 import wire          # noqa: E402
+from lockstep_b200._lib import check, lib   # noqa: E402
 from oracle import cref                 # noqa: E402
 
 
@@ -29,8 +30,10 @@ def student_t(n, seed):
 def main():
     rank, world, dev = wire.init()
     n = int(sys.argv[1]) if len(sys.argv) > 1 else 1_000_003
-    for method in ("mxfp4", "mxfp4ef"):
+    for method, pieces in (("mxfp4", 0), ("mxfp4ef", 0), ("mxfp4ef", 4)):
         w = wire.Wire(method, n, world, rank)
+        if pieces:                       # the pipelined form (as many pieces, up to 4, as divide the shard)
+            check(lib().ls_wire_set_chunks(w._handle(dev), pieces))
         ef = method == "mxfp4ef"
         res_c = [np.zeros(w._kpadded, np.float32) for _ in range(world)] if ef else None
         ores_c = [np.zeros(w._kpadded // world, np.float32) for _ in range(world)] if ef else None

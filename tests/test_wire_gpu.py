@@ -99,6 +99,37 @@ def test_wire_object_one_rank(wire):
         w.close()
 
 
+@pytest.mark.parametrize("pieces", [4, 8, 3])
+def test_pipelined_pieces_do_not_change_anything(wire, pieces):
+    # the all-reduce cut into pieces over three streams: same g, residuals and wire bytes
+    # as the single-piece call, step after step (one rank: the waits are met by this GPU's
+    # own earlier kernels, so nothing waits for a later launch)
+    from lockstep_b200 import _lib
+    L = _lib.lib()
+    n = (1 << 20) + 4096                   # shard = 262144 * 4 + 4096: divisible by 8 * 32 * 4 and * 8, not by 3
+    gen = torch.Generator().manual_seed(5)
+    steps = [torch.randn(n, generator=gen) * 1e-3 for _ in range(3)]
+    outs = []
+    for c in (1, pieces):
+        w = wire.Wire("mxfp4ef", n)
+        h = w._handle(torch.device("cuda", 0))
+        assert L.ls_wire_set_chunks(h, c) == 0
+        per = []
+        for g in steps:
+            x = g.clone().cuda()
+            w(x)
+            per.append((x.cpu(), w.res.cpu().clone(), w.ores.cpu().clone()))
+        w.status()
+        w.close()
+        outs.append(per)
+    for a, b in zip(*outs):
+        assert all(torch.equal(x, y) for x, y in zip(a, b))
+    w = wire.Wire("mxfp4ef", n)
+    h = w._handle(torch.device("cuda", 0))
+    assert L.ls_wire_set_chunks(h, 9) < 0 and L.ls_wire_set_chunks(h, -1) < 0
+    w.close()
+
+
 @pytest.mark.parametrize("method,tol", [("bf16", 1e-2), ("int16", 2e-4), ("int8", 3e-2), ("mxfp4", 0.2)])
 def test_one_rank_error(wire, method, tol):
     # reference tests/test_wire.py:26-30
