@@ -74,6 +74,17 @@ int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int b
 int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
                         uint8_t *packed, float *scale, uint8_t *sf, void *stream);
 
+/* Both orientations of one tensor from one read of x [R, C]: what
+ * ls_quantize_mxfp4 (packed + scale-factor bytes of x, blocks along C) and
+ * ls_quantize_mxfp4_t (of x^T, blocks along R) would write.  For a linear layer
+ * whose forward GEMM contracts over C and whose weight-gradient GEMM contracts
+ * over R (lockstep quantizes x and x.t().contiguous() separately).
+ * R % 128 == 0, C % 128 == 0; all four outputs required.
+ *   row_packed [R, C/2], row_sf ls_sf_bytes(R, C); t_packed [C, R/2], t_sf ls_sf_bytes(C, R) */
+int ls_quantize_mxfp4_both(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
+                           uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
+                           void *stream);
+
 /* Replaces fp4.py:43-54 (_round_to_e2m1) on values already divided by their
  * scale: q fp32 [n] -> codes [n]. */
 int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *codes, void *stream);

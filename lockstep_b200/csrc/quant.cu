@@ -254,12 +254,15 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 template <typename T, bool RNE>
 __global__ void __launch_bounds__(kThreads)
 quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__restrict__ packed,
-                  float *__restrict__ scale, uint8_t *__restrict__ sf)
+                  float *__restrict__ scale, uint8_t *__restrict__ sf, uint8_t *__restrict__ row_packed,
+                  uint8_t *__restrict__ row_sf)
 {
-    // A tile sits in shared memory as rows of 16-byte chunks, each group of 32 rows
-    // rotated by two more chunks: the column reads below (4 row groups x 8 columns per
-    // warp) then fall on different banks without padding, and the row writes stay
-    // 16-byte vectors.
+    // A tile sits in shared memory as rows of 16-byte chunks.  Row r is rotated by
+    // 2 * (r / 32) + r % 8 chunks: the column reads below (4 row groups x 8 columns per
+    // warp, all lanes at the same r % 8) and the row reads of the row-wise outputs (8
+    // consecutive rows per quarter warp) then fall on different banks without padding,
+    // and the row writes stay 16-byte vectors.
+    auto rot = [](int r) { return 2 * (r >> 5) + (r & 7); };
     constexpr int VEC = 16 / sizeof(T);                          // elements per 16-byte chunk
     constexpr int TC = kTRowBytes / sizeof(T);                   // tile columns
     constexpr int CHUNKS = TC / VEC;                             // per tile row
@@ -272,7 +275,7 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
 #pragma unroll
         for (int i = threadIdx.x; i < kTR * CHUNKS; i += kThreads) {
             const int r = i / CHUNKS, ch = i % CHUNKS, cc = ch * VEC;
-            uint4 *dst = buf + r * CHUNKS + ((ch + 2 * (r >> 5)) & (CHUNKS - 1));
+            uint4 *dst = buf + r * CHUNKS + ((ch + rot(r)) & (CHUNKS - 1));
             const T *src = x + (r0 + r) * C + c0 + cc;
             if (vec_ok && c0 + cc + VEC <= C) {
                 cp_async16(dst, src);
@@ -327,10 +330,10 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
             static_assert(sizeof(T) != 2 || 4 * (TC / 2) == kThreads, "one item per thread");
             const uint32_t *tile32 = reinterpret_cast<const uint32_t *>(tile);
             const int rb = threadIdx.x & 3, cp = threadIdx.x >> 2;
-            const int posw = (cp + 2 * VEC / 2 * rb) & (TC / 2 - 1);   // word of this column pair in the rotated rows
             uint32_t w[32];
 #pragma unroll
-            for (int i = 0; i < 32; i++) w[i] = tile32[(rb * 32 + i) * (TC / 2) + posw];
+            for (int i = 0; i < 32; i++)      // word of this column pair in row rb * 32 + i, rotated by 4 words per chunk
+                w[i] = tile32[(rb * 32 + i) * (TC / 2) + ((cp + 4 * (2 * rb + (i & 7))) & (TC / 2 - 1))];
             __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
 #pragma unroll
             for (int i = 1; i < 32; i++) m = __hmax2_nan(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
@@ -358,12 +361,11 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
 #pragma unroll
             for (int item = threadIdx.x; item < 4 * TC; item += kThreads) {
                 const int rb = item & 3, c = item >> 2;              // 4 blocks of 32 per column
-                const int pos = (c + 2 * VEC * rb) & (TC - 1);       // this column inside the rotated rows of group rb
                 float q[32];
                 uint32_t amax = 0;
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    q[i] = float(tile[(rb * 32 + i) * TC + pos]);
+                for (int i = 0; i < 32; i++) {                       // this column inside the rotated row rb * 32 + i
+                    q[i] = float(tile[(rb * 32 + i) * TC + ((c + VEC * (2 * rb + (i & 7))) & (TC - 1))]);
                     amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
                 }
                 const uint32_t e8 = block_e8m0(amax);
@@ -378,6 +380,56 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
                     else pk[h] = codes8<RNE>(v);
                 }
                 emit(c0 + c, rb, e8, pk);
+            }
+        }
+        if (row_packed) {
+            // Row-wise MXFP4 of the same tile (blocks of 32 along a row), for callers that
+            // need both orientations of one tensor: x is read from HBM once.
+            constexpr int BLKS = TC / 32, CPB = 32 / VEC;            // blocks per tile row, chunks per block
+            const uint4 *tile4 = tile_smem + b * kTR * CHUNKS;
+#pragma unroll
+            for (int item = threadIdx.x; item < kTR * BLKS; item += kThreads) {
+                const int blk = item / kTR, r = item % kTR;          // a warp: 32 consecutive rows, one block each
+                float q[32];
+                uint32_t amax = 0;
+#pragma unroll
+                for (int j = 0; j < CPB; j++) {
+                    const uint4 v = tile4[r * CHUNKS + ((blk * CPB + j + rot(r)) & (CHUNKS - 1))];
+                    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        if constexpr (sizeof(T) == 2) {
+                            q[j * 8 + 2 * k] = __uint_as_float(u[k] << 16);
+                            q[j * 8 + 2 * k + 1] = __uint_as_float(u[k] & 0xFFFF0000u);
+                        } else {
+                            q[j * 4 + k] = __uint_as_float(u[k]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++) amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
+                const uint32_t e8 = block_e8m0(amax);
+                const bool finite = amax < kBitsInf;
+                // bf16 values: the shortened reciprocal scale gives the reference's rounding
+                // through the round-to-nearest-even converter (see the column path above)
+                const bool fold = sizeof(T) == 2 && !RNE && finite;
+                const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u
+                                                  : fold     ? (((253u - e8) << 23) | 0x7FF000u)
+                                                             : inv_scale_bits(e8));
+                uint32_t pk[4];
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = q[8 * h + i] * inv;
+                    if (!finite) pk[h] = codes8<RNE>(v);
+                    else pk[h] = (RNE || sizeof(T) == 2) ? cvt_e2m1x8(v) : cvt_ref_e2m1x8(v);
+                }
+                const int64_t row = r0 + r, col = c0 + 32 * blk;
+                if (col < C) {
+                    *reinterpret_cast<uint4 *>(row_packed + row * (C / 2) + col / 2) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    row_sf[sf_offset(uint32_t(row), uint32_t(col / 32), uint32_t(C / 128))] = uint8_t(e8);
+                }
             }
         }
         __syncthreads();                                         // this buffer is refilled by the next iteration's copies
@@ -676,8 +728,9 @@ extern "C" int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *c
     return LS_OK;
 }
 
-extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
-                                   uint8_t *packed, float *scale, uint8_t *sf, void *stream)
+namespace {
+int quantize_t_impl(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, uint8_t *packed, float *scale,
+                    uint8_t *sf, uint8_t *row_packed, uint8_t *row_sf, void *stream)
 {
     if (int rc = check_device()) return rc;
     if (x_dtype != LS_F32 && x_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported dtype %d", x_dtype);
@@ -706,7 +759,7 @@ extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_
     auto launch = [&](auto kernel, auto xp, int tile_cols) -> int {
         const int64_t tiles = ((C + tile_cols - 1) / tile_cols) * (R / kTR);
         const int64_t cap = int64_t(sm_count()) * 3;             // three resident CTAs per SM (64 KB each)
-        kernel<<<unsigned(tiles < cap ? tiles : cap), kThreads, kTSmem, st>>>(xp, R, C, packed, scale, sf);
+        kernel<<<unsigned(tiles < cap ? tiles : cap), kThreads, kTSmem, st>>>(xp, R, C, packed, scale, sf, row_packed, row_sf);
         return LS_OK;
     };
     int rc;
@@ -722,4 +775,21 @@ extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_
     if (rc) return rc;
     LS_LAUNCH_CHECK("quantize_mxfp4_t");
     return LS_OK;
+}
+}  // namespace
+
+extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
+                                   uint8_t *packed, float *scale, uint8_t *sf, void *stream)
+{
+    return quantize_t_impl(x, x_dtype, R, C, rounding, packed, scale, sf, nullptr, nullptr, stream);
+}
+
+extern "C" int ls_quantize_mxfp4_both(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
+                                      uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
+                                      void *stream)
+{
+    if (C % 128 != 0) return fail(LS_EINVAL, "C=%lld must be a multiple of 128", (long long)C);
+    if (!row_packed || !row_sf || !t_packed || !t_sf) return fail(LS_EINVAL, "null output");
+    if (!aligned16(row_packed)) return fail(LS_EALIGN, "row_packed must be 16-byte aligned");
+    return quantize_t_impl(x, x_dtype, R, C, rounding, t_packed, nullptr, t_sf, row_packed, row_sf, stream);
 }

@@ -102,6 +102,24 @@ def quantize_mxfp4_packed_t(x: torch.Tensor, rounding: str = "ref", want_scale: 
     return (packed, sf, scale) if want_scale else (packed, sf)
 
 
+def quantize_mxfp4_both(x: torch.Tensor, rounding: str = "ref"):
+    """(extension) quantize_mxfp4_packed(x) and quantize_mxfp4_packed_t(x) from one read
+    of x [R, C]: returns (packed, sf, packed_t, sf_t).  R % 128 == 0 and C % 128 == 0."""
+    need_cuda(x)
+    assert x.dim() == 2 and x.shape[0] % 128 == 0 and x.shape[1] % 128 == 0, "both dimensions must be multiples of 128"
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.float()
+    x = aligned(x)
+    R, C = x.shape
+    packed = torch.empty((R, C // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(R, C), dtype=torch.uint8, device=x.device)
+    packed_t = torch.empty((C, R // 2), dtype=torch.uint8, device=x.device)
+    sf_t = torch.empty(sf_bytes(C, R), dtype=torch.uint8, device=x.device)
+    check(lib().ls_quantize_mxfp4_both(ptr(x), _lib.dtype_code(x.dtype), R, C, _ROUNDING[rounding],
+                                       ptr(packed), ptr(sf), ptr(packed_t), ptr(sf_t), stream()))
+    return packed, sf, packed_t, sf_t
+
+
 def sf_bytes(rows: int, K: int) -> int:
     """(extension) Size of the scale-factor buffer of a [rows, K] operand."""
     return int(lib().ls_sf_bytes(rows, K))

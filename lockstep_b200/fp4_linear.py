@@ -11,6 +11,8 @@ Backward, two modes:
   "mxfp4"  (extension) both backward GEMMs in MXFP4 too: dX contracts over the
            output features, so gy and w.T are quantized along that axis; dW
            contracts over tokens, so gy.T and x.T are quantized along tokens.
+           Each tensor is read once: one kernel emits both orientations, and
+           the forward keeps packed x.T and w.T for the backward instead of x.
 
 There is no CPU path: on a device without block-scaled tensor cores the
 forward raises.
@@ -59,27 +61,43 @@ def _quant_t(x):
     return fp4.quantize_mxfp4_packed(x.t().contiguous())
 
 
+def _quant_both(x):
+    """(packed, sf) of x and of x.T; one read of x when both dimensions allow it."""
+    if x.shape[0] % 128 == 0 and x.shape[1] % 128 == 0:
+        p, s, pt, st = fp4.quantize_mxfp4_both(x)
+        return (p, s), (pt, st)
+    return fp4.quantize_mxfp4_packed(x), _quant_t(x)
+
+
 class _MXFP4Matmul(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, backward_mode="ste"):
-        ctx.save_for_backward(x, w)
         ctx.backward_mode = backward_mode
-        return _gemm(x, w, x.dtype)
+        if backward_mode == "ste" or not any(ctx.needs_input_grad[:2]):
+            ctx.save_for_backward(x, w)
+            ctx.backward_mode = "ste"
+            return _gemm(x, w, x.dtype)
+        # MXFP4 backward: both orientations of x and w come out of the forward's own read
+        # of them; what is kept for the backward pass is packed MXFP4, not x itself
+        k = _need_kernel()
+        (px, sx), (pxt, sxt) = _quant_both(x)                     # x along K; x.T along tokens (for dW)
+        (pw, sw), (pwt, swt) = _quant_both(w)                     # w along K; w.T along N (for dX)
+        ctx.save_for_backward(pxt, sxt, pwt, swt)
+        ctx.dtypes = (x.dtype, w.dtype)
+        return k(px, pw, sx, sw, out_dtype=x.dtype)
 
     @staticmethod
     def backward(ctx, gy):
-        x, w = ctx.saved_tensors
         if ctx.backward_mode == "ste":
+            x, w = ctx.saved_tensors
             return (gy @ w.to(gy.dtype)).to(x.dtype), (gy.t() @ x.to(gy.dtype)).to(w.dtype), None
         k = _need_kernel()
-        gy = gy.contiguous()
-        pg, sg = fp4.quantize_mxfp4_packed(gy)                    # gy along N
-        pwt, swt = _quant_t(w)                                    # w.T along N
-        gx = k(pg, pwt, sg, swt, out_dtype=x.dtype)               # [T, K], contract over N
-        pgt, sgt = _quant_t(gy)                                   # gy.T along tokens
-        pxt, sxt = _quant_t(x)                                    # x.T along tokens
+        pxt, sxt, pwt, swt = ctx.saved_tensors
+        x_dtype, w_dtype = ctx.dtypes
+        (pg, sg), (pgt, sgt) = _quant_both(gy.contiguous())       # gy along N (for dX); gy.T along tokens (for dW)
+        gx = k(pg, pwt, sg, swt, out_dtype=x_dtype)               # [T, K], contract over N
         gw = k(pgt, pxt, sgt, sxt, out_dtype=torch.float32)       # [N, K], contract over tokens
-        return gx, gw.to(w.dtype), None
+        return gx, gw.to(w_dtype), None
 
 
 class MXFP4Linear(nn.Linear):

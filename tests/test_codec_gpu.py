@@ -227,6 +227,28 @@ def test_transposed_quantizer_equals_quantizer_of_transpose(fp4, dtype, R, C, go
     assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,C", [(128, 128), (256, 384), (1024, 4096), (4096, 1024)])
+def test_both_orientations_from_one_read(fp4, dtype, R, C, golden):
+    # one kernel, x read once: bit-identical to the row-wise and the transposed quantizer
+    g = torch.Generator().manual_seed(R * 3 + C)
+    x = torch.randn(R, C, generator=g) * torch.exp2(torch.randint(-20, 20, (R, 1), generator=g).float())
+    x = torch.where(torch.rand(R, C, generator=g) < 0.01, x * 50, x)
+    if R == 128:                                   # adversarial rows of the golden set (ties, exponent quirk, inf)
+        adv = torch.from_numpy(golden("quant_adversarial_f32")["x"].view(np.float32).copy()).reshape(-1)
+        k = min(R, adv.numel() // C)
+        x[:k] = adv[:k * C].reshape(k, C)
+    x = x.to(dtype).cuda()
+    for rounding in ("ref", "rne"):
+        p, s, pt, st = fp4.quantize_mxfp4_both(x, rounding)
+        p1, s1 = fp4.quantize_mxfp4_packed(x, rounding=rounding)
+        p2, s2 = fp4.quantize_mxfp4_packed_t(x, rounding=rounding)
+        assert torch.equal(p, p1) and torch.equal(pt, p2)
+        assert torch.equal(s, s1) and torch.equal(st, s2)          # both dimensions are multiples of 128: no padding bytes
+    with pytest.raises(AssertionError):
+        fp4.quantize_mxfp4_both(x[:, :96].contiguous())
+
+
 def test_fp32_exponent_rule_on_gpu(fp4):
     # block maxima a few ulps below powers of two: fp32 log2 rounds up
     vals = []
