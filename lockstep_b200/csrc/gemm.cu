@@ -813,7 +813,8 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     return LS_OK;
 }
 
-int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
+int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel (256-column tiles), 2 = CTA-pair kernel,
+                                 // 3 = single-CTA kernel with 128-column tiles
 int g_gemm_splits = 0;           // 0 = choose by shape, n = split K n ways where splitting is allowed
 
 // Per-device scratch for split-K partial sums; grows on demand and is kept.  One buffer
@@ -894,11 +895,15 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     const bool caller_err = err != nullptr;
     if (!err) err = error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
-    const int bn = 256;
     CUtensorMap ta0, ta1, tb;
     if (int rc = make_operand_map(&ta0, a0, M, K / 2, BM)) return rc;
     if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, BM)) return rc;
     const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && (nbatch == 2 || M > BM));
+    // Single-CTA kernel: 128-column tiles when 256-column tiles would leave more than half
+    // the SMs without one (the weight stream of a short-M product needs the SMs' loads in
+    // flight more than it needs wide tiles).
+    const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256) * nbatch;
+    const int bn = pair ? 256 : (g_gemm_variant == 3 || (g_gemm_variant == 0 && tiles256 * 2 <= sm_count())) ? 128 : 256;
     if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
@@ -935,7 +940,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
             // Pays only with a quarter of the CTA pairs busy and a long K (weight gradients
             // of small layers): the partial slabs and the second kernel cost about 10 us.
             if (tiles * 4 <= slots && k_tiles >= 32) s = std::min(slots / tiles, k_tiles / 8);
-        } else if (M <= 32 && tiles * 2 <= slots && k_tiles >= 4) {                 // partial traffic grows with M
+        } else if (M <= 32 && tiles * 2 <= slots && k_tiles >= 32) {                // partial traffic grows with M; K >= 8192
             s = std::min(slots / tiles, k_tiles / 2);
         }
         s = std::max(1, std::min(std::min(s, 16), k_tiles));
@@ -951,7 +956,9 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     if (pair) {
         if (int rc = launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
     } else {
-        if (int rc = launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
+        if (int rc = bn == 128 ? launch<128>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))
+                               : launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream)))
+            return rc;
     }
     if (p.splits > 1) {
         for (int b = 0; b < nbatch; b++) {
@@ -997,7 +1004,7 @@ extern "C" int ls_gemm_status(int *status_host)
 
 extern "C" int ls_gemm_set_variant(int variant)
 {
-    if (variant < 0 || variant > 2) return fail(LS_EINVAL, "variant must be 0, 1 or 2");
+    if (variant < 0 || variant > 3) return fail(LS_EINVAL, "variant must be 0..3");
     g_gemm_variant = variant;
     return LS_OK;
 }
