@@ -64,6 +64,7 @@ struct GemmParams {
     uint8_t *q_sf[2];              // scale-factor bytes of a [M, N] operand
     int act;                       // 0 none, 1 GELU (erf form)
     int store_c;                   // 0: C itself is not written (only its quantized form)
+    int a_box_bytes;               // bytes one TMA load of an A tile delivers (single-CTA kernel: rows of the box x 128)
 };
 
 // MXFP4 of one row's 32 consecutive outputs (exactly one scale block), as the next GEMM
@@ -325,7 +326,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     const uint32_t st = smem_base + s * C::STAGE_BYTES;
                     // scale tiles of W rows past N do not exist; their products are never stored
                     const int b_atoms = min(BN / 128, n_atoms - nt * (BN / 128));
-                    ptx::mbar_expect_tx(full_bar(s), C::A_BYTES + C::B_BYTES + sf_bytes * (1 + b_atoms));
+                    ptx::mbar_expect_tx(full_bar(s), uint32_t(p.a_box_bytes) + C::B_BYTES + sf_bytes * (1 + b_atoms));
                     ptx::tma_load_2d(st, tma, kt * BKB, mt * BM, full_bar(s));
                     ptx::tma_load_2d(st + C::A_BYTES, &tm_b, kt * BKB, nt * BN, full_bar(s));
                     ptx::bulk_load(st + C::A_BYTES + C::B_BYTES, sfa + int64_t(kt) * 1024, sf_bytes, full_bar(s));
@@ -896,9 +897,17 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     if (!err) err = error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     CUtensorMap ta0, ta1, tb;
-    if (int rc = make_operand_map(&ta0, a0, M, K / 2, BM)) return rc;
-    if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, BM)) return rc;
     const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && (nbatch == 2 || M > BM));
+    // A tile of the single-CTA kernel: the box has only as many rows (16, 32, 64 or 128) as
+    // A has.  The other rows of the stage keep whatever shared memory held; an output row
+    // depends on its own row of A only, and rows past M are never stored.  (A 128-row box
+    // that is almost entirely out of bounds still fills 16 KB of shared memory per k-tile:
+    // 16384-squared went 36 -> 28 us at M = 1, 8192-squared 14.7 -> 10.0 us.)
+    int a_box_rows = BM;
+    if (!pair)
+        for (a_box_rows = 16; a_box_rows < M; a_box_rows *= 2) {}
+    if (int rc = make_operand_map(&ta0, a0, M, K / 2, a_box_rows)) return rc;
+    if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, a_box_rows)) return rc;
     // Single-CTA kernel: 128-column tiles when 256-column tiles would leave more than half
     // the SMs without one (the weight stream of a short-M product needs the SMs' loads in
     // flight more than it needs wide tiles).
@@ -919,6 +928,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     p.kt_per_split = int((K / 2 + BKB - 1) / BKB);
     p.partial = nullptr;
     p.store_c = c0 != nullptr;
+    p.a_box_bytes = a_box_rows * BKB;
     p.act = fused ? qe->act : 0;
     for (int b = 0; b < 2; b++) {
         p.q_packed[b] = fused ? qe->packed[nbatch == 2 ? b : 0] : nullptr;
