@@ -152,9 +152,9 @@ int ls_mxfp4_gemm_quant(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t
  * (cta_group::2).  Results are identical; for measurements and tests. */
 int ls_gemm_set_variant(int variant);
 
-/* K-splitting of the two GEMM entry points: 0 = by shape (default: shapes with
- * few output tiles and a long K, i.e. decode-like products and weight
- * gradients), 1 = never, 2..16 = that many splits.  A split product
+/* K-splitting of the two GEMM entry points: 0 = by shape (default: products of
+ * more than 128 rows with few output tiles and a long K, i.e. weight gradients
+ * of small layers), 1 = never, 2..16 = that many splits.  A split product
  * accumulates each K range in fp32 on the tensor cores and sums the ranges in
  * ascending order in fp32 before the one rounding to out_dtype.  No reference
  * counterpart (dual_gemm.py:261-289 splits K with atomics); for measurements

@@ -950,9 +950,11 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
             // Pays only with a quarter of the CTA pairs busy and a long K (weight gradients
             // of small layers): the partial slabs and the second kernel cost about 10 us.
             if (tiles * 4 <= slots && k_tiles >= 32) s = std::min(slots / tiles, k_tiles / 8);
-        } else if (M <= 32 && tiles * 2 <= slots && k_tiles >= 32) {                // partial traffic grows with M; K >= 8192
-            s = std::min(slots / tiles, k_tiles / 2);
         }
+        // The single-CTA kernel does not split by itself: with 128-column tiles and an A box
+        // of M rows the unsplit launch was as fast or faster at every short-M shape measured
+        // (N = K = 2048 ... 16384; an in-kernel summation by the tile's last CTA was slower
+        // still: one CTA reads all slabs).
         s = std::max(1, std::min(std::min(s, 16), k_tiles));
     }
     if (s > 1) {

@@ -116,8 +116,8 @@ def test_ragged_shapes(mods, M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 2048, 8192), (100, 512, 2048), (128, 1000, 1152)])
-def test_skinny_shapes_split_k(mods, M, N, K):
-    # few tiles and a long K: the kernel splits K across SMs and sums fp32 partials
+def test_skinny_shapes(mods, M, N, K):
+    # few rows and a long K: 128-column tiles, an A box of only M rows (K splits are forced in the next test)
     fp4, mg, _ = mods
     g = torch.Generator().manual_seed(M + N)
     a = torch.randn(M, K, generator=g)
@@ -134,7 +134,7 @@ def test_skinny_shapes_split_k(mods, M, N, K):
     assert torch.equal(mg.mxfp4_gemm_packed(pa, pw, sfa, sfw), mg.mxfp4_gemm_packed(pa, pw, sfa, sfw))   # deterministic
 
 
-@pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2),
+@pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2), (3, 40, 300, 1152, 2),
                                                   (2, 300, 520, 4096, 5), (2, 1024, 1024, 16384, 0)])
 def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
     # power-of-two scales on an integer grid: every partial sum is exact, so a split
