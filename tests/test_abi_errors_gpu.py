@@ -32,6 +32,13 @@ def test_quantize_argument_errors(L):
     assert L.ls_quantize_mxfp4(_p(x, 2), 1, 2, 64, 32, 0, _p(out), None, None, None, None, None) == EALIGN
     assert b"aligned" in L.ls_last_error()
     assert L.ls_quantize_mxfp4(_p(x), 1, 0, 64, 32, 0, None, None, None, None, None, None) == 0              # empty: nothing to do
+    y = torch.zeros(128, 128, device="cuda", dtype=torch.bfloat16)
+    o = [torch.zeros(128 * 64, device="cuda", dtype=torch.uint8) for _ in range(4)]
+    assert L.ls_quantize_mxfp4_both(_p(y), 1, 128, 96, 0, _p(o[0]), _p(o[1]), _p(o[2]), _p(o[3]), None) == EINVAL   # C % 128
+    assert L.ls_quantize_mxfp4_both(_p(y), 1, 100, 128, 0, _p(o[0]), _p(o[1]), _p(o[2]), _p(o[3]), None) == EINVAL  # R % 128
+    assert L.ls_quantize_mxfp4_both(_p(y), 1, 128, 128, 0, _p(o[0]), None, _p(o[2]), _p(o[3]), None) == EINVAL      # all four outputs
+    assert L.ls_quantize_mxfp4_both(_p(y), 1, 128, 128, 0, _p(o[0], 8), _p(o[1]), _p(o[2]), _p(o[3]), None) == EALIGN
+    assert L.ls_quantize_mxfp4_both(_p(y), 1, 128, 128, 0, _p(o[0]), _p(o[1]), _p(o[2]), _p(o[3]), None) == 0
 
 
 def test_gemm_argument_errors(L):
@@ -44,7 +51,8 @@ def test_gemm_argument_errors(L):
     assert L.ls_mxfp4_gemm(_p(a, 4), _p(a), _p(a), _p(a), _p(c), 1, 128, 128, 128, None) == EALIGN
     assert L.ls_mxfp4_gemm(*args(128)[:6], 0, 128, 128, None) == 0                # M = 0
     assert L.ls_mxfp4_gemm_quant(_p(a), _p(a), _p(a), _p(a), _p(c), 1, 0, _p(a), _p(a), 128, 100, 128, None) == EINVAL   # N % 128
-    assert L.ls_gemm_set_variant(9) == EINVAL and L.ls_gemm_set_variant(0) == 0
+    assert L.ls_gemm_set_variant(9) == EINVAL and L.ls_gemm_set_variant(3) == 0 and L.ls_gemm_set_variant(0) == 0
+    assert L.ls_gemm_set_splits(17) == EINVAL and L.ls_gemm_set_splits(0) == 0
 
 
 def test_wire_argument_errors(L):
@@ -60,4 +68,5 @@ def test_wire_argument_errors(L):
     assert L.ls_wire_create(0, 1, 512, ctypes.byref(h)) == 0
     assert L.ls_wire_send(h, _p(g), 1024, None, None) == EINVAL                   # numel beyond the wire
     assert L.ls_wire_set_poll_limit(h, 0) == EINVAL
+    assert L.ls_wire_set_chunks(h, 9) == EINVAL and L.ls_wire_set_chunks(h, 0) == 0
     assert L.ls_wire_destroy(h) == 0
