@@ -392,6 +392,7 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
                 const int blk = item / kTR, r = item % kTR;          // a warp: 32 consecutive rows, one block each
                 float q[32];
                 uint32_t amax = 0;
+                __nv_bfloat162 m2 = __floats2bfloat162_rn(0.0f, 0.0f);   // bf16: |x| maxima on packed pairs, NaN-propagating
 #pragma unroll
                 for (int j = 0; j < CPB; j++) {
                     const uint4 v = tile4[r * CHUNKS + ((blk * CPB + j + rot(r)) & (CHUNKS - 1))];
@@ -399,15 +400,19 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         if constexpr (sizeof(T) == 2) {
+                            m2 = __hmax2_nan(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&u[k])));
                             q[j * 8 + 2 * k] = __uint_as_float(u[k] << 16);
                             q[j * 8 + 2 * k + 1] = __uint_as_float(u[k] & 0xFFFF0000u);
                         } else {
                             q[j * 4 + k] = __uint_as_float(u[k]);
+                            amax = max(amax, u[k] & 0x7FFFFFFFu);
                         }
                     }
                 }
-#pragma unroll
-                for (int i = 0; i < 32; i++) amax = max(amax, __float_as_uint(q[i]) & 0x7FFFFFFFu);
+                if constexpr (sizeof(T) == 2) {
+                    const uint32_t mb = *reinterpret_cast<uint32_t *>(&m2);
+                    amax = max(mb & 0xFFFF0000u, mb << 16);              // as fp32 bits
+                }
                 const uint32_t e8 = block_e8m0(amax);
                 const bool finite = amax < kBitsInf;
                 // bf16 values: the shortened reciprocal scale gives the reference's rounding
