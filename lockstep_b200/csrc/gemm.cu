@@ -905,7 +905,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     // 16384-squared went 36 -> 28 us at M = 1, 8192-squared 14.7 -> 10.0 us.)
     int a_box_rows = BM;
     if (!pair)
-        for (a_box_rows = 16; a_box_rows < M; a_box_rows *= 2) {}
+        for (a_box_rows = 16; a_box_rows < M && a_box_rows < BM; a_box_rows *= 2) {}
     if (int rc = make_operand_map(&ta0, a0, M, K / 2, a_box_rows)) return rc;
     if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, a_box_rows)) return rc;
     // Single-CTA kernel: 128-column tiles when 256-column tiles would leave more than half

@@ -134,7 +134,7 @@ def test_skinny_shapes(mods, M, N, K):
     assert torch.equal(mg.mxfp4_gemm_packed(pa, pw, sfa, sfw), mg.mxfp4_gemm_packed(pa, pw, sfa, sfw))   # deterministic
 
 
-@pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2), (3, 40, 300, 1152, 2),
+@pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2), (3, 40, 300, 1152, 2), (1, 700, 520, 1024, 1), (3, 300, 264, 512, 2),
                                                   (2, 300, 520, 4096, 5), (2, 1024, 1024, 16384, 0)])
 def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
     # power-of-two scales on an integer grid: every partial sum is exact, so a split
