@@ -128,6 +128,8 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     args.steps = min(args.steps, 5)          # each step is seconds of CPU work
+    # every host core this process may use (torchrun sets OMP_NUM_THREADS=1 for N > 1)
+    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = torch.get_num_threads()
     for _ in range(min(args.warmup, 1)):
         cpu_reference_step(CPU_SAMPLE_ROWS)
