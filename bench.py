@@ -9,14 +9,19 @@ MXFP4 on the fly and multiplied, in one launch, by one pre-quantized
 With N > 1 every rank runs this step on its own GPU (the GEMM path does not
 shard: replicas only) and the line reports the aggregate.
 
-Prints one JSON line (rank 0).  `value` is device-timed with inputs resident
-in HBM; `e2e` is the same step through the public Python API with pinned HOST
-buffers, host<->device copies inside the timed region.
+Prints one JSON line (rank 0).  `value` is device-timed over exactly K steps
+with inputs resident in HBM; every step carries three events (start, after the
+quantizer, after the GEMM), so quantize_ms + gemm_ms = ms_per_step.  The same
+loop then keeps running, still timed, until the GPU has been under this load
+for about half a second: `value_sustained`, the roofline figures and the clock
+record all come from that longer region.  `e2e` is the same step through the
+public Python API with pinned HOST buffers, host<->device copies inside the
+timed region.
 
 `--impl reference` times the reference's own CPU path for the same step
-(quantize both batches, dequantize, fp32 F.linear: what lockstep's
-fp4_linear.py runs anywhere but on an H100) on the host cores, on a bounded
-row sample of the batch.
+(quantize both batches, dequantize, fp32 F.linear -> bf16: what lockstep's
+fp4_linear.py runs anywhere but on an H100) on the host cores, on the full
+configuration.
 """
 
 import argparse
@@ -39,11 +44,13 @@ FLOPS_PER_STEP = 2 * 2 * M * N * K                      # two batches
 METRIC = "dual MXFP4 GEMM TFLOPS/GPU (% FP4 peak); FP4 all-reduce algbw GB/s @1/2/4/8"
 WORKLOAD = "dual-batch packed MXFP4 GEMM: 2 x [4096x8192 bf16, quantized on the fly] @ 8192x8192 MXFP4 W -> 2 x 4096x8192 bf16"
 FP4_SPEC_TFLOPS = 9000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one dual-GEMM launch on this workload, from the
-# ncu capture summarised in profiles/mxfp4_gemm_pair_dual_4096x8192x8192.md
+# DRAM bytes of one dual-GEMM launch on this workload (dram__bytes_read.sum + dram__bytes_write.sum of one
+# ncu capture of mxfp4_gemm_pair_kernel).  Not measured by this script: carried with its source.
 GEMM_DRAM_BYTES_PER_LAUNCH = 197.87e6
+GEMM_DRAM_BYTES_SOURCE = ("one ncu capture (--set full, 1 launch) of mxfp4_gemm_pair_kernel on this workload; "
+                          "carried as a constant, not re-measured in this run")
 GEMM_ALGORITHMIC_BYTES = 2 * (M * K // 2 + M * K // 32) + (N * K // 2 + N * K // 32) + 2 * M * N * 2
-CPU_SAMPLE_ROWS = 256                                   # rows per batch in the CPU-baseline sample
+SUSTAINED_SECONDS = 0.5                                 # length of the timed region the clock record covers
 
 
 def env_int(name, default):
@@ -102,81 +109,98 @@ class ClockSampler:
                 "samples": len(rows), "power_w_max": max(power) if power else None}
 
 
-def cpu_reference_step(rows, threads=None):
-    """The reference's CPU path for `rows` rows of each batch; returns
-    (seconds, flops).  Uses the oracle port: this leg is the one place the
-    benchmark may execute it."""
-    from oracle import ref_port
-    if threads:
-        torch.set_num_threads(threads)
-    g = torch.Generator().manual_seed(0)
-    x1 = torch.randn(rows, K, generator=g).bfloat16()
-    x2 = torch.randn(rows, K, generator=g).bfloat16()
-    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
-    wc, ws = ref_port.quantize(w)                          # W is pre-quantized in this configuration
-    t0 = time.perf_counter()
-    outs = []
-    for x in (x1, x2):
-        xc, xs = ref_port.quantize(x)
-        outs.append(torch.nn.functional.linear(ref_port.dequantize(xc, xs),
-                                               ref_port.dequantize(wc, ws)).to(torch.bfloat16))
-    dt = time.perf_counter() - t0
-    return dt, 2 * 2 * rows * N * K
+class CpuReference:
+    """The reference's CPU path for the benchmark step (fp4_linear.py:33-40 on the
+    non-H100 branch, with W quantized ahead of time as the workload states): per batch
+    quantize x, dequantize x and W, fp32 F.linear, cast to bf16.  Uses the oracle port,
+    which calls the same torch CPU kernels as the reference: this leg and the
+    `cpu_baseline` figure are the places the benchmark may execute it."""
+
+    def __init__(self, rows=M):
+        from oracle import ref_port
+        self.rp, self.rows = ref_port, rows
+        g = torch.Generator().manual_seed(0)
+        self.x = [torch.randn(rows, K, generator=g).bfloat16() for _ in range(2)]
+        w = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+        self.wc, self.ws = ref_port.quantize(w)                # W is pre-quantized in this configuration
+        self.flops = 2 * 2 * rows * N * K
+
+    def step(self):
+        t0 = time.perf_counter()
+        outs = []
+        for x in self.x:
+            xc, xs = self.rp.quantize(x)
+            outs.append(torch.nn.functional.linear(self.rp.dequantize(xc, xs),
+                                                   self.rp.dequantize(self.wc, self.ws)).to(torch.bfloat16))
+        return time.perf_counter() - t0
+
+    def sample(self):
+        if self.rows == M:
+            return (f"the full step: both {M}-row batches against the full {N}x{K} W, oracle port of "
+                    "fp4.py / fp4_linear.py on torch CPU")
+        return f"{self.rows} of {M} rows of each batch against the full W (not the full configuration)"
+
+
+def host_threads():
+    """Every host core this process may use (torchrun sets OMP_NUM_THREADS=1 for N > 1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    args.steps = min(args.steps, 5)          # each step is seconds of CPU work
-    # every host core this process may use (torchrun sets OMP_NUM_THREADS=1 for N > 1)
-    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
-    cores = torch.get_num_threads()
-    for _ in range(min(args.warmup, 1)):
-        cpu_reference_step(CPU_SAMPLE_ROWS)
-    times = []
-    flops = 0
-    for _ in range(args.steps):
-        dt, flops = cpu_reference_step(CPU_SAMPLE_ROWS)
-        times.append(dt)
+    cores = host_threads()
+    ref = CpuReference(args.ref_rows)
+    for _ in range(args.warmup):
+        ref.step()
+    times = [ref.step() for _ in range(args.steps)]
     t = sum(times) / len(times)
-    val = flops / t / 1e12
-    sample = f"{CPU_SAMPLE_ROWS} of {M} rows of each batch, full 8192x8192 W, oracle port of fp4.py/fp4_linear.py on torch CPU"
+    val = ref.flops / t / 1e12
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3 * (M / CPU_SAMPLE_ROWS),
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4 (e2m1 x ue8m0), fp32 accumulate",
-            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
-            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "data": "synthetic", "config": {"workload": WORKLOAD, "sample": ref.sample(),
+                                            "ms_per_step_median": statistics.median(times) * 1e3},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": ref.sample()},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def run_sweep(args):
+def run_sweep(m_list=(1, 16, 128, 4096, 16384), nk_list=(4096, 8192, 16384)):
     """Shape sweep of the single MXFP4 GEMM: M in {1, 16, 128, 4096, 16384}, N = K in
     {4096, 8192, 16384}; weights N(0, 0.02), activations N(0, 1) with 1 % of the entries
-    multiplied by 50.  One JSON line per shape: TFLOP/s, and for M <= 16 the fraction of
-    the bytes roofline (packed W + scales + A + output over the measured HBM peak)."""
+    multiplied by 50.  One dict per shape: TFLOP/s, and for M <= 16 the fraction of
+    the bytes roofline (packed W + scales + A + output over the measured HBM peak).
+    Launches are replayed from a CUDA graph (device time, not launch overhead); successive
+    launches walk through enough copies of the packed weight (> 256 MB together) that no
+    launch finds its weight in the 126 MB L2."""
     from lockstep_b200 import fp4, mxfp4_gemm
     dev = torch.device("cuda", 0)
     pk = peaks()
     g = torch.Generator(device=dev).manual_seed(0)
-    for nk in (4096, 8192, 16384):
+    lines = []
+    for nk in nk_list:
         w = (torch.randn(nk, nk, device=dev, generator=g) * 0.02).bfloat16()
         w_pk, w_sf = fp4.quantize_mxfp4_packed(w)
         del w
-        for m in (1, 16, 128, 4096, 16384):
+        ncopies = max(2, -(-(256 << 20) // (w_pk.numel() + w_sf.numel())))
+        w_pks = [w_pk] + [w_pk.clone() for _ in range(ncopies - 1)]
+        w_sfs = [w_sf] + [w_sf.clone() for _ in range(ncopies - 1)]
+        for m in m_list:
             a = torch.randn(m, nk, device=dev, generator=g)
             a = torch.where(torch.rand(m, nk, device=dev, generator=g) < 0.01, a * 50, a).bfloat16()
             a_pk, a_sf = fp4.quantize_mxfp4_packed(a)
-            for _ in range(3):
-                mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf)
-            reps = 20 if m <= 4096 else 5
-            # replayed as a CUDA graph so that small shapes show device time, not launch overhead
+            for i in range(3):
+                mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pks[i % ncopies], a_sf, w_sfs[i % ncopies])
+            reps = max(ncopies, 20) if m <= 4096 else 5
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize()
             with torch.cuda.graph(graph):
-                for _ in range(reps):
-                    c = mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf)
+                for i in range(reps):
+                    c = mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pks[i % ncopies], a_sf, w_sfs[i % ncopies])
             graph.replay()
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -184,15 +208,17 @@ def run_sweep(args):
             graph.replay()
             t1.record()
             torch.cuda.synchronize()
-            ms = t0.elapsed_time(t1) / reps
+            t_ms = t0.elapsed_time(t1) / reps
             del graph, c
             nbytes = nk * nk * 17 / 32 + m * nk * 17 / 32 + 2 * m * nk
-            line = {"shape": [m, nk, nk], "us": ms * 1e3, "tflops": 2 * m * nk * nk / ms / 1e9,
-                    "gbs": nbytes / ms / 1e6}
+            line = {"shape": [m, nk, nk], "us": t_ms * 1e3, "tflops": 2 * m * nk * nk / t_ms / 1e9,
+                    "gbs": nbytes / t_ms / 1e6}
             if m <= 16:
-                line["bytes_roofline_frac"] = nbytes / ms / 1e6 / pk["hbm"]
-            print(json.dumps(line), flush=True)
+                line["bytes_roofline_frac"] = nbytes / t_ms / 1e6 / pk["hbm"]
+            lines.append(line)
+        del w_pks, w_sfs
     mxfp4_gemm.gemm_status()
+    return lines
 
 
 def run_shape(m, n, k, out_f32, steps):
@@ -232,17 +258,147 @@ def run_shape(m, n, k, out_f32, steps):
                       "out_gbs": m * n * (4 if out_f32 else 2) / best / 1e6}), flush=True)
 
 
+def wire_leg(args, dev, rank, world, barrier, pk):
+    """FP4-compressed all-reduce of a 256 MiB fp32 gradient per rank, error feedback on.
+    Returns (dict for the line, kernel launches, [ms, send, reduce, finish] for the max over ranks)."""
+    import numpy as np
+    import torch.distributed as dist
+    from lockstep_b200 import wire
+    from oracle import cref                                   # checker of the correctness bit only
+
+    # ---- correctness bit, before and outside every timed region: two steps with error feedback on a
+    # 1 Mi-element buffer per rank against the CPU oracle of the protocol, and rank against rank
+    cn = 1 << 20
+    grads = []
+    for r in range(world):
+        gg = torch.Generator().manual_seed(1000 + r)
+        z = torch.randn(cn, generator=gg)
+        chi = (torch.randn(3, cn, generator=gg) ** 2).sum(0) / 3
+        grads.append((z / chi.sqrt() * 1e-3).float().numpy())
+    wchk = wire.Wire("mxfp4ef", cn, world, rank)
+    res_c = [np.zeros(wchk._kpadded, np.float32) for _ in range(world)]
+    ores_c = [np.zeros(wchk._kpadded // world, np.float32) for _ in range(world)]
+    exact = True
+    for step in range(2):
+        want, _, _ = cref.wire_step([g * (1 + step) for g in grads], res_c, ores_c, unit=256)
+        out = wchk(torch.from_numpy(grads[rank] * (1 + step)).to(dev))
+        exact = exact and bool(np.array_equal(out.cpu().numpy(), want))
+        if world > 1:
+            everyone = [torch.empty_like(out) for _ in range(world)]
+            dist.all_gather(everyone, out)
+            exact = exact and all(torch.equal(out, o) for o in everyone)
+    wchk.status()
+    wchk.close()
+    flag = torch.tensor([1.0 if exact else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    exact = bool(flag.item() == 1.0)
+
+    wn = (8 << 20) if args.small else (64 << 20)
+    wsteps = max(3, min(args.steps, 30))
+    gw = torch.Generator(device=dev).manual_seed(100 + rank)
+    z = torch.randn(wn, device=dev, generator=gw)
+    chi = torch.zeros(wn, device=dev)
+    for _ in range(3):
+        chi += torch.randn(wn, device=dev, generator=gw) ** 2
+    grad = z / (chi / 3).sqrt() * 1e-3                       # Student-t(3) * 1e-3
+    del z, chi
+    wobj = wire.Wire("mxfp4ef", wn, world, rank)
+    for _ in range(3):
+        wobj(grad)
+    wobj.status()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(wsteps):
+        wobj(grad)
+    b.record()
+    barrier()
+    wobj.status()
+    wire_ms = a.elapsed_time(b) / wsteps
+    # ---- per phase (three launches with an event between them; ranks aligned by a barrier before each step)
+    psteps = 10
+    pev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(psteps)]
+    for i in range(psteps):
+        barrier()
+        pev[i][0].record()
+        wobj.send(grad)
+        pev[i][1].record()
+        wobj.reduce()
+        pev[i][2].record()
+        wobj.finish(grad)
+        pev[i][3].record()
+    barrier()
+    wobj.status()
+    phases = [statistics.median(e[j].elapsed_time(e[j + 1]) for e in pev) for j in range(3)]
+    mode = wobj.mode_name()
+    wobj.close()
+    t = torch.tensor([wire_ms] + phases, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    wire_ms, send_ms, reduce_ms, finish_ms = t.tolist()
+    comp = wn * 0.53125                                      # packed + exponent bytes of one buffer
+    # per rank and step: send reads g, res and writes res, payload; reduce reads W payloads,
+    # ores, writes ores and W payloads; finish reads the payload and writes g
+    hbm = wn * (12 + 0.53125) + (wn / world) * (world * 0.53125 + 8 + world * 0.53125) + wn * (0.53125 + 4)
+    out = {
+        "method": "mxfp4ef", "world": world, "elements_per_rank": wn, "steps": wsteps, "mode": mode,
+        "bit_exact": exact, "bit_exact_check": "2 steps, 1 Mi elements per rank, error feedback: every rank's result "
+                                               "equals the CPU oracle of the protocol and every other rank's",
+        "ms": wire_ms, "algbw_gbs": wn * 4 / (wire_ms * 1e-3) / 1e9,
+        "link_busbw_gbs": 2 * (world - 1) / world * comp / (wire_ms * 1e-3) / 1e9,
+        "link_peak_gbs": 900.0, "hbm_bytes_per_rank": hbm,
+        "hbm_gbs": hbm / (wire_ms * 1e-3) / 1e9, "hbm_peak_gbs": pk["hbm"],
+        "hbm_frac": hbm / (wire_ms * 1e-3) / 1e9 / pk["hbm"],
+        "phases_ms": {"send": send_ms, "reduce_incl_wait": reduce_ms, "finish_incl_wait": finish_ms,
+                      "how": f"three separate launches, median of {psteps} steps, barrier before each step, max over ranks"},
+        "data": "Student-t(3) * 1e-3, seed 100 + rank"}
+    if world == 1 and not args.no_cpu_baseline:
+        cn = 8 << 20                                         # bounded sample of the 64 Mi buffer
+        rng = np.random.default_rng(100)
+        gc = (rng.standard_t(3, cn) * 1e-3).astype(np.float32)
+        res_c, ores_c = [np.zeros(cn, np.float32)], [np.zeros(cn, np.float32)]
+        cref.wire_step([gc], res_c, ores_c, unit=256)
+        t0 = time.perf_counter()
+        cref.wire_step([gc], res_c, ores_c, unit=256)
+        dt = time.perf_counter() - t0
+        out["cpu_baseline"] = {"algbw_gbs": cn * 4 / dt / 1e9, "cores": os.cpu_count(), "kind": "port",
+                               "sample": "8 Mi of 64 Mi elements, one rank, C oracle (OpenMP)"}
+    return out, 3 * (2 + 3 + wsteps + psteps)
+
+
+def copy_bandwidth(dev, hx, hc):
+    """Pinned-buffer copy rates of this rank alone in each direction, GB/s (context for `e2e`)."""
+    d = torch.empty_like(hx, device=dev)
+    out = {}
+    for name, fn, nbytes in (("h2d_gbs", lambda: d.copy_(hx, non_blocking=True), hx.numel() * 2),
+                             ("d2h_gbs", lambda: hc.view(-1)[:hx.numel()].copy_(d.view(-1), non_blocking=True), hx.numel() * 2)):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = 3 * nbytes / (a.elapsed_time(b) * 1e-3) / 1e9
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ref-rows", type=int, default=M, help="rows per batch of the CPU reference step (default: all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--e2e-chunks", type=int, default=2, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--no-wire", action="store_true", help="skip the all-reduce leg")
     ap.add_argument("--no-train", action="store_true", help="skip the FP4-linear training-step leg")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the M <= 16 rows of the shape sweep")
+    ap.add_argument("--no-sustained", action="store_true", help="time only the K steps (profiling runs)")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
     ap.add_argument("--sweep", action="store_true", help="shape sweep of the single GEMM instead of the benchmark step")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time one shape of the single GEMM instead")
@@ -258,7 +414,8 @@ def main():
             if args.shape:
                 run_shape(*args.shape, args.out_f32, min(args.steps, 50))
             else:
-                run_sweep(args)
+                for line in run_sweep():
+                    print(json.dumps(line), flush=True)
         return
 
     import torch.distributed as dist
@@ -278,68 +435,72 @@ def main():
 
     m = 1024 if args.small else M
     flops_step = 2 * 2 * m * N * K
+    warmup = max(args.warmup, 3)
     g = torch.Generator(device=dev).manual_seed(rank)
     xs = torch.randn(2, m, K, device=dev, generator=g).bfloat16()        # the two microbatches, one allocation
     x1, x2 = xs[0], xs[1]
+    both = xs.view(2 * m, K)
     w = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
     w_pk, w_sf = fp4.quantize_mxfp4_packed(w)
     del w
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)        # > 126 MB L2
 
-    def step():                                            # the public call: quantize both batches + dual GEMM
-        return dual_gemm.dual_mxfp4(x1, x2, w_pk, w_sf)
+    class Ev:                                              # start / after the quantizer / after the GEMM
+        def __init__(self):
+            self.e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
 
-    for _ in range(max(args.warmup, 3)):
+    def step(ev=None):
+        """What dual_gemm.dual_mxfp4(x1, x2, w_pk, w_sf) runs for two adjacent microbatches: one
+        quantizer launch over both, one dual-GEMM launch; written out so that an event can sit between."""
+        if ev:
+            ev.e[0].record()
+        p, sf = fp4.quantize_mxfp4_packed(both)
+        if ev:
+            ev.e[1].record()
+        half = sf.numel() // 2
+        out = dual_gemm.dual_mxfp4_packed(p[:m], p[m:], w_pk, sf[:half], sf[half:], w_sf)
+        if ev:
+            ev.e[2].record()
+        return out
+
+    for _ in range(warmup):
         c1, c2 = step()
+    ref1, ref2 = dual_gemm.dual_mxfp4(x1, x2, w_pk, w_sf)                # the one-call form gives the same bits
+    assert torch.equal(ref1, c1) and torch.equal(ref2, c2)
     mxfp4_gemm.gemm_status()
 
-    # ---- device-timed: inputs resident in HBM, L2 flushed between steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.steps)]
+    # ---- device-timed: inputs resident in HBM, L2 flushed between steps.  Exactly K steps between
+    # two barriers; then the same loop goes on (timed the same way) until the load has lasted
+    # SUSTAINED_SECONDS, so that the clock sampler sees the region the roofline numbers come from.
+    evs = [Ev() for _ in range(args.steps)]
     barrier()
     sampler = ClockSampler(dev) if rank == 0 else None
-    t_start = time.time()
-    for i in range(args.steps):
+    for ev in evs:
         flush.zero_()
-        ev[i][0].record()
-        c1, c2 = step()
-        ev[i][1].record()
+        step(ev)
     barrier()
-    extra = 0
-    if sampler:
-        # nvidia-smi samples every 20 ms: a short timed region is followed by more (untimed)
-        # steps of the same load until the sampler has seen at least 0.3 s of it
-        while time.time() - t_start < 0.3:
-            for _ in range(20):
-                step()
-            torch.cuda.synchronize()
-            extra += 20
+    step_ms = sum(ev.e[0].elapsed_time(ev.e[2]) for ev in evs)
+    quant_ms_k = sum(ev.e[0].elapsed_time(ev.e[1]) for ev in evs) / args.steps
+    gemm_ms_k = sum(ev.e[1].elapsed_time(ev.e[2]) for ev in evs) / args.steps
+    sus = []
+    if not args.no_sustained:
+        n_sus = int(min(4000, max(args.steps, SUSTAINED_SECONDS / max(step_ms / args.steps * 1e-3 + 60e-6, 1e-5))))
+        sus = [Ev() for _ in range(n_sus)]
+        for ev in sus:
+            flush.zero_()
+            step(ev)
+        barrier()
     clocks = sampler.stop() if sampler else None
-    if clocks is not None:
-        clocks["extra_untimed_steps"] = extra
     mxfp4_gemm.gemm_status()
-    step_ms = sum(e[0].elapsed_time(e[1]) for e in ev)
-
-    # ---- the dominant kernel alone (roofline): one dual-GEMM launch over both full batches
-    pk, sf = fp4.quantize_mxfp4_packed(xs.view(2 * m, K))
-    half = sf.numel() // 2
-    gsteps = max(3, min(args.steps, 200))
-    gev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(gsteps)]
-    for i in range(gsteps):
-        flush.zero_()
-        gev[i][0].record()
-        dual_gemm.dual_mxfp4_packed(pk[:m], pk[m:], w_pk, sf[:half], sf[half:], w_sf)
-        gev[i][1].record()
-    torch.cuda.synchronize()
-    gemm_ms = sum(e[0].elapsed_time(e[1]) for e in gev) / gsteps
-    qev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    flush.zero_()
-    qev[0].record()
-    for _ in range(10):
-        fp4.quantize_mxfp4_packed(xs.view(2 * m, K))
-    qev[1].record()
-    torch.cuda.synchronize()
-    quant_ms = qev[0].elapsed_time(qev[1]) / 10
-    del pk, sf
+    timed = sus if sus else evs
+    gemm_all = sorted(ev.e[1].elapsed_time(ev.e[2]) for ev in timed)
+    quant_all = sorted(ev.e[0].elapsed_time(ev.e[1]) for ev in timed)
+    gemm_ms = gemm_all[len(gemm_all) // 2]                    # median over the region the clocks were sampled on
+    quant_ms = quant_all[len(quant_all) // 2]
+    sus_ms = sum(ev.e[0].elapsed_time(ev.e[2]) for ev in timed) / len(timed)
+    if clocks is not None:
+        clocks["region"] = (f"{args.steps} + {len(sus)} timed steps (about {SUSTAINED_SECONDS} s of this load); "
+                            "median SM clock over the samples under load")
 
     # ---- end to end: pinned host buffers in, pinned host buffers out, every step.
     # Row chunks of both batches flow through three streams (copy in, compute, copy out)
@@ -380,6 +541,7 @@ def main():
                 ev_free_c[b].record(s_out)
 
     e2e_ms = float("nan")
+    copies = {}
     if not args.no_e2e:
         e2e_step()
         torch.cuda.current_stream().wait_stream(s_out)
@@ -392,114 +554,88 @@ def main():
         b.record()
         barrier()
         e2e_ms = a.elapsed_time(b) / e2e_steps
-        ref1, ref2 = dual_gemm.dual_mxfp4(x1, x2, w_pk, w_sf)
         assert torch.equal(hc[0], ref1.cpu()) and torch.equal(hc[1], ref2.cpu()), "host-buffer path disagrees"
-
-    # ---- FP4-compressed all-reduce of a 256 MiB fp32 gradient per rank (error feedback on)
-    from lockstep_b200 import wire
-    wn = (8 << 20) if args.small else (64 << 20)
-    wsteps = 0 if args.no_wire else max(3, min(args.steps, 30))
-    wire_ms = float("nan")
-    if wsteps:
-        del flush
-        gw = torch.Generator(device=dev).manual_seed(100 + rank)
-        z = torch.randn(wn, device=dev, generator=gw)
-        chi = torch.zeros(wn, device=dev)
-        for _ in range(3):
-            chi += torch.randn(wn, device=dev, generator=gw) ** 2
-        grad = z / (chi / 3).sqrt() * 1e-3                   # Student-t(3) * 1e-3
-        del z, chi
-        wobj = wire.Wire("mxfp4ef", wn, world, rank)
-        for _ in range(3):
-            wobj(grad)
-        wobj.status()
         barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(wsteps):
-            wobj(grad)
-        b.record()
+        copies = copy_bandwidth(dev, hx, hc)                  # all ranks at once: what the host gives N GPUs together
         barrier()
-        wobj.status()
-        wire_ms = a.elapsed_time(b) / wsteps
-        wobj.close()
+    del dx, dc, flush
 
-    t = torch.tensor([step_ms, e2e_ms, gemm_ms, wire_ms], device=dev, dtype=torch.float64)  # max over ranks below
-    if world > 1:
+    pk = peaks()
+    allreduce, wire_launches = None, 0
+    if not args.no_wire:
+        allreduce, wire_launches = wire_leg(args, dev, rank, world, barrier, pk)
+
+    t = torch.tensor([step_ms, e2e_ms, sus_ms, copies.get("h2d_gbs", 0.0), copies.get("d2h_gbs", 0.0)],
+                     device=dev, dtype=torch.float64)
+    tmin = t.clone()
+    if world > 1:                                             # times: max over ranks; copy rates: sum over ranks
+        tsum = t.clone()
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    step_ms_max, e2e_ms_max, gemm_ms_max, wire_ms_max = t.tolist()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    else:
+        tsum = t
+    step_ms_max, e2e_ms_max, sus_ms_max = t.tolist()[:3]
+    h2d_sum, d2h_sum = tsum.tolist()[3:]
 
     if rank == 0:
-        pk = peaks()
         value = world * flops_step * args.steps / (step_ms_max * 1e-3) / 1e12
         gemm_tflops = flops_step / (gemm_ms * 1e-3) / 1e12
         fp4_peak = 4 * pk["bf16"]
+        mhz = clocks.get("sm_mhz") if clocks else None
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": step_ms_max / args.steps, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": step_ms_max / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "mxfp4 (e2m1 x ue8m0), fp32 accumulate",
             "data": "synthetic",
+            "value_sustained": world * flops_step / (sus_ms_max * 1e-3) / 1e12,
             "config": {"workload": WORKLOAD if not args.small else WORKLOAD.replace("4096x8192 bf16", "1024x8192 bf16"),
                        "step": "dual_gemm.dual_mxfp4: quantize A1 and A2 (1 launch over both microbatches) + dual GEMM "
                                "(1 launch); W pre-quantized",
                        "parallelism": f"replicas x{world}", "l2": "256 MiB buffer written between timed steps",
-                       "quantize_ms": quant_ms, "gemm_ms": gemm_ms},
+                       "quantize_ms": quant_ms_k, "gemm_ms": gemm_ms_k,
+                       "timing": "three events per step: quantize_ms + gemm_ms = ms_per_step (means over the K steps, rank 0)",
+                       "sustained": {"steps": len(timed), "ms_per_step": sus_ms_max, "quantize_ms_median": quant_ms,
+                                     "gemm_ms_median": gemm_ms,
+                                     "gemm_us_x_ghz": None if not mhz else gemm_ms * 1e3 * mhz / 1e3}},
             "e2e": {"value": world * flops_step / (e2e_ms_max * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": hx.numel() * 2, "d2h_bytes_per_step": hc.numel() * 2,
                     "pipeline": f"{chunks} row chunks over copy-in / compute / copy-out streams",
-                    "ms_per_step": e2e_ms_max},
-            "gpu_launches": 2 * args.steps + gsteps + 10 + 3 * wsteps,
+                    "ms_per_step": e2e_ms_max,
+                    "copy_only": {"h2d_gbs_all_ranks": h2d_sum, "d2h_gbs_all_ranks": d2h_sum,
+                                  "how": "every rank copies its own 134 MB pinned buffer at the same time, one direction "
+                                         "at a time; sum over ranks"}},
+            "gpu_launches": 2 * (warmup + 1 + args.steps + len(sus)) + 2 * chunks * (e2e_steps + 2) + wire_launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_pair_kernel (cta_group::2, dual batch)",
                          "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
+                         "timed": f"median launch duration over the {len(timed)} steps of the sustained region (events "
+                                  "around the launch, on its stream)",
                          "peak_source": f"4 x {pk['source']} bf16 burst {pk['bf16']} (no FP4 figure is measured); "
-                                        f"spec dense FP4 {FP4_SPEC_TFLOPS}",
+                                        f"4 x sustained bf16 = {4 * (pk['bf16_sustained'] or 0):.0f}; spec dense FP4 {FP4_SPEC_TFLOPS}",
+                         "frac_of_sustained": gemm_tflops / (4 * pk["bf16_sustained"]) if pk.get("bf16_sustained") else None,
                          "frac_of_spec": gemm_tflops / FP4_SPEC_TFLOPS,
                          "flop_per_launch": flops_step,
                          "traffic": None if args.small else GEMM_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_source": None if args.small else GEMM_DRAM_BYTES_SOURCE,
                          "algorithmic_bytes": None if args.small else GEMM_ALGORITHMIC_BYTES},
         }
-        if wsteps:
-            comp = wn * 0.53125                              # packed + exponent bytes of one buffer
-            # per rank and step: send reads g, res and writes res, payload; reduce reads W payloads,
-            # ores, writes ores and W payloads; finish reads the payload and writes g
-            hbm = wn * (12 + 0.53125) + (wn / world) * (world * 0.53125 + 8 + world * 0.53125) + wn * (0.53125 + 4)
-            line["allreduce"] = {
-                "method": "mxfp4ef", "world": world, "elements_per_rank": wn, "steps": wsteps,
-                "ms": wire_ms_max, "algbw_gbs": wn * 4 / (wire_ms_max * 1e-3) / 1e9,
-                "link_busbw_gbs": 2 * (world - 1) / world * comp / (wire_ms_max * 1e-3) / 1e9,
-                "link_peak_gbs": 900.0, "hbm_bytes_per_rank": hbm,
-                "hbm_gbs": hbm / (wire_ms_max * 1e-3) / 1e9, "hbm_peak_gbs": pk["hbm"],
-                "hbm_frac": hbm / (wire_ms_max * 1e-3) / 1e9 / pk["hbm"], "data": "Student-t(3) * 1e-3, seed 100 + rank"}
-        if wsteps and world == 1 and not args.no_cpu_baseline:
-            import numpy as np
-            from oracle import cref
-            cn = 8 << 20                                     # bounded sample of the 64 Mi buffer
-            rng = np.random.default_rng(100)
-            gc = (rng.standard_t(3, cn) * 1e-3).astype(np.float32)
-            res_c, ores_c = [np.zeros(cn, np.float32)], [np.zeros(cn, np.float32)]
-            cref.wire_step([gc], res_c, ores_c, unit=256)
-            t0 = time.perf_counter()
-            cref.wire_step([gc], res_c, ores_c, unit=256)
-            dt = time.perf_counter() - t0
-            line["allreduce"]["cpu_baseline"] = {"algbw_gbs": cn * 4 / dt / 1e9, "cores": os.cpu_count(), "kind": "port",
-                                                 "sample": "8 Mi of 64 Mi elements, one rank, C oracle (OpenMP)"}
+        if allreduce:
+            line["allreduce"] = allreduce
         if world == 1 and not args.no_train and not args.small:
-            from lockstep_b200 import gpt
+            import train_bench
             torch.cuda.empty_cache()
-            tr = {}
-            for mode in ("ste", "mxfp4"):
-                sec, loss = gpt.training_step_time(backward=mode, steps=5, warmup=2, device=dev)
-                tr[mode] = {"tokens_per_s": 16 * 1024 / sec, "ms_per_step": sec * 1e3, "loss": loss}
-            line["train_step"] = {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 vocab32000, every block "
-                                           "linear MXFP4Linear, bf16 autocast, fused AdamW, synthetic ids seed 0",
-                                  "backward": tr}
+            line["train_step"] = train_bench.report(dev)
+        if world == 1 and not args.no_sweep and not args.small:
+            torch.cuda.empty_cache()
+            line["sweep_skinny"] = {"lines": run_sweep(m_list=(1, 16)),
+                                    "what": "single MXFP4 GEMM, M <= 16, N = K in {4096, 8192, 16384}: us per launch "
+                                            "(CUDA graph, weights not in L2) and fraction of the bytes roofline"}
         if world == 1 and not args.no_cpu_baseline:
-            dt, fl = cpu_reference_step(CPU_SAMPLE_ROWS)
-            dt2, fl = cpu_reference_step(CPU_SAMPLE_ROWS)
-            line["cpu_baseline"] = {"value": fl / min(dt, dt2) / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-                                    "kind": "port",
-                                    "sample": f"{CPU_SAMPLE_ROWS} of {M} rows of each batch against the full W, best of 2"}
+            cores = host_threads()
+            ref = CpuReference(M)
+            dts = [ref.step() for _ in range(2)]
+            line["cpu_baseline"] = {"value": ref.flops / min(dts) / 1e12, "unit": "TFLOP/s", "cores": cores,
+                                    "kind": "port", "sample": ref.sample() + ", best of 2"}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

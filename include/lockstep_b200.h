@@ -119,10 +119,12 @@ int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint8_t *sf, in
  *   sfa    scale bytes of A in the scale-factor layout  sfb    likewise for W
  *   c      [M, N] row-major, LS_BF16 (round to nearest even) or LS_F32
  * K % 128 == 0; M and N are free.  All buffers 16-byte aligned.
- * Entry points may be called from several host threads.  A product that the
- * library splits along K (few output tiles, long K; see ls_gemm_set_splits)
- * puts its partial sums in one scratch buffer per device: such calls must not
- * overlap in time on one device. */
+ * Entry points may be called from several host threads and streams.  A product
+ * that the library splits along K (few output tiles, long K; see
+ * ls_gemm_set_splits) puts its partial sums in one scratch buffer per device;
+ * the library orders such calls on different streams with an event (the later
+ * call waits for the earlier one's summation), so they are safe but do not
+ * overlap.  Encoded TMA descriptors are cached per host thread. */
 int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
                   void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 
@@ -186,17 +188,31 @@ int ls_wire_local_handle(void *handle, void *blob_host);
 int ls_wire_map_peers(void *handle, const void *all_blobs_host);
 int ls_wire_map_local(void *handle, void *const *handles_host);
 
-/* In-place average of g[numel] (fp32) over the ranks: the three phases of one
- * step, enqueued on `stream`.  res [padded] / ores [padded / world] are the
- * sender / owner error-feedback residuals (wire.py:109-111,128-135), updated in
- * place; NULL disables error feedback.  reverse != 0 sums senders in
- * descending order (wire.py:122-123).  Every rank must make the same calls in
- * the same order.  ls_wire_allreduce = send + reduce + finish. */
+/* In-place average of g[numel] (fp32) over the ranks, enqueued on `stream`.
+ * res [padded] / ores [padded / world] are the sender / owner error-feedback
+ * residuals (wire.py:109-111,128-135), updated in place; NULL disables error
+ * feedback.  reverse != 0 sums senders in descending order (wire.py:122-123).
+ * Every rank must make the same calls in the same order.
+ * ls_wire_send / _reduce / _finish are the three phases of one step as separate
+ * launches (a kernel then only waits for kernels of other GPUs; callers that
+ * interleave ranks in one process, or that want to start the send early, use
+ * them).  ls_wire_allreduce runs the step either as those three launches or as
+ * ONE cooperative launch that pipelines sub-ranges of the shards through the
+ * three phases (see ls_wire_set_mode); results and wire bytes are the same. */
 int ls_wire_send(void *handle, const float *g, int64_t numel, float *res, void *stream);
 int ls_wire_reduce(void *handle, float *ores, int reverse, void *stream);
 int ls_wire_finish(void *handle, float *g, int64_t numel, void *stream);
 int ls_wire_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, int reverse,
                       void *stream);
+
+/* One step of ALL ranks of a group created in one process on one GPU
+ * (ls_wire_map_local) as a single cooperative launch: every rank's CTAs are
+ * resident together, so the waits between ranks are met inside the launch.
+ * handles / gs / ress / oress: host arrays of `world` entries in rank order
+ * (ress / oress may be NULL).  Used by the single-GPU tests of the pipelined
+ * kernel; no reference counterpart. */
+int ls_wire_allreduce_group(void *const *handles, float *const *gs, int64_t numel, float *const *ress,
+                            float *const *oress, int reverse, void *stream);
 
 /* The reference's integer wires (wire.py:104-138: int16, int8, int8 with error
  * feedback) on the same transport: a shared grid per chunk of 64 from the
@@ -209,20 +225,36 @@ int ls_wire_create_int(int rank, int world, int64_t padded, int bits, void **han
 int ls_wire_int_phase(void *handle, int phase, float *g, int64_t numel, float *res, float *ores, void *stream);
 int ls_wire_int_allreduce(void *handle, float *g, int64_t numel, float *res, float *ores, void *stream);
 
-/* ls_wire_allreduce cuts a call into pieces (the same sub-range of every
- * owner's shard) whose three phases run on the caller's stream and on two
- * streams owned by the handle, joined back into the caller's stream before the
- * call's work counts as done there: the exchange of one piece overlaps the
- * memory passes of the others.  Results and wire bytes do not depend on the
- * number of pieces.  0 or 1 = one piece (default: on one and two GPUs the
- * concurrent phases cost more HBM time than the hidden latency saves),
- * 2..8 = that many where the shard divides.  No reference counterpart. */
-int ls_wire_set_chunks(void *handle, int chunks);
+/* How ls_wire_allreduce runs a step on this handle.  mode: 0 = default (the
+ * cooperative launch), 1 = three launches, 2 = one cooperative launch.  subs:
+ * sub-ranges each shard is cut into by the cooperative launch (0 = default 4,
+ * else 1..8; lowered until the shard divides into multiples of 256 elements).
+ * stagger != 0: the CTAs take the three items of a pipeline step in rotated
+ * orders.  The cooperative launch needs the whole grid resident at once: do not
+ * run it beside other kernels that occupy the SMs for long.  ls_wire_mode
+ * returns the mode in force (1 or 2).  No reference counterpart. */
+int ls_wire_set_mode(void *handle, int mode, int subs, int stagger);
+int ls_wire_mode(void *handle);
 
-/* How many times (about 100 ns apart, default 2^22 = ~0.5 s) a kernel polls a
- * peer's flag before it gives up, records a time-out in the status word and
- * carries on with whatever its buffers hold; the context stays usable. */
-int ls_wire_set_poll_limit(void *handle, int64_t polls);
+/* How long (default 20 s) a kernel waits for a peer's flag before it gives up.
+ * A CTA whose wait ran out records it in the status word, stores nothing more
+ * (g, the owner residual and the peers' slots keep what they held) and raises
+ * no further flag, so every rank that depends on it runs out as well and the
+ * step fails on all ranks; the context stays usable.  The sender residual of
+ * that step has already been updated: after a time-out call ls_wire_reset on
+ * every rank and clear or restore the residuals. */
+int ls_wire_set_timeout_us(void *handle, int64_t microseconds);
+
+/* Non-blocking status: every all-reduce call ends by copying the status word to
+ * pinned host memory on its stream; this returns LS_ETIMEOUT if the last
+ * finished copy was non-zero.  A call still in flight is not waited for, so a
+ * time-out is seen one call late at the latest. */
+int ls_wire_poll_status(void *handle, int *status_host);
+
+/* After a time-out: synchronises this device, clears flags, counters and the
+ * status word and rewinds the epoch.  Collective by contract: every rank calls
+ * it between two host-side barriers. */
+int ls_wire_reset(void *handle);
 
 /* Synchronising: LS_ETIMEOUT (and clears it) if a wire kernel gave up waiting
  * for a peer since the last call.  status_host (host int) may be NULL. */
@@ -235,7 +267,9 @@ int ls_wire_debug_slots(void *handle, int which, uint8_t *out, int64_t *slot_byt
 
 /* MXFP4 linear forward without any allocation: quantizes x [M, K] (LS_BF16 or
  * LS_F32) to MXFP4 and multiplies by a pre-quantized weight (w_pk [N, K/2],
- * w_sf its scale-factor buffer), c [M, N] as in ls_mxfp4_gemm.  No counterpart
+ * w_sf its scale-factor buffer), c [M, N] as in ls_mxfp4_gemm.  x must be
+ * 32-byte aligned (the quantizer reads 32-byte words), the other buffers
+ * 16-byte aligned, as in ls_quantize_mxfp4 / ls_mxfp4_gemm.  No counterpart
  * in lockstep; added for callers that may not call cudaMalloc (a plugin
  * inside a host's fixed memory plan, a loop that cannot afford an
  * allocation's device-wide synchronisation).  The temporaries between the

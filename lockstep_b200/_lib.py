@@ -47,8 +47,13 @@ _SIGS = {
     "ls_wire_int_phase": (c_int, [c_vp, c_int, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "ls_wire_int_allreduce": (c_int, [c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "ls_wire_status": (c_int, [c_vp, c_vp]),
-    "ls_wire_set_poll_limit": (c_int, [c_vp, c_i64]),
-    "ls_wire_set_chunks": (c_int, [c_vp, c_int]),
+    "ls_wire_allreduce_group": (c_int, [ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_i64, ctypes.POINTER(c_vp),
+                                        ctypes.POINTER(c_vp), c_int, c_vp]),
+    "ls_wire_set_mode": (c_int, [c_vp, c_int, c_int, c_int]),
+    "ls_wire_mode": (c_int, [c_vp]),
+    "ls_wire_set_timeout_us": (c_int, [c_vp, c_i64]),
+    "ls_wire_poll_status": (c_int, [c_vp, c_vp]),
+    "ls_wire_reset": (c_int, [c_vp]),
     "ls_wire_debug_slots": (c_int, [c_vp, c_int, c_vp, ctypes.POINTER(c_i64), c_vp]),
     "ls_scales_to_sf": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
 }

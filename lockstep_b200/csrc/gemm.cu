@@ -18,6 +18,7 @@
 // MMAs start.
 #include <cuda.h>
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -720,8 +721,7 @@ EncodeFn encode_fn()
     return fn;
 }
 
-// [rows, kbytes] bytes, K-contiguous; box = 128 bytes x box_rows, 128-byte swizzle
-int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kbytes, int box_rows)
+int encode_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kbytes, int box_rows)
 {
     EncodeFn fn = encode_fn();
     if (!fn) return fail(LS_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -733,6 +733,44 @@ int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kby
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LS_ECUDA, "cuTensorMapEncodeTiled failed with %d", int(r));
+    return LS_OK;
+}
+
+// Encoded tensor maps are pure functions of (base, shape, box): a small per-thread,
+// direct-mapped cache keeps the last ones, so that a layer called every step with the
+// same buffers (weights, a caching allocator's recycled activations) does not pay the
+// driver's encoding on every launch.  kind 0: operand map, 1: scale-factor map.
+struct MapKey {
+    const void *base;
+    int64_t rows, inner;
+    int box_rows, kind;
+    bool operator==(const MapKey &o) const
+    {
+        return base == o.base && rows == o.rows && inner == o.inner && box_rows == o.box_rows && kind == o.kind;
+    }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int kMapSlots = 256;
+MapSlot *map_slot(const MapKey &k)
+{
+    static thread_local MapSlot slots[kMapSlots] = {};
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
+    h ^= uint64_t(k.rows) * 0x9E3779B97F4A7C15ull + uint64_t(k.inner) * 0xC2B2AE3D27D4EB4Full + uint64_t(k.box_rows) * 31 + uint64_t(k.kind);
+    h ^= h >> 29;
+    return &slots[h % kMapSlots];
+}
+
+// [rows, kbytes] bytes, K-contiguous; box = 128 bytes x box_rows, 128-byte swizzle
+int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kbytes, int box_rows)
+{
+    const MapKey key{base, rows, kbytes, box_rows, 0};
+    MapSlot *slot = map_slot(key);
+    if (slot->used && slot->key == key) {
+        *m = slot->map;
+        return LS_OK;
+    }
+    if (int rc = encode_operand_map(m, base, rows, kbytes, box_rows)) return rc;
+    slot->key = key, slot->map = *m, slot->used = true;
     return LS_OK;
 }
 
@@ -762,6 +800,12 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
 // one box = two consecutive k-tiles of one row tile.
 int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K)
 {
+    const MapKey key{base, rows, K, 2, 1};
+    MapSlot *slot = map_slot(key);
+    if (slot->used && slot->key == key) {
+        *m = slot->map;
+        return LS_OK;
+    }
     EncodeFn fn = encode_fn();
     if (!fn) return fail(LS_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {128, cuuint64_t(((rows + 127) / 128) * (K / 128))};
@@ -772,6 +816,7 @@ int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K)
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LS_ECUDA, "cuTensorMapEncodeTiled (scales) failed with %d", int(r));
+    slot->key = key, slot->map = *m, slot->used = true;
     return LS_OK;
 }
 
@@ -814,31 +859,48 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     return LS_OK;
 }
 
-int g_gemm_variant = 0;          // 0 = choose by shape, 1 = single-CTA kernel (256-column tiles), 2 = CTA-pair kernel,
-                                 // 3 = single-CTA kernel with 128-column tiles
-int g_gemm_splits = 0;           // 0 = choose by shape, n = split K n ways where splitting is allowed
+std::atomic<int> g_gemm_variant{0};   // 0 = choose by shape, 1 = single-CTA kernel (256-column tiles), 2 = CTA-pair kernel,
+                                      // 3 = single-CTA kernel with 128-column tiles
+std::atomic<int> g_gemm_splits{0};    // 0 = choose by shape, n = split K n ways where splitting is allowed
 
-// Per-device scratch for split-K partial sums; grows on demand and is kept.  One buffer
-// per device: K-split GEMMs of one device must not overlap in time (streams or threads),
-// and a larger request re-allocates after a device synchronisation.
-float *splitk_scratch(size_t bytes)
+// Per-device scratch for split-K partial sums, shared by every K-split GEMM of the device.
+// Two such GEMMs on different streams are ordered by an event: the later one waits for the
+// earlier one's summation kernel before its own partial sums may overwrite the slabs.  A
+// request larger than the buffer gets a new, larger buffer; the old one may still be in use
+// by a launch in flight, so it is kept until the process ends (a handful of doublings at most).
+struct SplitScratch {
+    float *buf = nullptr;
+    size_t cap = 0;
+    cudaEvent_t last_use = nullptr;     // recorded after the summation kernel of the last K-split GEMM
+    cudaStream_t last_stream = nullptr;
+    bool used = false;
+};
+SplitScratch g_split[64];
+
+// Returns the scratch (>= bytes) after making `st` wait for the previous user on another stream.
+float *splitk_acquire(size_t bytes, cudaStream_t st)
 {
-    static float *buf[64] = {};
-    static size_t cap[64] = {};
     int dev = 0;
     if (current_device(&dev)) return nullptr;
     std::lock_guard<std::mutex> lk(state_mutex());
-    if (cap[dev] < bytes) {
-        if (buf[dev]) {
-            cudaDeviceSynchronize();
-            cudaFree(buf[dev]);
-            buf[dev] = nullptr, cap[dev] = 0;
-        }
+    SplitScratch &sc = g_split[dev];
+    if (!sc.last_use && cudaEventCreateWithFlags(&sc.last_use, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (sc.cap < bytes) {
         size_t want = bytes < (size_t(32) << 20) ? (size_t(32) << 20) : bytes;
-        if (cudaMalloc(&buf[dev], want) != cudaSuccess) return nullptr;
-        cap[dev] = want;
+        float *fresh = nullptr;
+        if (cudaMalloc(&fresh, want) != cudaSuccess) return nullptr;
+        sc.buf = fresh, sc.cap = want, sc.used = false;            // the old buffer stays allocated
     }
-    return buf[dev];
+    if (sc.used && sc.last_stream != st && cudaStreamWaitEvent(st, sc.last_use, 0) != cudaSuccess) return nullptr;
+    return sc.buf;
+}
+void splitk_release(cudaStream_t st)
+{
+    int dev = 0;
+    if (current_device(&dev)) return;
+    std::lock_guard<std::mutex> lk(state_mutex());
+    SplitScratch &sc = g_split[dev];
+    if (cudaEventRecord(sc.last_use, st) == cudaSuccess) sc.last_stream = st, sc.used = true;
 }
 
 }  // namespace
@@ -897,7 +959,8 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     if (!err) err = error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     CUtensorMap ta0, ta1, tb;
-    const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && (nbatch == 2 || M > BM));
+    const int variant = g_gemm_variant.load(std::memory_order_relaxed), forced_splits = g_gemm_splits.load(std::memory_order_relaxed);
+    const bool pair = variant == 2 || (variant == 0 && (nbatch == 2 || M > BM));
     // A tile of the single-CTA kernel: the box has only as many rows (16, 32, 64 or 128) as
     // A has.  The other rows of the stage keep whatever shared memory held; an output row
     // depends on its own row of A only, and rows past M are never stored.  (A 128-row box
@@ -912,7 +975,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     // the SMs without one (the weight stream of a short-M product needs the SMs' loads in
     // flight more than it needs wide tiles).
     const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256) * nbatch;
-    const int bn = pair ? 256 : (g_gemm_variant == 3 || (g_gemm_variant == 0 && tiles256 * 2 <= sm_count())) ? 128 : 256;
+    const int bn = pair ? 256 : (variant == 3 || (variant == 0 && tiles256 * 2 <= sm_count())) ? 128 : 256;
     if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
@@ -944,8 +1007,8 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     const int slots = pair ? sm_count() / 2 : sm_count();       // work items that run at once
     int s = 1;
     if (!caller_err && !fused) {
-        if (g_gemm_splits > 0) {
-            s = g_gemm_splits;
+        if (forced_splits > 0) {
+            s = forced_splits;
         } else if (pair) {
             // Pays only with a quarter of the CTA pairs busy and a long K (weight gradients
             // of small layers): the partial slabs and the second kernel cost about 10 us.
@@ -962,7 +1025,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
         p.splits = (k_tiles + p.kt_per_split - 1) / p.kt_per_split;
     }
     if (p.splits > 1) {
-        p.partial = splitk_scratch(size_t(p.splits) * nbatch * M * N * sizeof(float));
+        p.partial = splitk_acquire(size_t(p.splits) * nbatch * M * N * sizeof(float), static_cast<cudaStream_t>(stream));
         if (!p.partial) return fail(LS_ECUDA, "could not allocate split-K scratch");
     }
     if (pair) {
@@ -980,6 +1043,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
             splitk_reduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
                 p.partial + int64_t(b) * p.splits * mn, p.c[b], mn, p.splits, p.out_bf16);
         }
+        splitk_release(static_cast<cudaStream_t>(stream));
         LS_LAUNCH_CHECK("splitk_reduce");
     }
     return LS_OK;
@@ -1017,14 +1081,14 @@ extern "C" int ls_gemm_status(int *status_host)
 extern "C" int ls_gemm_set_variant(int variant)
 {
     if (variant < 0 || variant > 3) return fail(LS_EINVAL, "variant must be 0..3");
-    g_gemm_variant = variant;
+    g_gemm_variant.store(variant, std::memory_order_relaxed);
     return LS_OK;
 }
 
 extern "C" int ls_gemm_set_splits(int splits)
 {
     if (splits < 0 || splits > 16) return fail(LS_EINVAL, "splits must be 0 (choose by shape) or 1..16");
-    g_gemm_splits = splits;
+    g_gemm_splits.store(splits, std::memory_order_relaxed);
     return LS_OK;
 }
 

@@ -62,9 +62,10 @@ extern "C" int ls_mxfp4_linear_noalloc(const void *x, int x_dtype, const uint8_t
                                        int32_t *status, void *stream)
 {
     if (int rc = check_device()) return rc;
-    if (M < 0 || N < 0 || K <= 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a positive multiple of 128", (long long)K);
+    if (M < 0 || N < 0) return fail(LS_EINVAL, "M=%lld and N=%lld must not be negative", (long long)M, (long long)N);
+    if (K <= 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a positive multiple of 128", (long long)K);
     if (M == 0 || N == 0) return LS_OK;
-    if (M * K > kMaxElems)
+    if (M > kMaxElems / K)                              // M * K > kMaxElems without the overflow
         return fail(LS_EINVAL, "no-alloc path holds at most %lld activation elements per call, got %lld x %lld",
                     (long long)kMaxElems, (long long)M, (long long)K);
     const int64_t sf_bytes = ls_sf_bytes(M, K);

@@ -11,9 +11,27 @@
 //           fp32); val += ores; encode; ores = val - decode; store the result
 //           into every rank's gather slot [my rank]; raise the gather flag
 //   finish  wait for every owner's gather flag; g = decode(all shards) / world
-// NCCL/gloo only carries the 64-byte IPC handles at set-up.  The three phases
-// are three launches on the caller's stream; a phase only ever waits for
-// kernels of OTHER GPUs (bounded, reported through the status word).
+// NCCL/gloo only carries the 64-byte IPC handles at set-up.
+//
+// Two ways to run a step.  Three launches on the caller's stream (send, reduce,
+// finish): a kernel then only ever waits for kernels of OTHER GPUs.  Or one
+// cooperative launch that cuts every shard into S sub-ranges and walks them as
+// a pipeline -- send(t), reduce(t-1), finish(t-2) -- with one flag per
+// sub-range, sender and phase, so that the owner's work on a sub-range and the
+// decode of the one before overlap the memory passes of the next send instead
+// of queueing behind a kernel boundary.  The cooperative launch guarantees that
+// all CTAs are resident, which the waits inside one kernel rely on.
+//
+// Senders walk the owners starting at their right-hand neighbour (rank + 1),
+// so at any moment every owner receives from one sender only instead of all
+// ranks storing into owner 0 first.  A thread owns 16 consecutive values (two
+// 32-byte loads per operand, one 8-byte packed store); two adjacent lanes share
+// a block of 32 and a half-warp writes its 8 exponent bytes as one word pair.
+//
+// Every wait is bounded by a wall-clock limit (%globaltimer).  A CTA whose wait
+// runs out records it in the status word, stores nothing more and raises no
+// further flag, so the ranks that depend on it run out too: a lost peer becomes
+// an error on every rank of that step instead of a silently different average.
 // All arithmetic uses explicitly rounded intrinsics so that no multiply-add
 // contraction changes a bit against the CPU oracle.
 #include <cstring>
@@ -26,13 +44,13 @@ namespace {
 
 constexpr int kMaxWorld = 8;
 constexpr int kThreads = 256;
-constexpr uint32_t kPollLimit = 1u << 22;     // default polls (x ~100 ns sleep each) before a wait gives up
+constexpr int kMaxSub = 8;                                  // sub-ranges a shard may be cut into
+constexpr uint64_t kDefaultTimeoutNs = 20ull * 1000 * 1000 * 1000;   // a wait gives up after 20 s
 
-constexpr int kMaxChunks = 8;   // pieces an all-reduce call may be cut into (each with its own flags)
 struct Header {                 // start of every rank's arena
-    uint32_t rs_flag[kMaxChunks][kMaxWorld];    // epoch of the last completed send of chunk c from rank s
-    uint32_t ag_flag[kMaxChunks][kMaxWorld];    // epoch of the last completed reduce of chunk c by owner o
-    uint32_t counter[kMaxChunks][2];            // CTA completion counters (send, reduce)
+    uint32_t rs_flag[kMaxSub][kMaxWorld];       // epoch of the last completed send of sub-range c from rank s
+    uint32_t ag_flag[kMaxSub][kMaxWorld];       // epoch of the last completed reduce of sub-range c by owner o
+    uint32_t counter[kMaxSub][2];               // CTA completion counters (send, reduce)
     uint32_t status;                // non-zero: a wait ran out
     uint32_t mx_flag[kMaxWorld];    // integer wires: epoch of rank s's last published chunk maxima
     uint32_t counter_mx;
@@ -40,12 +58,11 @@ struct Header {                 // start of every rank's arena
 constexpr size_t kHeaderBytes = 1024;
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
 
-// A piece of one all-reduce: the same sub-range [first, first + count) (in groups of 8
-// elements) of every owner's shard.  Pieces of one call run as separate launches on three
-// streams, so that one piece's exchange overlaps the memory passes of the others.
-struct Chunk {
+// The same sub-range [first, first + count) of every owner's shard, in groups of 16
+// elements; both are multiples of 16 groups, so a half-warp never straddles a sub-range.
+struct Sub {
     int index;
-    uint32_t first, count;      // multiples of 32: a warp never straddles a piece
+    uint32_t first, count;
 };
 
 struct Peers { uint8_t *arena[kMaxWorld]; };
@@ -55,7 +72,7 @@ struct WireGeom {
     int64_t padded, shard;          // elements
     int64_t slot_bytes;             // packed + exponent bytes of one shard, 256-aligned
     int64_t rs_off, ag_off;         // byte offsets of the slot arrays in an arena
-    uint32_t poll_limit;            // polls before a wait on a peer's flag gives up
+    uint64_t timeout_ns;            // how long a wait on a peer's flag may last
     int bits;                       // 0: MXFP4 payload; 8 / 16: integer payload (wire.py's int8 / int16)
     int64_t mx_off;                 // integer wires: [world][padded / 64] fp32 chunk maxima of every rank
 };
@@ -68,12 +85,10 @@ struct Wire {
     Peers peers;
     bool mapped, opened[kMaxWorld];
     uint32_t epoch;
-    // pipelined all-reduce: pieces of a call run on the caller's stream (send) and on two
-    // streams of the wire (owner phase, decode), chained by events
-    int chunks;                     // 0 = choose by size and world, n = cut every call into n pieces
-    cudaStream_t s_reduce, s_finish;
-    cudaEvent_t ev_start, ev_done, ev_sent[kMaxChunks], ev_reduced[kMaxChunks];
-    bool pipe_ready;
+    int mode;                       // 0 = choose, 1 = three launches, 2 = one cooperative launch
+    int subs;                       // sub-ranges of the cooperative launch (0 = choose)
+    int fused_ctas;                 // CTAs of the cooperative kernel that fit the device at once (0 = not asked yet)
+    int *status_host;               // pinned: copy of the status word after the last all-reduce call
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
@@ -86,34 +101,45 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-
-// Thread s of every CTA polls rank s's flag; returns after all `world` flags reached `epoch`
-// (or after poll_limit polls, recording the time-out).
-__device__ __forceinline__ void wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch,
-                                           uint32_t poll_limit)
+__device__ __forceinline__ uint64_t global_ns()
 {
-    if (int(threadIdx.x) < world) {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Thread s of the CTA polls rank s's flag until it reaches `epoch`.  Returns true (to
+// every thread of the CTA) when all `world` flags arrived, false when the time limit ran
+// out first; the time-out is recorded in the status word of this rank's arena.
+__device__ __forceinline__ bool wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch,
+                                           uint64_t timeout_ns)
+{
+    bool ok = true;
+    if (int(threadIdx.x) < world && int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
+        const uint64_t t0 = global_ns();
         uint32_t polls = 0;
         while (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
-            if (++polls > poll_limit) {
+            if ((++polls & 15u) == 0 && global_ns() - t0 > timeout_ns) {
                 atomicExch(&h->status, 1u);
+                ok = false;
                 break;
             }
             __nanosleep(100);
         }
     }
-    __syncthreads();
+    return __syncthreads_and(ok) != 0;
 }
 
-// After this CTA's stores: the last CTA of the grid raises flag[rank] = epoch on every peer.
-__device__ __forceinline__ void signal_done(Header *mine, uint32_t *counter, const Peers &peers, int world,
+// After this CTA's stores: the last of the `ncta` CTAs that work for this rank raises
+// flag[rank] = epoch on every peer.
+__device__ __forceinline__ void signal_done(uint32_t *counter, uint32_t ncta, const Peers &peers, int world,
                                             int rank, size_t flag_off, uint32_t epoch)
 {
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
         uint32_t done = atomicAdd(counter, 1u);
-        if (done == gridDim.x - 1) {
+        if (done == ncta - 1) {
             *counter = 0;
             __threadfence_system();
             for (int p = 0; p < world; p++)
@@ -122,50 +148,383 @@ __device__ __forceinline__ void signal_done(Header *mine, uint32_t *counter, con
     }
 }
 
-// Encodes 8 values held by this thread (4 adjacent lanes share a block of 32).
-// Returns packed nibbles; e8 = exponent byte of the block; dq[] = decoded values.
-__device__ __forceinline__ uint32_t encode8(const float (&v)[8], uint32_t &e8, float (&dq)[8])
+// ---- 16 values per thread -------------------------------------------------------------
+__device__ __forceinline__ void ld8(const float *p, float *v)
+{
+    asm volatile("ld.global.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+                 : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st8(float *p, const float *v)
+{
+    asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
+}
+__device__ __forceinline__ void load16(const float *p, int64_t i0, int64_t n, float (&v)[16])
+{
+    if (i0 + 16 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 31) == 0) {
+        ld8(p + i0, v);
+        ld8(p + i0 + 8, v + 8);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = i0 + i < n ? p[i0 + i] : 0.0f;
+    }
+}
+__device__ __forceinline__ void store16(float *p, int64_t i0, int64_t n, const float (&v)[16])
+{
+    if (i0 + 16 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 31) == 0) {
+        st8(p + i0, v);
+        st8(p + i0 + 8, v + 8);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i0 + i < n) p[i0 + i] = v[i];
+    }
+}
+
+// Mask of the half-warp this lane belongs to.
+__device__ __forceinline__ uint32_t half_mask() { return 0xFFFFu << (threadIdx.x & 16); }
+
+// Encodes the 16 values of this thread; the adjacent lane (lane ^ 1) holds the other half
+// of the block of 32.  Returns the packed nibbles; e8 = exponent byte of the block;
+// dq[] = decoded values.
+__device__ __forceinline__ uint2 encode16(const float (&v)[16], uint32_t hmask, uint32_t &e8, float (&dq)[16])
 {
     uint32_t amax = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) amax = max(amax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
-    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    for (int i = 0; i < 16; i++) amax = max(amax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    amax = max(amax, __shfl_xor_sync(hmask, amax, 1));
     e8 = block_e8m0(amax);
     const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
     const float sc = __uint_as_float(scale_bits(e8));
-    float q[8];
+    uint32_t pk[2];
 #pragma unroll
-    for (int i = 0; i < 8; i++) q[i] = __fmul_rn(v[i], inv);
-    uint32_t pk;
-    if (amax < kBitsInf) {
-        pk = cvt_ref_e2m1x8(q);                          // all quotients finite: hardware converter
-    } else {
-        pk = 0;
+    for (int h = 0; h < 2; h++) {
+        float q[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) pk |= e2m1_code<false>(q[i]) << (4 * i);
+        for (int i = 0; i < 8; i++) q[i] = __fmul_rn(v[8 * h + i], inv);
+        if (amax < kBitsInf) {
+            pk[h] = cvt_ref_e2m1x8(q);                       // all quotients finite: hardware converter
+        } else {
+            pk[h] = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) pk[h] |= e2m1_code<false>(q[i]) << (4 * i);
+        }
+        float lo[4], hi[4];
+        e2m1x4_values(pk[h], lo);
+        e2m1x4_values(pk[h] >> 16, hi);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            dq[8 * h + i] = __fmul_rn(lo[i], sc);
+            dq[8 * h + 4 + i] = __fmul_rn(hi[i], sc);
+        }
     }
-    float lo[4], hi[4];
-    e2m1x4_values(pk, lo);
-    e2m1x4_values(pk >> 16, hi);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        dq[i] = __fmul_rn(lo[i], sc);
-        dq[4 + i] = __fmul_rn(hi[i], sc);
-    }
-    return pk;
+    return make_uint2(pk[0], pk[1]);
 }
 
-// The 8 exponent bytes of a warp's 8 blocks, gathered into lane 0 as one 64-bit word.
-__device__ __forceinline__ uint2 gather_exponents(uint32_t e8)
+// val[i] += decode(pk)[i] * 2^(e8 - 127), each add rounded to fp32
+__device__ __forceinline__ void add_decoded16(uint2 pk, uint32_t e8, float (&val)[16])
 {
-    uint2 w = make_uint2(0, 0);
+    const float sc = __uint_as_float(scale_bits(e8));
+    const uint32_t w[2] = {pk.x, pk.y};
 #pragma unroll
-    for (int b = 0; b < 4; b++) w.x |= __shfl_sync(0xFFFFFFFFu, e8, 4 * b) << (8 * b);
+    for (int h = 0; h < 2; h++) {
+        float lo[4], hi[4];
+        e2m1x4_values(w[h], lo);
+        e2m1x4_values(w[h] >> 16, hi);
 #pragma unroll
-    for (int b = 0; b < 4; b++) w.y |= __shfl_sync(0xFFFFFFFFu, e8, 16 + 4 * b) << (8 * b);
-    return w;
+        for (int i = 0; i < 4; i++) {
+            val[8 * h + i] = __fadd_rn(val[8 * h + i], __fmul_rn(lo[i], sc));
+            val[8 * h + 4 + i] = __fadd_rn(val[8 * h + 4 + i], __fmul_rn(hi[i], sc));
+        }
+    }
 }
+
+// The 8 exponent bytes of a half-warp's 8 blocks (held by its even lanes), gathered into
+// the half-warp's first lane as two words.
+__device__ __forceinline__ uint2 gather_exponents16(uint32_t e8, uint32_t hmask)
+{
+    uint32_t w = e8 | (__shfl_down_sync(hmask, e8, 2, 16) << 8);     // lanes 0, 4, 8, 12: two blocks
+    w |= __shfl_down_sync(hmask, w, 4, 16) << 16;                    // lanes 0, 8: four blocks
+    const uint32_t hi = __shfl_down_sync(hmask, w, 8, 16);           // lane 0: blocks 4..7
+    return make_uint2(w, hi);
+}
+
+// ---- phase 1: sender ---------------------------------------------------------------
+// CTA `cta` of `ncta` encodes its share of sub-range `sub` of every owner's shard.
+__device__ __forceinline__ void send_part(const float *g, int64_t n, float *res, const WireGeom &geo,
+                                          const Peers &peers, Sub sub, uint32_t cta, uint32_t ncta)
+{
+    const uint32_t stride = ncta * kThreads;
+    const uint32_t hmask = half_mask();
+    const uint32_t per_shard = uint32_t(geo.shard / 16);       // groups of 16 per shard
+    const uint32_t total = uint32_t(geo.world) * sub.count;
+    const int64_t exp_off = geo.shard / 2;
+    // one flat loop over the sub-range's groups of all owners; the step index i advances with the
+    // position, and step i goes to owner rank + 1 + i (this rank's own shard comes last)
+    uint32_t j = cta * kThreads + threadIdx.x;
+    uint32_t i = j / sub.count, k = j - i * sub.count;
+    for (; j < total; j += stride, k += stride) {
+        while (k >= sub.count) k -= sub.count, i++;
+        uint32_t o = uint32_t(geo.rank) + 1u + i;
+        if (o >= uint32_t(geo.world)) o -= uint32_t(geo.world);
+        const uint32_t in_shard = sub.first + k;
+        uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
+        const int64_t i0 = (int64_t(o) * per_shard + in_shard) * 16;
+        float v[16], dq[16];
+        load16(g, i0, n, v);
+        if (res) {
+            float r[16];
+            load16(res, i0, geo.padded, r);
+#pragma unroll
+            for (int t = 0; t < 16; t++) v[t] = __fadd_rn(v[t], r[t]);
+        }
+        uint32_t e8;
+        const uint2 pk = encode16(v, hmask, e8, dq);
+        if (res) {
+#pragma unroll
+            for (int t = 0; t < 16; t++) dq[t] = __fsub_rn(v[t], dq[t]);
+            store16(res, i0, geo.padded, dq);
+        }
+        reinterpret_cast<uint2 *>(slot)[in_shard] = pk;
+        const uint2 ex = gather_exponents16(e8, hmask);
+        if ((threadIdx.x & 15) == 0) *reinterpret_cast<uint2 *>(slot + exp_off + in_shard / 2) = ex;
+    }
+}
+
+// ---- phase 2: owner ------------------------------------------------------------------
+// WORLD > 0: the world size as a compile-time constant, so that the loads of all
+// senders' slots are issued together before the first decode.  WORLD = 0: any size.
+template <int WORLD>
+__device__ __forceinline__ void reduce_part(float *ores, const WireGeom &geo, const Peers &peers, int reverse, Sub sub,
+                                            uint32_t cta, uint32_t ncta)
+{
+    const int world = WORLD ? WORLD : geo.world;
+    const uint32_t hmask = half_mask();
+    const uint32_t end = sub.first + sub.count;
+    const uint32_t stride = ncta * kThreads;
+    const uint8_t *rs = peers.arena[geo.rank] + geo.rs_off;
+    const int64_t exp_off = geo.shard / 2;
+    for (uint32_t g16 = sub.first + cta * kThreads + threadIdx.x; g16 < end; g16 += stride) {
+        float val[16], dq[16], r[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) val[i] = 0.0f;
+        if (ores) load16(ores, int64_t(g16) * 16, geo.shard, r);
+        if (WORLD) {
+            constexpr int B = WORLD < 4 ? (WORLD ? WORLD : 1) : 4;     // senders whose loads are in flight together
+#pragma unroll
+            for (int t0 = 0; t0 < WORLD; t0 += B) {
+                uint2 pk[B];
+                uint32_t eb[B];
+#pragma unroll
+                for (int t = 0; t < B; t++) {
+                    const uint8_t *slot = rs + int64_t(reverse ? WORLD - 1 - (t0 + t) : t0 + t) * geo.slot_bytes;
+                    pk[t] = reinterpret_cast<const uint2 *>(slot)[g16];
+                    eb[t] = slot[exp_off + g16 / 2];
+                }
+#pragma unroll
+                for (int t = 0; t < B; t++) add_decoded16(pk[t], eb[t], val);
+            }
+        } else {
+            for (int t = 0; t < world; t++) {
+                const uint8_t *slot = rs + int64_t(reverse ? world - 1 - t : t) * geo.slot_bytes;
+                add_decoded16(reinterpret_cast<const uint2 *>(slot)[g16], slot[exp_off + g16 / 2], val);
+            }
+        }
+        if (ores) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) val[i] = __fadd_rn(val[i], r[i]);
+        }
+        uint32_t e8;
+        const uint2 pk2 = encode16(val, hmask, e8, dq);
+        if (ores) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) dq[i] = __fsub_rn(val[i], dq[i]);
+            store16(ores, int64_t(g16) * 16, geo.shard, dq);
+        }
+        const uint2 ex = gather_exponents16(e8, hmask);
+        const bool first_lane = (threadIdx.x & 15) == 0;
+        // every rank's gather slot, starting at the right-hand neighbour
+#pragma unroll
+        for (int i = 0; i < (WORLD ? WORLD : kMaxWorld); i++) {
+            if (i >= world) break;
+            int p = geo.rank + 1 + i;
+            if (p >= world) p -= world;
+            uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
+            reinterpret_cast<uint2 *>(slot)[g16] = pk2;
+            if (first_lane) *reinterpret_cast<uint2 *>(slot + exp_off + g16 / 2) = ex;
+        }
+    }
+}
+
+__device__ __forceinline__ void reduce_any(float *ores, const WireGeom &geo, const Peers &peers, int reverse, Sub sub,
+                                           uint32_t cta, uint32_t ncta)
+{
+    switch (geo.world) {
+    case 1: reduce_part<1>(ores, geo, peers, reverse, sub, cta, ncta); break;
+    case 2: reduce_part<2>(ores, geo, peers, reverse, sub, cta, ncta); break;
+    case 4: reduce_part<4>(ores, geo, peers, reverse, sub, cta, ncta); break;
+    case 8: reduce_part<8>(ores, geo, peers, reverse, sub, cta, ncta); break;
+    default: reduce_part<0>(ores, geo, peers, reverse, sub, cta, ncta); break;
+    }
+}
+
+// ---- phase 3: everyone ---------------------------------------------------------------
+// One thread decodes 16 values (one 8-byte packed word) and writes two 32-byte words; U
+// groups per thread are in flight.  POW2: the world size is a power of two, so dividing by
+// it is an exact multiplication that folds into the block scale.  Otherwise an IEEE
+// division (wire.py:138 `.div_(world)`).
+template <bool POW2>
+__device__ __forceinline__ void finish_part(float *g, int64_t n, const WireGeom &geo, const Peers &peers, Sub sub,
+                                            uint32_t cta, uint32_t ncta)
+{
+    constexpr int U = 2;
+    const uint8_t *my = peers.arena[geo.rank];
+    const uint32_t stride = ncta * kThreads;
+    const uint32_t end = sub.first + sub.count;
+    const float w = float(geo.world), rw = 1.0f / w;
+    for (int o = 0; o < geo.world; o++) {
+        const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
+        const uint8_t *slot_e = slot + geo.shard / 2;
+        const int64_t first = int64_t(o) * geo.shard;
+        if (first >= n) break;
+        const int64_t left = (n - first + 15) / 16;             // groups of this shard that hold elements of g
+        const uint32_t count = left < int64_t(end) ? uint32_t(left) : end;
+        float *gs = g + first;
+        const int64_t ns = n - first;                           // elements of g in this shard and beyond
+        for (uint32_t q0 = sub.first + cta * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
+            uint2 pk[U];
+            uint32_t e8[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const uint32_t q = q0 + u * stride;
+                const bool ok = q < count;
+                pk[u] = ok ? reinterpret_cast<const uint2 *>(slot)[q] : make_uint2(0u, 0u);
+                e8[u] = ok ? slot_e[q >> 1] : 127u;
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const uint32_t q = q0 + u * stride;
+                if (q >= count) break;
+                float sc = __uint_as_float(scale_bits(e8[u]));
+                if (POW2) sc = __fmul_rn(sc, rw);
+                float t[16];
+                e2m1x4_values(pk[u].x, *reinterpret_cast<float(*)[4]>(t));
+                e2m1x4_values(pk[u].x >> 16, *reinterpret_cast<float(*)[4]>(t + 4));
+                e2m1x4_values(pk[u].y, *reinterpret_cast<float(*)[4]>(t + 8));
+                e2m1x4_values(pk[u].y >> 16, *reinterpret_cast<float(*)[4]>(t + 12));
+#pragma unroll
+                for (int i = 0; i < 16; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
+                store16(gs, int64_t(q) * 16, ns, t);
+            }
+        }
+    }
+}
+
+// ---- the three phases as separate launches ---------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+wire_send_kernel(const float *g, int64_t n, float *res, const __grid_constant__ WireGeom geo,
+                 const __grid_constant__ Peers peers, uint32_t epoch, Sub sub)
+{
+    send_part(g, n, res, geo, peers, sub, blockIdx.x, gridDim.x);
+    Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
+    signal_done(&mine->counter[sub.index][0], gridDim.x, peers, geo.world, geo.rank,
+                offsetof(Header, rs_flag) + sub.index * sizeof(mine->rs_flag[0]), epoch);
+}
+
+__global__ void __launch_bounds__(kThreads, 3)
+wire_reduce_kernel(float *ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
+                   uint32_t epoch, int reverse, Sub sub)
+{
+    Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
+    if (!wait_flags(mine, mine->rs_flag[sub.index], geo.world, epoch, geo.timeout_ns)) return;
+    reduce_any(ores, geo, peers, reverse, sub, blockIdx.x, gridDim.x);
+    signal_done(&mine->counter[sub.index][1], gridDim.x, peers, geo.world, geo.rank,
+                offsetof(Header, ag_flag) + sub.index * sizeof(mine->ag_flag[0]), epoch);
+}
+
+__global__ void __launch_bounds__(kThreads)
+wire_finish_kernel(float *g, int64_t n, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
+                   uint32_t epoch, Sub sub)
+{
+    Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
+    if (!wait_flags(mine, mine->ag_flag[sub.index], geo.world, epoch, geo.timeout_ns)) return;
+    if ((geo.world & (geo.world - 1)) == 0) finish_part<true>(g, n, geo, peers, sub, blockIdx.x, gridDim.x);
+    else finish_part<false>(g, n, geo, peers, sub, blockIdx.x, gridDim.x);
+}
+
+// ---- one cooperative launch ---------------------------------------------------------
+// The grid serves `nranks` ranks (one on a real multi-GPU run; all of them when several
+// ranks are emulated on one GPU, which is how the single-GPU tests exercise the waits
+// between ranks: all CTAs of a cooperative launch are resident together).  Rank v gets
+// CTAs [v * ctas, (v + 1) * ctas).
+struct RankArgs {
+    float *g, *res, *ores;
+    int64_t n;
+    uint32_t epoch;
+    WireGeom geo;
+    Peers peers;
+};
+struct FusedArgs {
+    RankArgs r[kMaxWorld];
+    int nranks, ctas, subs, reverse, stagger;
+};
+
+template <int WORLD>
+__global__ void __launch_bounds__(kThreads, 3)
+wire_fused_kernel(const __grid_constant__ FusedArgs a)
+{
+    const uint32_t vr = blockIdx.x / uint32_t(a.ctas), cta = blockIdx.x - vr * uint32_t(a.ctas), ncta = uint32_t(a.ctas);
+    const RankArgs &ra = a.r[vr];
+    const WireGeom &geo = ra.geo;
+    Header *mine = reinterpret_cast<Header *>(ra.peers.arena[geo.rank]);
+    const int S = a.subs;
+    const uint32_t per = uint32_t(geo.shard / 16) / uint32_t(S);
+    const bool pow2 = (geo.world & (geo.world - 1)) == 0;
+    // Within pipeline step t the three items are independent of each other (each depends on
+    // items of step t - 1 at most), so CTAs may take them in different orders: with `stagger`
+    // a third of the CTAs starts each step with the send, a third with the owner's part and a
+    // third with the decode, which keeps the HBM-bound and the link-bound work mixed on every SM.
+    const int rot = a.stagger ? int(cta % 3u) : 0;
+    bool alive = true;
+    for (int t = 0; t < S + 2 && alive; t++) {
+        for (int q = 0; q < 3 && alive; q++) {
+            const int item = (q + rot) % 3;
+            if (item == 0 && t < S) {
+                const Sub sub{t, uint32_t(t) * per, per};
+                send_part(ra.g, ra.n, ra.res, geo, ra.peers, sub, cta, ncta);
+                signal_done(&mine->counter[t][0], ncta, ra.peers, geo.world, geo.rank,
+                            offsetof(Header, rs_flag) + t * sizeof(mine->rs_flag[0]), ra.epoch);
+            } else if (item == 1 && t >= 1 && t - 1 < S) {
+                const int c = t - 1;
+                const Sub sub{c, uint32_t(c) * per, per};
+                alive = wait_flags(mine, mine->rs_flag[c], geo.world, ra.epoch, geo.timeout_ns);
+                if (alive) {
+                    reduce_part<WORLD>(ra.ores, geo, ra.peers, a.reverse, sub, cta, ncta);
+                    signal_done(&mine->counter[c][1], ncta, ra.peers, geo.world, geo.rank,
+                                offsetof(Header, ag_flag) + c * sizeof(mine->ag_flag[0]), ra.epoch);
+                }
+            } else if (item == 2 && t >= 2) {
+                const int c = t - 2;
+                const Sub sub{c, uint32_t(c) * per, per};
+                alive = wait_flags(mine, mine->ag_flag[c], geo.world, ra.epoch, geo.timeout_ns);
+                if (alive) {
+                    if (pow2) finish_part<true>(ra.g, ra.n, geo, ra.peers, sub, cta, ncta);
+                    else finish_part<false>(ra.g, ra.n, geo, ra.peers, sub, cta, ncta);
+                }
+            }
+        }
+    }
+}
+
+// ======================================================================================
+// Integer wires of the reference (wire.py:104-138): one fp32 scale per chunk of 64, shared
+// by all ranks (maximum over ranks), exact int32 sum at the owner, owner re-encodes with its
+// own grid, gather.  Same transport as above; every fp32 operation is the one torch runs,
+// explicitly rounded (division by IEEE divide, rounding to nearest even integer).
+// One thread owns 8 consecutive elements; 8 adjacent lanes share a chunk.
+// ======================================================================================
+constexpr int kChunk = 64;
 
 __device__ __forceinline__ void load8(const float *p, int64_t i0, int64_t n, float (&v)[8])
 {
@@ -188,196 +547,6 @@ __device__ __forceinline__ void store8(float *p, int64_t i0, int64_t n, const fl
             if (i0 + i < n) p[i0 + i] = v[i];
     }
 }
-
-// ---- phase 1: sender ---------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
-wire_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__ res, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
-                 uint32_t epoch, Chunk ch)
-{
-    const uint32_t stride = gridDim.x * kThreads;
-    const int lane = threadIdx.x & 31;
-    const uint32_t g_per_shard = uint32_t(geo.shard / 8);      // a multiple of 32: warps never straddle shards
-    const uint32_t total = uint32_t(geo.world) * ch.count;
-    // one flat loop over the piece's groups of all owners; the owner index advances with the position
-    uint32_t j = blockIdx.x * kThreads + threadIdx.x;
-    uint32_t o = j / ch.count, k = j - o * ch.count;
-    for (; j < total; j += stride, k += stride) {
-        while (k >= ch.count) k -= ch.count, o++;
-        const uint32_t in_shard = ch.first + k, g8 = o * g_per_shard + in_shard;
-        uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
-        const int64_t i0 = int64_t(g8) * 8;
-        float v[8], dq[8];
-        load8(g, i0, n, v);
-        if (res) {
-            float r[8];
-            load8(res, i0, geo.padded, r);
-#pragma unroll
-            for (int i = 0; i < 8; i++) v[i] = __fadd_rn(v[i], r[i]);
-        }
-        uint32_t e8;
-        const uint32_t pk = encode8(v, e8, dq);
-        if (res) {
-            float r[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(v[i], dq[i]);
-            store8(res, i0, geo.padded, r);
-        }
-        reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
-        const uint2 ex = gather_exponents(e8);
-        if (lane == 0) *reinterpret_cast<uint2 *>(slot + geo.shard / 2 + in_shard / 4) = ex;
-    }
-    Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
-    signal_done(mine, &mine->counter[ch.index][0], peers, geo.world, geo.rank,
-                offsetof(Header, rs_flag) + ch.index * sizeof(mine->rs_flag[0]), epoch);
-}
-
-// ---- phase 2: owner ------------------------------------------------------------------
-// WORLD > 0: the world size as a compile-time constant, so that the loads of all
-// senders' slots are issued together before the first decode.  WORLD = 0: any size.
-template <int WORLD>
-__global__ void __launch_bounds__(kThreads)
-wire_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch, int reverse,
-                   Chunk ch)
-{
-    uint8_t *my = peers.arena[geo.rank];
-    Header *mine = reinterpret_cast<Header *>(my);
-    const int world = WORLD ? WORLD : geo.world;
-    wait_flags(mine, mine->rs_flag[ch.index], world, epoch, geo.poll_limit);
-    const uint32_t groups = ch.first + ch.count;               // end of this piece inside the shard
-    const uint32_t stride = gridDim.x * kThreads;
-    const int lane = threadIdx.x & 31;
-    const uint8_t *rs = my + geo.rs_off;
-    const int64_t exp_off = geo.shard / 2;
-    for (uint32_t g8 = ch.first + blockIdx.x * kThreads + threadIdx.x; g8 < groups; g8 += stride) {
-        float val[8], dq[8], r[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) val[i] = 0.0f;
-        if (ores) load8(ores, int64_t(g8) * 8, geo.shard, r);
-        if (WORLD) {
-            uint32_t pk[WORLD ? WORLD : 1], eb[WORLD ? WORLD : 1];
-#pragma unroll
-            for (int t = 0; t < WORLD; t++) {
-                const uint8_t *slot = rs + int64_t(reverse ? WORLD - 1 - t : t) * geo.slot_bytes;
-                pk[t] = reinterpret_cast<const uint32_t *>(slot)[g8];
-                eb[t] = slot[exp_off + g8 / 4];
-            }
-#pragma unroll
-            for (int t = 0; t < WORLD; t++) {
-                const float sc = __uint_as_float(scale_bits(eb[t]));
-                float lo[4], hi[4];
-                e2m1x4_values(pk[t], lo);
-                e2m1x4_values(pk[t] >> 16, hi);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    val[i] = __fadd_rn(val[i], __fmul_rn(lo[i], sc));
-                    val[4 + i] = __fadd_rn(val[4 + i], __fmul_rn(hi[i], sc));
-                }
-            }
-        } else {
-            for (int t = 0; t < world; t++) {
-                const uint8_t *slot = rs + int64_t(reverse ? world - 1 - t : t) * geo.slot_bytes;
-                const uint32_t pk = reinterpret_cast<const uint32_t *>(slot)[g8];
-                const float sc = __uint_as_float(scale_bits(slot[exp_off + g8 / 4]));
-                float lo[4], hi[4];
-                e2m1x4_values(pk, lo);
-                e2m1x4_values(pk >> 16, hi);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    val[i] = __fadd_rn(val[i], __fmul_rn(lo[i], sc));
-                    val[4 + i] = __fadd_rn(val[4 + i], __fmul_rn(hi[i], sc));
-                }
-            }
-        }
-        if (ores) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
-        }
-        uint32_t e8;
-        const uint32_t pk2 = encode8(val, e8, dq);
-        if (ores) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) r[i] = __fsub_rn(val[i], dq[i]);
-            store8(ores, int64_t(g8) * 8, geo.shard, r);
-        }
-        const uint2 ex = gather_exponents(e8);
-#pragma unroll
-        for (int p = 0; p < (WORLD ? WORLD : kMaxWorld); p++) {
-            if (p >= world) break;
-            uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
-            reinterpret_cast<uint32_t *>(slot)[g8] = pk2;
-            if (lane == 0) *reinterpret_cast<uint2 *>(slot + exp_off + g8 / 4) = ex;
-        }
-    }
-    signal_done(mine, &mine->counter[ch.index][1], peers, world, geo.rank,
-                offsetof(Header, ag_flag) + ch.index * sizeof(mine->ag_flag[0]), epoch);
-}
-
-// ---- phase 3: everyone ---------------------------------------------------------------
-// One thread decodes 4 values (two packed bytes) per step and writes one 16-byte
-// word, so every load and store of a warp is one contiguous segment.  POW2: the
-// world size is a power of two, so dividing by it is an exact multiplication that
-// folds into the block scale.  Otherwise an IEEE division (wire.py:138 `.div_(world)`).
-template <bool POW2>
-__global__ void __launch_bounds__(kThreads)
-wire_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers, uint32_t epoch,
-                   Chunk ch)
-{
-    constexpr int U = 4;                                        // independent quads in flight per thread
-    uint8_t *my = peers.arena[geo.rank];
-    Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->ag_flag[ch.index], geo.world, epoch, geo.poll_limit);
-    const uint32_t stride = gridDim.x * kThreads;
-    const uint32_t q_first = 2 * ch.first, q_end = 2 * (ch.first + ch.count);   // this piece in quads of 4 elements
-    const float w = float(geo.world), rw = 1.0f / w;
-    const bool vec = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
-    for (int o = 0; o < geo.world; o++) {
-        const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
-        const uint8_t *slot_e = slot + geo.shard / 2;
-        const int64_t first = int64_t(o) * geo.shard;
-        if (first >= n) break;
-        const int64_t left = (n - first + 3) / 4;
-        const uint32_t count = left < int64_t(q_end) ? uint32_t(left) : q_end;
-        float *gs = g + first;
-        const int64_t ns = n - first;                           // elements of g in this shard and beyond
-        for (uint32_t q0 = q_first + blockIdx.x * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
-            uint32_t pk[U], e8[U];
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                const uint32_t q = q0 + u * stride;
-                const bool ok = q < count;
-                pk[u] = ok ? reinterpret_cast<const uint16_t *>(slot)[q] : 0u;
-                e8[u] = ok ? slot_e[q >> 3] : 127u;
-            }
-#pragma unroll
-            for (int u = 0; u < U; u++) {
-                const uint32_t q = q0 + u * stride;
-                if (q >= count) break;
-                float sc = __uint_as_float(scale_bits(e8[u]));
-                if (POW2) sc = __fmul_rn(sc, rw);
-                float t[4];
-                e2m1x4_values(pk[u], t);
-#pragma unroll
-                for (int i = 0; i < 4; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
-                const int64_t i0 = int64_t(q) * 4;
-                if (vec && i0 + 4 <= ns) {
-                    *reinterpret_cast<float4 *>(gs + i0) = make_float4(t[0], t[1], t[2], t[3]);
-                } else {
-                    for (int i = 0; i < 4; i++)
-                        if (i0 + i < ns) gs[i0 + i] = t[i];
-                }
-            }
-        }
-    }
-}
-
-// ======================================================================================
-// Integer wires of the reference (wire.py:104-138): one fp32 scale per chunk of 64, shared
-// by all ranks (maximum over ranks), exact int32 sum at the owner, owner re-encodes with its
-// own grid, gather.  Same transport as above; every fp32 operation is the one torch runs,
-// explicitly rounded (division by IEEE divide, rounding to nearest even integer).
-// One thread owns 8 consecutive elements; 8 adjacent lanes share a chunk.
-// ======================================================================================
-constexpr int kChunk = 64;
 
 __device__ __forceinline__ float chunk_max8(const float (&v)[8])
 {
@@ -456,7 +625,7 @@ wire_int_max_kernel(const float *__restrict__ g, int64_t n, const float *__restr
                 reinterpret_cast<float *>(peers.arena[p] + geo.mx_off)[geo.rank * chunks + g8 / 8] = m;
     }
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
-    signal_done(mine, &mine->counter_mx, peers, geo.world, geo.rank, offsetof(Header, mx_flag), epoch);
+    signal_done(&mine->counter_mx, gridDim.x, peers, geo.world, geo.rank, offsetof(Header, mx_flag), epoch);
 }
 
 // phase 1: quantize on the shared grid, update the sender residual, push to the owners
@@ -468,7 +637,7 @@ wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__
     constexpr int LIM = (1 << (BITS - 1)) - 1;
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->mx_flag, geo.world, epoch, geo.poll_limit);
+    if (!wait_flags(mine, mine->mx_flag, geo.world, epoch, geo.timeout_ns)) return;
     const uint32_t groups = uint32_t(geo.padded / 8), stride = gridDim.x * kThreads;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);
     uint32_t g8 = blockIdx.x * kThreads + threadIdx.x;
@@ -495,7 +664,7 @@ wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__
         }
         store_q8<BITS>(peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes, in_shard, q);
     }
-    signal_done(mine, &mine->counter[0][0], peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
+    signal_done(&mine->counter[0][0], gridDim.x, peers, geo.world, geo.rank, offsetof(Header, rs_flag), epoch);
 }
 
 // phase 2: exact integer sum at the owner, owner grid, owner residual, push to everyone
@@ -506,7 +675,7 @@ wire_int_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeo
     constexpr int LIM = (1 << (BITS - 1)) - 1;
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->rs_flag[0], geo.world, epoch, geo.poll_limit);
+    if (!wait_flags(mine, mine->rs_flag[0], geo.world, epoch, geo.timeout_ns)) return;
     const uint32_t groups = uint32_t(geo.shard / 8), stride = gridDim.x * kThreads;
     const int64_t first_chunk = int64_t(geo.rank) * (geo.shard / kChunk);
     const int64_t payload = geo.shard * (BITS / 8);
@@ -544,7 +713,7 @@ wire_int_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeo
             if ((threadIdx.x & 7) == 0) reinterpret_cast<float *>(slot + payload)[g8 / 8] = s2;
         }
     }
-    signal_done(mine, &mine->counter[0][1], peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
+    signal_done(&mine->counter[0][1], gridDim.x, peers, geo.world, geo.rank, offsetof(Header, ag_flag), epoch);
 }
 
 // phase 3: decode the gathered shards, divide by the world size
@@ -554,7 +723,7 @@ wire_int_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    wait_flags(mine, mine->ag_flag[0], geo.world, epoch, geo.poll_limit);
+    if (!wait_flags(mine, mine->ag_flag[0], geo.world, epoch, geo.timeout_ns)) return;
     const uint32_t groups = uint32_t((n + 7) / 8), stride = gridDim.x * kThreads;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);
     const int64_t payload = geo.shard * (BITS / 8);
@@ -614,6 +783,8 @@ static int wire_create(int rank, int world, int64_t padded, int bits, void **out
     if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return fail(LS_EINVAL, "rank %d / world %d unsupported (world <= %d)", rank, world, kMaxWorld);
     if (padded <= 0 || padded % (int64_t(world) * 256) != 0)
         return fail(LS_EINVAL, "padded=%lld must be a positive multiple of world*256", (long long)padded);
+    if (padded / 4 > int64_t(0xFFFFFFFFu) - (int64_t(1) << 24))
+        return fail(LS_EINVAL, "padded=%lld exceeds the 32-bit group index of the wire kernels", (long long)padded);
     Wire *w = new (std::nothrow) Wire();
     if (!w) return fail(LS_ECUDA, "out of host memory");
     w->g.rank = rank, w->g.world = world, w->g.padded = padded, w->g.shard = padded / world;
@@ -621,23 +792,26 @@ static int wire_create(int rank, int world, int64_t padded, int bits, void **out
     w->g.slot_bytes = (raw + 255) / 256 * 256;
     w->g.rs_off = int64_t(kHeaderBytes);
     w->g.ag_off = w->g.rs_off + w->g.slot_bytes * world;
-    w->g.poll_limit = kPollLimit;
+    w->g.timeout_ns = kDefaultTimeoutNs;
     w->g.bits = bits;
     w->g.mx_off = w->g.ag_off + w->g.slot_bytes * world;
     w->arena_bytes = size_t(w->g.mx_off + (bits ? int64_t(world) * (padded / kChunk) * 4 : 0));
     w->mapped = false;
     w->epoch = 0;
-    w->chunks = 0;
-    w->pipe_ready = false;
+    w->mode = 0, w->subs = 0, w->fused_ctas = 0;
+    w->status_host = nullptr;
     for (int i = 0; i < kMaxWorld; i++) w->opened[i] = false, w->peers.arena[i] = nullptr;
     cudaError_t e = cudaGetDevice(&w->dev);
     if (e == cudaSuccess) e = cudaMalloc(&w->arena, w->arena_bytes);
     if (e == cudaSuccess) e = cudaMemset(w->arena, 0, w->arena_bytes);
+    if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void **>(&w->status_host), sizeof(int), cudaHostAllocDefault);
     if (e != cudaSuccess) {
         size_t bytes = w->arena_bytes;
+        if (w->arena) cudaFree(w->arena);
         delete w;
         return fail(LS_ECUDA, "wire arena of %zu bytes: %s", bytes, cudaGetErrorString(e));
     }
+    *w->status_host = 0;
     w->peers.arena[rank] = w->arena;
     if (world == 1) w->mapped = true;
     *out = w;
@@ -651,12 +825,8 @@ extern "C" int ls_wire_destroy(void *h)
     cudaDeviceSynchronize();
     for (int i = 0; i < kMaxWorld; i++)
         if (w->opened[i]) cudaIpcCloseMemHandle(w->peers.arena[i]);
-    if (w->pipe_ready) {
-        cudaStreamDestroy(w->s_reduce), cudaStreamDestroy(w->s_finish);
-        cudaEventDestroy(w->ev_start), cudaEventDestroy(w->ev_done);
-        for (int c = 0; c < kMaxChunks; c++) cudaEventDestroy(w->ev_sent[c]), cudaEventDestroy(w->ev_reduced[c]);
-    }
     cudaFree(w->arena);
+    if (w->status_host) cudaFreeHost(w->status_host);
     delete w;
     return LS_OK;
 }
@@ -703,65 +873,66 @@ extern "C" int ls_wire_map_local(void *h, void *const *wires)
 }
 
 namespace {
-Chunk whole_shard(const Wire *w) { return Chunk{0, 0u, uint32_t(w->g.shard / 8)}; }
+Sub whole_shard(const Wire *w) { return Sub{0, 0u, uint32_t(w->g.shard / 16)}; }
 
-int launch_send(Wire *w, const float *g, int64_t numel, float *res, Chunk ch, int ctas_per_sm, cudaStream_t st)
+// Sub-ranges of the cooperative launch: the requested number, lowered until it divides the
+// shard into pieces of whole half-warps (multiples of 256 elements).
+int subs_of(const Wire *w, int want)
 {
-    wire_send_kernel<<<grid_for(int64_t(w->g.world) * ch.count, ctas_per_sm), kThreads, 0, st>>>(g, numel, res, w->g, w->peers,
-                                                                                               w->epoch, ch);
-    LS_LAUNCH_CHECK("wire_send");
-    return LS_OK;
+    const int64_t units = w->g.shard / 256;
+    int s = want > 0 ? want : 4;
+    if (s > kMaxSub) s = kMaxSub;
+    while (s > 1 && units % s != 0) s--;
+    return s;
 }
 
-int launch_reduce(Wire *w, float *ores, int reverse, Chunk ch, int ctas_per_sm, cudaStream_t st)
+const void *fused_entry(int world)
 {
-    const int grid = grid_for(ch.count, ctas_per_sm);
-    switch (w->g.world) {
-    case 1: wire_reduce_kernel<1><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
-    case 2: wire_reduce_kernel<2><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
-    case 4: wire_reduce_kernel<4><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
-    case 8: wire_reduce_kernel<8><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
-    default: wire_reduce_kernel<0><<<grid, kThreads, 0, st>>>(ores, w->g, w->peers, w->epoch, reverse, ch); break;
+    switch (world) {
+    case 1: return reinterpret_cast<const void *>(wire_fused_kernel<1>);
+    case 2: return reinterpret_cast<const void *>(wire_fused_kernel<2>);
+    case 4: return reinterpret_cast<const void *>(wire_fused_kernel<4>);
+    case 8: return reinterpret_cast<const void *>(wire_fused_kernel<8>);
+    default: return reinterpret_cast<const void *>(wire_fused_kernel<0>);
     }
-    LS_LAUNCH_CHECK("wire_reduce");
-    return LS_OK;
 }
 
-int launch_finish(Wire *w, float *g, int64_t numel, Chunk ch, int ctas_per_sm, cudaStream_t st)
+// CTAs of the cooperative kernel that can be resident on this device at once.
+int fused_capacity(Wire *w)
 {
-    const bool pow2 = (w->g.world & (w->g.world - 1)) == 0;
-    const int grid = grid_for((int64_t(w->g.world) * ch.count + 1) / 2, ctas_per_sm);    // four quads per thread and step
-    if (pow2) wire_finish_kernel<true><<<grid, kThreads, 0, st>>>(g, numel, w->g, w->peers, w->epoch, ch);
-    else wire_finish_kernel<false><<<grid, kThreads, 0, st>>>(g, numel, w->g, w->peers, w->epoch, ch);
-    LS_LAUNCH_CHECK("wire_finish");
-    return LS_OK;
-}
-
-int pipe_setup(Wire *w)
-{
-    if (w->pipe_ready) return LS_OK;
-    LS_CUDA(cudaStreamCreateWithFlags(&w->s_reduce, cudaStreamNonBlocking));
-    LS_CUDA(cudaStreamCreateWithFlags(&w->s_finish, cudaStreamNonBlocking));
-    LS_CUDA(cudaEventCreateWithFlags(&w->ev_start, cudaEventDisableTiming));
-    LS_CUDA(cudaEventCreateWithFlags(&w->ev_done, cudaEventDisableTiming));
-    for (int c = 0; c < kMaxChunks; c++) {
-        LS_CUDA(cudaEventCreateWithFlags(&w->ev_sent[c], cudaEventDisableTiming));
-        LS_CUDA(cudaEventCreateWithFlags(&w->ev_reduced[c], cudaEventDisableTiming));
+    if (!w->fused_ctas) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_entry(w->g.world), kThreads, 0) != cudaSuccess || per_sm < 1)
+            return 0;
+        w->fused_ctas = per_sm * sm_count();
     }
-    w->pipe_ready = true;
+    return w->fused_ctas;
+}
+
+void fill_rank(RankArgs &r, Wire *w, float *g, int64_t numel, float *res, float *ores)
+{
+    r.g = g, r.res = res, r.ores = ores, r.n = numel, r.epoch = w->epoch, r.geo = w->g, r.peers = w->peers;
+}
+
+int launch_fused(FusedArgs &a, int capacity, cudaStream_t st)
+{
+    const int64_t groups = int64_t(a.r[0].geo.world) * (a.r[0].geo.shard / 16) / a.subs;     // send work of one sub-range
+    int ctas = capacity / a.nranks;
+    const int64_t want = (groups + kThreads - 1) / kThreads;
+    if (want < ctas) ctas = int(want < 1 ? 1 : want);
+    if (ctas < 1) return fail(LS_ECUDA, "the cooperative wire kernel does not fit %d ranks on this device", a.nranks);
+    a.ctas = ctas;
+    void *params[] = {&a};
+    LS_CUDA(cudaLaunchCooperativeKernel(fused_entry(a.r[0].geo.world), dim3(unsigned(ctas * a.nranks)),
+                                        dim3(kThreads), params, 0, st));
     return LS_OK;
 }
 
-// Pieces per call.  One unless the caller asks for more: on 1 and 2 GPUs the three phases
-// of concurrent pieces compete for HBM (64 Mi elements, error feedback on: 312 -> 356 us
-// alone, 284 -> 349 us with one peer at four pieces), which costs more than the hidden
-// exchange latency saves.
-int pieces_of(const Wire *w)
+int copy_status(Wire *w, cudaStream_t st)
 {
-    const int64_t groups = w->g.shard / 8;
-    int c = w->chunks > 0 ? w->chunks : 1;
-    while (c > 1 && groups % (int64_t(c) * 32) != 0) c--;
-    return c;
+    LS_CUDA(cudaMemcpyAsync(w->status_host, &reinterpret_cast<Header *>(w->arena)->status, sizeof(int),
+                            cudaMemcpyDeviceToHost, st));
+    return LS_OK;
 }
 }  // namespace
 
@@ -770,30 +941,53 @@ extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, 
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
     w->epoch++;
-    return launch_send(w, g, numel, res, whole_shard(w), 5, static_cast<cudaStream_t>(stream));
+    const Sub sub = whole_shard(w);
+    wire_send_kernel<<<grid_for(int64_t(w->g.world) * sub.count, 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        g, numel, res, w->g, w->peers, w->epoch, sub);
+    LS_LAUNCH_CHECK("wire_send");
+    return LS_OK;
 }
 
 extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
 {
     Wire *w = as_wire(h);
-    if (!w || !w->mapped) return fail(LS_ESTATE, "wire not ready");
-    return launch_reduce(w, ores, reverse, whole_shard(w), 4, static_cast<cudaStream_t>(stream));
+    if (!w || !w->mapped || w->g.bits) return fail(LS_ESTATE, "wire not ready");
+    const Sub sub = whole_shard(w);
+    wire_reduce_kernel<<<grid_for(sub.count, 3), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        ores, w->g, w->peers, w->epoch, reverse, sub);
+    LS_LAUNCH_CHECK("wire_reduce");
+    return LS_OK;
 }
 
 extern "C" int ls_wire_finish(void *h, float *g, int64_t numel, void *stream)
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
-    return launch_finish(w, g, numel, whole_shard(w), 8, static_cast<cudaStream_t>(stream));
+    const Sub sub = whole_shard(w);
+    // two groups per thread and step
+    wire_finish_kernel<<<grid_for((int64_t(w->g.world) * sub.count + 1) / 2, 6), kThreads, 0,
+                         static_cast<cudaStream_t>(stream)>>>(g, numel, w->g, w->peers, w->epoch, sub);
+    LS_LAUNCH_CHECK("wire_finish");
+    return copy_status(w, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ls_wire_set_chunks(void *h, int chunks)
+extern "C" int ls_wire_set_mode(void *h, int mode, int subs, int stagger)
 {
     Wire *w = as_wire(h);
     if (!w) return fail(LS_EINVAL, "null wire handle");
-    if (chunks < 0 || chunks > kMaxChunks) return fail(LS_EINVAL, "chunks must be 0 (choose) or 1..%d", kMaxChunks);
-    w->chunks = chunks;
+    if (mode < 0 || mode > 2) return fail(LS_EINVAL, "mode must be 0 (choose), 1 (three launches) or 2 (one cooperative launch)");
+    if (subs < 0 || subs > kMaxSub) return fail(LS_EINVAL, "sub-ranges must be 0 (choose) or 1..%d", kMaxSub);
+    w->mode = mode | (stagger ? 0x100 : 0), w->subs = subs;
     return LS_OK;
+}
+
+// 1 = three launches, 2 = one cooperative launch: what ls_wire_allreduce runs on this handle.
+extern "C" int ls_wire_mode(void *h)
+{
+    Wire *w = as_wire(h);
+    if (!w) return 0;
+    const int m = w->mode & 0xFF;
+    return m ? m : 2;
 }
 
 extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, float *ores, int reverse,
@@ -801,35 +995,47 @@ extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, f
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
-    const int pieces = pieces_of(w);
-    if (pieces == 1) {
+    if (ls_wire_mode(h) == 1) {
         if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
         if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
         return ls_wire_finish(h, g, numel, stream);
     }
-    // Send pieces follow each other on the caller's stream; the owner phase of piece c
-    // runs on a second stream once piece c is sent, its decode on a third once it is
-    // reduced here.  The grids leave room for the three kernels to be resident together:
-    // a kernel that waits for its peers must not keep the others off the SMs.
-    if (int rc = pipe_setup(w)) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int capacity = fused_capacity(w);
+    if (!capacity) return fail(LS_ECUDA, "could not size the cooperative wire kernel");
     w->epoch++;
-    const uint32_t per = uint32_t(w->g.shard / 8 / pieces);
-    LS_CUDA(cudaEventRecord(w->ev_start, st));
-    LS_CUDA(cudaStreamWaitEvent(w->s_reduce, w->ev_start, 0));     // residuals and g are ready when the caller's stream says so
-    LS_CUDA(cudaStreamWaitEvent(w->s_finish, w->ev_start, 0));
-    for (int c = 0; c < pieces; c++) {
-        const Chunk ch{c, uint32_t(c) * per, per};
-        if (int rc = launch_send(w, g, numel, res, ch, 3, st)) return rc;
-        LS_CUDA(cudaEventRecord(w->ev_sent[c], st));
-        LS_CUDA(cudaStreamWaitEvent(w->s_reduce, w->ev_sent[c], 0));
-        if (int rc = launch_reduce(w, ores, reverse, ch, 2, w->s_reduce)) return rc;
-        LS_CUDA(cudaEventRecord(w->ev_reduced[c], w->s_reduce));
-        LS_CUDA(cudaStreamWaitEvent(w->s_finish, w->ev_reduced[c], 0));
-        if (int rc = launch_finish(w, g, numel, ch, 2, w->s_finish)) return rc;
+    FusedArgs a{};
+    fill_rank(a.r[0], w, g, numel, res, ores);
+    a.nranks = 1, a.subs = subs_of(w, w->subs), a.reverse = reverse, a.stagger = (w->mode & 0x100) ? 1 : 0;
+    if (int rc = launch_fused(a, capacity, static_cast<cudaStream_t>(stream))) return rc;
+    return copy_status(w, static_cast<cudaStream_t>(stream));
+}
+
+// All ranks of a group created in ONE process on one GPU (ls_wire_map_local), one step, one
+// cooperative launch: every rank's CTAs are resident together, so the waits between ranks
+// are met inside the launch.  handles / gs / ress / oress: arrays of `world` entries in
+// rank order (ress / oress or their entries may be NULL).
+extern "C" int ls_wire_allreduce_group(void *const *handles, float *const *gs, int64_t numel, float *const *ress,
+                                       float *const *oress, int reverse, void *stream)
+{
+    if (!handles || !gs) return fail(LS_EINVAL, "null argument");
+    Wire *w0 = as_wire(handles[0]);
+    if (int rc = check_call(w0, gs[0], numel)) return rc;
+    const int world = w0->g.world;
+    const int capacity = fused_capacity(w0);
+    if (!capacity) return fail(LS_ECUDA, "could not size the cooperative wire kernel");
+    FusedArgs a{};
+    for (int r = 0; r < world; r++) {
+        Wire *w = as_wire(handles[r]);
+        if (int rc = check_call(w, gs[r], numel)) return rc;
+        if (w->g.rank != r || w->g.world != world || w->g.padded != w0->g.padded || w->dev != w0->dev)
+            return fail(LS_EINVAL, "handle %d does not belong to this group", r);
+        w->epoch++;
+        fill_rank(a.r[r], w, gs[r], numel, ress ? ress[r] : nullptr, oress ? oress[r] : nullptr);
     }
-    LS_CUDA(cudaEventRecord(w->ev_done, w->s_finish));
-    LS_CUDA(cudaStreamWaitEvent(st, w->ev_done, 0));
+    a.nranks = world, a.subs = subs_of(w0, w0->subs), a.reverse = reverse, a.stagger = (w0->mode & 0x100) ? 1 : 0;
+    if (int rc = launch_fused(a, capacity, static_cast<cudaStream_t>(stream))) return rc;
+    for (int r = 0; r < world; r++)
+        if (int rc = copy_status(as_wire(handles[r]), static_cast<cudaStream_t>(stream))) return rc;
     return LS_OK;
 }
 
@@ -863,6 +1069,7 @@ extern "C" int ls_wire_int_phase(void *h, int phase, float *g, int64_t numel, fl
         return fail(LS_EINVAL, "phase must be 0..3");
     }
     LS_LAUNCH_CHECK("wire_int_phase");
+    if (phase == 3) return copy_status(w, st);
     return LS_OK;
 }
 
@@ -873,11 +1080,12 @@ extern "C" int ls_wire_int_allreduce(void *h, float *g, int64_t numel, float *re
     return LS_OK;
 }
 
-extern "C" int ls_wire_set_poll_limit(void *h, int64_t polls)
+extern "C" int ls_wire_set_timeout_us(void *h, int64_t microseconds)
 {
     Wire *w = as_wire(h);
-    if (!w || polls < 1 || polls > (int64_t(1) << 31)) return fail(LS_EINVAL, "bad wire handle or poll limit");
-    w->g.poll_limit = uint32_t(polls);
+    if (!w || microseconds < 1 || microseconds > int64_t(3600) * 1000 * 1000)
+        return fail(LS_EINVAL, "bad wire handle or time limit (1 us .. 1 h)");
+    w->g.timeout_ns = uint64_t(microseconds) * 1000u;
     return LS_OK;
 }
 
@@ -889,8 +1097,37 @@ extern "C" int ls_wire_status(void *h, int *status_host)
     Header *hd = reinterpret_cast<Header *>(w->arena);
     LS_CUDA(cudaMemcpy(&v, &hd->status, sizeof v, cudaMemcpyDeviceToHost));
     if (v) LS_CUDA(cudaMemset(&hd->status, 0, sizeof v));
+    *w->status_host = 0;
     if (status_host) *status_host = int(v);
     return v ? fail(LS_ETIMEOUT, "a wire kernel gave up waiting for a peer's flag") : LS_OK;
+}
+
+// Non-blocking: what the status word held when the last all-reduce call on this handle
+// finished on its stream (copied to pinned host memory by that call).  A call still in
+// flight is not waited for, so a time-out shows up one call late at the latest.
+extern "C" int ls_wire_poll_status(void *h, int *status_host)
+{
+    Wire *w = as_wire(h);
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    const int v = *static_cast<volatile int *>(w->status_host);
+    if (status_host) *status_host = v;
+    return v ? fail(LS_ETIMEOUT, "a wire kernel gave up waiting for a peer's flag") : LS_OK;
+}
+
+// After a time-out: waits for this device, clears flags, counters and the status word and
+// rewinds the epoch.  Every rank of the wire must call it (and meet in a host-side barrier
+// before and after) before the wire is used again; error-feedback residuals are the
+// caller's to clear.
+extern "C" int ls_wire_reset(void *h)
+{
+    Wire *w = as_wire(h);
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    LS_CUDA(cudaDeviceSynchronize());
+    LS_CUDA(cudaMemset(w->arena, 0, kHeaderBytes));
+    LS_CUDA(cudaDeviceSynchronize());
+    w->epoch = 0;
+    *w->status_host = 0;
+    return LS_OK;
 }
 
 // Raw bytes of the arena, for byte-exact checks of what crossed the wire:

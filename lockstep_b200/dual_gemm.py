@@ -89,6 +89,7 @@ def dual_mxfp4(x1, x2, w_pk, w_sf, out_dtype=torch.bfloat16):
 
 # ---- reference signatures (bf16 / fp8 operands, fp32 out) -------------------
 def _mm(a, b):
+    need_cuda(a, b)
     return a.float() @ b.float()
 
 

@@ -59,9 +59,12 @@ def init():
 
 
 class Wire:
-    """Averages a flat fp32 gradient across ranks, in place, with one method."""
+    """Averages a flat fp32 gradient across ranks, in place, with one method.
 
-    def __init__(self, method, numel, world=1, rank=0):
+    timeout: seconds a kernel of the peer-store transport waits for another rank
+    before it gives up (then the step fails on every rank: see `status`)."""
+
+    def __init__(self, method, numel, world=1, rank=0, timeout=20.0):
         bits = {"int16": 16, "int8": 8, "int8ef": 8}.get(method)
         self.method, self.world, self.rank, self.n = method, world, rank, numel
         self.fp4 = method in ("mxfp4", "mxfp4ef")
@@ -75,6 +78,7 @@ class Wire:
             self.bytes_per_el = 0.5 + 1 / 32       # 16 packed bytes + 1 exponent byte per 32
         else:
             self.bytes_per_el = {"fp32": 4.0, "bf16": 2.0}.get(method) or bits / 8 + 4 / CHUNK
+        self.timeout = timeout
         self._h = None
         self._kpadded = -(-numel // (world * _KUNIT)) * world * _KUNIT
 
@@ -88,6 +92,7 @@ class Wire:
                 bits = 16 if self.dtype == torch.int16 else 8
                 check(lib().ls_wire_create_int(self.rank, self.world, self._kpadded, bits, ctypes.byref(h)))
             self._h = h
+            check(lib().ls_wire_set_timeout_us(h, max(1, int(self.timeout * 1e6))))
             if self.world > 1:
                 nb = int(lib().ls_wire_handle_bytes())
                 blob = (ctypes.c_uint8 * nb)()
@@ -100,21 +105,76 @@ class Wire:
                 dist.barrier()
         return self._h
 
-    def _mxfp4(self, g, reverse):
+    def _residuals(self, device):
+        """The kernels pad to world * 256 elements (the reference to world * 64): the
+        residual buffers have the kernels' length.  `res` is flat [kpadded]; `ores` is
+        [kpadded / world / 64, 64], the reference's owner-residual shape (wire.py:128-130)."""
+        if self.ef and self.res is None:
+            self.res = torch.zeros(self._kpadded, device=device)
+            self.ores = torch.zeros(self._kpadded // self.world // CHUNK, CHUNK, device=device)
+
+    def _check_args(self, g):
         need_cuda(g)
         assert g.dtype == torch.float32 and g.is_contiguous() and g.numel() == self.n
         h = self._handle(g.device)
-        if self.ef and self.res is None:
-            self.res = torch.zeros(self._kpadded, device=g.device)
-            self.ores = torch.zeros(self._kpadded // self.world, device=g.device)
+        self._residuals(g.device)
+        check(lib().ls_wire_poll_status(h, None))        # a time-out of an earlier call: raise before queueing more
+        return h
+
+    def _mxfp4(self, g, reverse):
+        h = self._check_args(g)
         check(lib().ls_wire_allreduce(h, ptr(g), self.n, ptr(self.res), ptr(self.ores), int(bool(reverse)),
                                       stream()))
         return g
+
+    # The three phases of an MXFP4 step as separate launches: send may be queued as soon as
+    # the gradient is final (for instance under the rest of a backward pass, on a side
+    # stream); reduce and finish follow in this order on every rank.
+    def send(self, g):
+        assert self.fp4
+        h = self._check_args(g)
+        check(lib().ls_wire_send(h, ptr(g), self.n, ptr(self.res), stream()))
+
+    def reduce(self, reverse=False):
+        assert self.fp4 and self._h is not None
+        check(lib().ls_wire_reduce(self._h, ptr(self.ores), int(bool(reverse)), stream()))
+
+    def finish(self, g):
+        assert self.fp4 and self._h is not None
+        check(lib().ls_wire_finish(self._h, ptr(g), self.n, stream()))
+        return g
+
+    def set_mode(self, mode="auto", subs=0, stagger=False, device=None):
+        """How an MXFP4 step runs: "launches" (three kernels), "fused" (one cooperative
+        launch that pipelines `subs` sub-ranges of every shard), or "auto"."""
+        h = self._handle(device or torch.device("cuda", torch.cuda.current_device()))
+        check(lib().ls_wire_set_mode(h, {"auto": 0, "launches": 1, "fused": 2}[mode], subs, int(bool(stagger))))
+
+    def mode_name(self):
+        if self._h is None or not self.fp4:
+            return "launches"
+        return {1: "three launches", 2: "one cooperative launch"}[int(lib().ls_wire_mode(self._h))]
 
     def status(self):
         """Raises if a wire kernel gave up waiting for a peer (synchronises)."""
         if self._h is not None:
             check(lib().ls_wire_status(self._h, None))
+
+    def reset(self):
+        """After a time-out: clears flags and residuals and realigns the ranks.
+        Collective when world > 1."""
+        if self._h is None:
+            return
+        if self.world > 1 and dist.is_initialized():
+            torch.cuda.synchronize()
+            dist.barrier()
+        check(lib().ls_wire_reset(self._h))
+        if self.res is not None:
+            self.res.zero_()
+            self.ores.zero_()
+        if self.world > 1 and dist.is_initialized():
+            torch.cuda.synchronize()
+            dist.barrier()
 
     def close(self):
         """Frees the receive arena.  Collective when world > 1: every rank must call
@@ -127,8 +187,9 @@ class Wire:
             self._h = None
 
     def __del__(self):
-        # With peers, memory they may still store into is never freed behind their back:
-        # an unclosed multi-rank wire keeps its arena until the process ends.
+        # With peers, memory they may still store into cannot be freed behind their back, and
+        # a destructor cannot run a collective: an unclosed multi-rank wire keeps its arena
+        # until the process ends.  Call close() on every rank to release it.
         try:
             if self.world == 1:
                 self.close()
@@ -136,11 +197,27 @@ class Wire:
             pass
 
     def state_dict(self):
-        """Residuals carried across steps (what a checkpoint must hold)."""
-        return {"res": self.res, "ores": self.ores}
+        """Residuals carried across steps (what a checkpoint must hold).  `res` is cut to
+        the reference's [padded] (the tail beyond it is padding and stays zero); `ores` is
+        [own, 64].  The shapes equal the reference's whenever numel is a multiple of
+        world * 256; otherwise this wire's shards are longer than the reference's
+        (padded / world) and an owner residual cannot be exchanged with it."""
+        if self.res is None:
+            return {"res": None, "ores": None}
+        return {"res": self.res[:self.padded], "ores": self.ores}
 
     def load_state_dict(self, sd):
-        self.res, self.ores = sd["res"], sd["ores"]
+        if sd["res"] is None:
+            self.res = self.ores = None
+            return
+        dev = sd["res"].device
+        if self.res is None:
+            self._residuals(dev if dev.type == "cuda" else torch.device("cuda", torch.cuda.current_device()))
+        assert sd["res"].numel() in (self.padded, self._kpadded) and sd["ores"].numel() == self.ores.numel(), \
+            "residuals of another geometry"
+        self.res.zero_()
+        self.res[:sd["res"].numel()].copy_(sd["res"].reshape(-1))
+        self.ores.copy_(sd["ores"].reshape(self.ores.shape))
 
     # ---- call ----------------------------------------------------------------
     def __call__(self, g, reverse=False):
@@ -163,12 +240,7 @@ class Wire:
         peer-store transport: shared grid from the maximum over ranks, exact
         int32 sum at the owner, owner grid, gather.  `reverse` has no effect:
         integer sums do not depend on the order (tests/test_wire.py:58-59)."""
-        need_cuda(g)
-        assert g.dtype == torch.float32 and g.is_contiguous() and g.numel() == self.n
-        h = self._handle(g.device)
-        if self.ef and self.res is None:
-            self.res = torch.zeros(self._kpadded, device=g.device)
-            self.ores = torch.zeros(self._kpadded // self.world, device=g.device)
+        h = self._check_args(g)
         check(lib().ls_wire_int_allreduce(h, ptr(g), self.n, ptr(self.res), ptr(self.ores), stream()))
         return g
 
@@ -198,6 +270,7 @@ class LocalWireGroup:
         self.ores = [torch.zeros(self.kpadded // world, device=dev) for _ in range(world)] if ef else [None] * world
 
     def step(self, gs, reverse=False):
+        """One step with the phases as separate launches, rank after rank."""
         L = lib()
         if self.bits:
             for phase in range(4):
@@ -214,6 +287,24 @@ class LocalWireGroup:
             check(L.ls_wire_finish(h, ptr(gs[r]), self.n, stream()))
         for h in self.handles:
             check(L.ls_wire_status(h, None))
+        return gs
+
+    def step_fused(self, gs, reverse=False, subs=0, stagger=False, check_status=True):
+        """One step of every rank as ONE cooperative launch (the pipelined kernel): all
+        ranks' CTAs are resident together, so the waits between ranks are real."""
+        L = lib()
+        assert not self.bits
+        vp = ctypes.c_void_p
+        for h in self.handles:
+            check(L.ls_wire_set_mode(h, 2, subs, int(bool(stagger))))
+        hs = (vp * self.world)(*[h.value for h in self.handles])
+        g_arr = (vp * self.world)(*[g.data_ptr() for g in gs])
+        r_arr = (vp * self.world)(*[None if r is None else r.data_ptr() for r in self.res])
+        o_arr = (vp * self.world)(*[None if o is None else o.data_ptr() for o in self.ores])
+        check(L.ls_wire_allreduce_group(hs, g_arr, self.n, r_arr, o_arr, int(reverse), stream()))
+        if check_status:
+            for h in self.handles:
+                check(L.ls_wire_status(h, None))
         return gs
 
     def slots(self, rank, which):

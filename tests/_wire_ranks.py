@@ -16,7 +16,6 @@ sys.path.insert(0, str(ROOT))
 os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
 from lockstep_b200 import wire          # noqa: E402
-from lockstep_b200._lib import check, lib   # noqa: E402
 from oracle import cref                 # noqa: E402
 
 
@@ -30,10 +29,10 @@ def student_t(n, seed):
 def main():
     rank, world, dev = wire.init()
     n = int(sys.argv[1]) if len(sys.argv) > 1 else 1_000_003
-    for method, pieces in (("mxfp4", 0), ("mxfp4ef", 0), ("mxfp4ef", 4)):
+    for method, mode, subs, stagger in (("mxfp4", "launches", 0, False), ("mxfp4ef", "launches", 0, False),
+                                        ("mxfp4ef", "fused", 0, False), ("mxfp4ef", "fused", 8, True), ("mxfp4", "fused", 2, False)):
         w = wire.Wire(method, n, world, rank)
-        if pieces:                       # the pipelined form (as many pieces, up to 4, as divide the shard)
-            check(lib().ls_wire_set_chunks(w._handle(dev), pieces))
+        w.set_mode(mode, subs, stagger, device=dev)
         ef = method == "mxfp4ef"
         res_c = [np.zeros(w._kpadded, np.float32) for _ in range(world)] if ef else None
         ores_c = [np.zeros(w._kpadded // world, np.float32) for _ in range(world)] if ef else None
@@ -43,13 +42,13 @@ def main():
             g = torch.from_numpy(grads[rank].copy()).to(dev)
             out = w(g)
             w.status()
-            assert np.array_equal(out.cpu().numpy(), want), f"{method} step {step} rank {rank}: bits differ from the oracle"
+            assert np.array_equal(out.cpu().numpy(), want), f"{method} {mode} step {step} rank {rank}: bits differ from the oracle"
             everyone = [torch.empty_like(out) for _ in range(world)]
             dist.all_gather(everyone, out)
             assert all(torch.equal(out, o) for o in everyone), f"{method}: ranks disagree"
             if ef:
                 assert np.array_equal(w.res.cpu().numpy(), res_c[rank])
-                assert np.array_equal(w.ores.cpu().numpy(), ores_c[rank])
+                assert np.array_equal(w.ores.cpu().numpy().reshape(-1), ores_c[rank])
         ref = torch.from_numpy(np.mean(np.stack(grads).astype(np.float64), 0))
         rel = ((out.cpu().double() - ref).norm() / ref.norm()).item()
         if not ef:                       # one-shot gate; with error feedback a step also carries old residuals

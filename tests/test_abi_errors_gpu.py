@@ -67,6 +67,6 @@ def test_wire_argument_errors(L):
     assert L.ls_wire_destroy(h) == 0
     assert L.ls_wire_create(0, 1, 512, ctypes.byref(h)) == 0
     assert L.ls_wire_send(h, _p(g), 1024, None, None) == EINVAL                   # numel beyond the wire
-    assert L.ls_wire_set_poll_limit(h, 0) == EINVAL
-    assert L.ls_wire_set_chunks(h, 9) == EINVAL and L.ls_wire_set_chunks(h, 0) == 0
+    assert L.ls_wire_set_timeout_us(h, 0) == EINVAL and L.ls_wire_set_timeout_us(h, 10**6) == 0
+    assert L.ls_wire_set_mode(h, 3, 0, 0) == EINVAL and L.ls_wire_set_mode(h, 0, 9, 0) == EINVAL and L.ls_wire_set_mode(h, 0, 0, 0) == 0
     assert L.ls_wire_destroy(h) == 0

@@ -164,6 +164,23 @@ def test_integer_wire_golden(golden, method, lim, ef):
         assert np.array_equal(out.numpy(), gd["outs"][s]), (method, s)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("method,lim,ef", [("int16", 32767, False), ("int8", 127, False),
+                                            ("int8ef", 127, True)])
+def test_integer_wire_golden_several_ranks(golden, method, lim, ef, world):
+    # outputs of the real reference Wire on 2 and 4 gloo ranks (make_golden_wire_ranks.py)
+    gd = golden(f"wire_{method}_w{world}")
+    grads = gd["grads"]                                      # [step, rank, n]
+    n = grads.shape[-1]
+    padded = ref_port.padded_len(n, world)
+    res = [torch.zeros(padded) for _ in range(world)] if ef else None
+    ores = [torch.zeros(padded // 64 // world, 64) for _ in range(world)] if ef else None
+    for s in range(3):
+        outs = ref_port.wire_int_step([torch.from_numpy(grads[s, r].copy()) for r in range(world)], lim, res, ores)
+        for r in range(world):
+            assert np.array_equal(outs[r].numpy(), gd["outs"][s]), (method, world, s, r)
+
+
 @pytest.mark.parametrize("world", [1, 2, 4])
 @pytest.mark.parametrize("ef", [False, True])
 def test_mxfp4_wire_golden(golden, world, ef):

@@ -99,35 +99,77 @@ def test_wire_object_one_rank(wire):
         w.close()
 
 
-@pytest.mark.parametrize("pieces", [4, 8, 3])
-def test_pipelined_pieces_do_not_change_anything(wire, pieces):
-    # the all-reduce cut into pieces over three streams: same g, residuals and wire bytes
-    # as the single-piece call, step after step (one rank: the waits are met by this GPU's
-    # own earlier kernels, so nothing waits for a later launch)
-    from lockstep_b200 import _lib
-    L = _lib.lib()
-    n = (1 << 20) + 4096                   # shard = 262144 * 4 + 4096: divisible by 8 * 32 * 4 and * 8, not by 3
+@pytest.mark.parametrize("world,n,subs,stagger", [(1, 70_001, 0, False), (2, 300_000, 4, False), (3, 70_001, 2, True),
+                                                  (4, 1 << 20, 8, True), (8, 100_003, 0, False), (8, 3_000_000, 4, True)])
+def test_cooperative_launch_bytes_and_residuals_vs_oracle(wire, world, n, subs, stagger):
+    # The pipelined kernel (send(t), reduce(t-1), finish(t-2) over sub-ranges, one flag per
+    # sub-range) with every rank's CTAs inside ONE cooperative launch: the waits between ranks
+    # are real.  Same bits as the oracle: g, both residuals and the bytes on the wire.
+    grp = wire.LocalWireGroup(world, n, ef=True)
+    padded, shard = grp.kpadded, grp.kpadded // world
+    res_c = [np.zeros(padded, np.float32) for _ in range(world)]
+    ores_c = [np.zeros(shard, np.float32) for _ in range(world)]
+    for step in range(3):
+        grads = [_student_t(n, 100 * step + r).numpy() for r in range(world)]
+        want, sent, owned = cref.wire_step(grads, res_c, ores_c, unit=256)
+        gs = [torch.from_numpy(g.copy()).cuda() for g in grads]
+        grp.step_fused(gs, subs=subs, stagger=stagger)
+        for r in range(world):
+            assert np.array_equal(gs[r].cpu().numpy(), want), (step, r)
+            assert np.array_equal(grp.res[r].cpu().numpy(), res_c[r])
+            assert np.array_equal(grp.ores[r].cpu().numpy(), ores_c[r])
+            rs = grp.slots(r, 0).cpu().numpy()
+            ag = grp.slots(r, 1).cpu().numpy()
+            for s in range(world):
+                assert np.array_equal(rs[s, :shard // 2], sent[s][0][r * shard // 2:(r + 1) * shard // 2])
+                assert np.array_equal(rs[s, shard // 2:shard // 2 + shard // 32],
+                                      sent[s][1][r * shard // 32:(r + 1) * shard // 32])
+                assert np.array_equal(ag[s, :shard // 2], owned[s][0])
+                assert np.array_equal(ag[s, shard // 2:shard // 2 + shard // 32], owned[s][1])
+    grp.close()
+
+
+def test_cooperative_launch_reverse_and_no_error_feedback(wire):
+    world, n = 4, 50_000
+    grads = [_student_t(n, 7 + r) for r in range(world)]
+    grp = wire.LocalWireGroup(world, n)
+    gs = [g.clone().cuda() for g in grads]
+    grp.step_fused(gs, reverse=True, subs=2)
+    want, _, _ = cref.wire_step([g.numpy() for g in grads], reverse=True, unit=256)
+    for r in range(world):
+        assert np.array_equal(gs[r].cpu().numpy(), want)
+    grp.close()
+
+
+@pytest.mark.parametrize("mode,subs", [("launches", 0), ("fused", 1), ("fused", 4), ("fused", 8), ("fused", 3)])
+def test_wire_modes_give_the_same_bits(wire, mode, subs):
+    # one rank, error feedback, three steps: g and both residuals against the oracle in every mode
+    n = (1 << 20) + 4096
     gen = torch.Generator().manual_seed(5)
-    steps = [torch.randn(n, generator=gen) * 1e-3 for _ in range(3)]
-    outs = []
-    for c in (1, pieces):
-        w = wire.Wire("mxfp4ef", n)
-        h = w._handle(torch.device("cuda", 0))
-        assert L.ls_wire_set_chunks(h, c) == 0
-        per = []
-        for g in steps:
-            x = g.clone().cuda()
-            w(x)
-            per.append((x.cpu(), w.res.cpu().clone(), w.ores.cpu().clone()))
-        w.status()
-        w.close()
-        outs.append(per)
-    for a, b in zip(*outs):
-        assert all(torch.equal(x, y) for x, y in zip(a, b))
     w = wire.Wire("mxfp4ef", n)
-    h = w._handle(torch.device("cuda", 0))
-    assert L.ls_wire_set_chunks(h, 9) < 0 and L.ls_wire_set_chunks(h, -1) < 0
+    w.set_mode(mode, subs, stagger=subs == 4)
+    assert w.mode_name() == ("three launches" if mode == "launches" else "one cooperative launch")
+    res_c, ores_c = [np.zeros(w._kpadded, np.float32)], [np.zeros(w._kpadded, np.float32)]
+    for _ in range(3):
+        g = torch.randn(n, generator=gen) * 1e-3
+        want, _, _ = cref.wire_step([g.numpy()], res_c, ores_c, unit=256)
+        x = g.clone().cuda()
+        w(x)
+        assert np.array_equal(x.cpu().numpy(), want)
+        assert np.array_equal(w.res.cpu().numpy(), res_c[0])
+        assert np.array_equal(w.ores.cpu().numpy().reshape(-1), ores_c[0])
+    w.status()
+    sd = w.state_dict()
+    assert sd["res"].shape == (w.padded,) and sd["ores"].shape == (w._kpadded // 64, 64)
+    w2 = wire.Wire("mxfp4ef", n)
+    w2.load_state_dict({k: v.clone() for k, v in sd.items()})
+    g = torch.randn(n, generator=gen) * 1e-3
+    a, b = w(g.clone().cuda()), w2(g.clone().cuda())
+    assert torch.equal(a, b) and torch.equal(w.res, w2.res) and torch.equal(w.ores, w2.ores)
+    from lockstep_b200 import _lib
+    assert _lib.lib().ls_wire_set_mode(w._h, 3, 0, 0) < 0 and _lib.lib().ls_wire_set_mode(w._h, 2, 9, 0) < 0
     w.close()
+    w2.close()
 
 
 @pytest.mark.parametrize("method,tol", [("bf16", 1e-2), ("int16", 2e-4), ("int8", 3e-2), ("mxfp4", 0.2)])
@@ -204,31 +246,87 @@ def test_ranks_come_from_torchrun_then_slurm(wire, monkeypatch):
     assert wire.env_rank() == (3, 8, 3)
 
 
-def test_missing_peer_is_reported_not_hung(wire):
-    """Failure detection: rank 1 never sends.  Rank 0's owner kernel polls rank 1's
-    flag a bounded number of times, records a time-out and returns; the host reads
-    the status as an error, and the same handles work again afterwards."""
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("method", ["int16", "int8", "int8ef"])
+def test_integer_wire_golden_several_ranks(wire, golden, method, world):
+    # outputs of the real reference Wire on 2 and 4 gloo ranks, three steps: bit for bit
+    gd = golden(f"wire_{method}_w{world}")
+    grads = gd["grads"]
+    grp = wire.LocalWireGroup(world, grads.shape[-1], ef=method == "int8ef", bits=16 if method == "int16" else 8)
+    for s in range(3):
+        gs = [torch.from_numpy(grads[s, r].copy()).cuda() for r in range(world)]
+        grp.step(gs)
+        for r in range(world):
+            assert np.array_equal(gs[r].cpu().numpy(), gd["outs"][s]), (method, world, s, r)
+    grp.close()
+
+
+def test_missing_peer_fails_the_step_everywhere_and_absorbs_nothing(wire):
+    """Failure detection: rank 1 never sends.  Rank 0's owner kernel waits for rank 1's
+    flag up to the time limit, records the time-out and returns WITHOUT storing: the owner
+    residual and the gather slots keep what they held, no gather flag is raised, so the
+    decode kernels of both ranks run out as well and g is left alone.  The host reads the
+    status as an error (also without synchronising, through the pinned copy); after a
+    reset on every rank the same handles give the oracle's bits again."""
     import ctypes
     from lockstep_b200._lib import check, lib, ptr, stream
     L = lib()
     world, n = 2, 4096
-    grp = wire.LocalWireGroup(world, n)
+    grp = wire.LocalWireGroup(world, n, ef=True)
     for h in grp.handles:
-        check(L.ls_wire_set_poll_limit(h, 2000))             # ~ a few ms
+        check(L.ls_wire_set_timeout_us(h, 3000))
     g0 = torch.randn(n, device="cuda")
-    check(L.ls_wire_send(grp.handles[0], ptr(g0), n, None, stream()))   # rank 1's send is "lost"
-    check(L.ls_wire_reduce(grp.handles[0], None, 0, stream()))
+    g1 = torch.randn(n, device="cuda")
+    keep0, keep1 = g0.clone(), g1.clone()
+    ag_before = grp.slots(0, 1).clone()
+    check(L.ls_wire_send(grp.handles[0], ptr(g0), n, ptr(grp.res[0]), stream()))   # rank 1's send is "lost"
+    check(L.ls_wire_reduce(grp.handles[0], ptr(grp.ores[0]), 0, stream()))
+    check(L.ls_wire_reduce(grp.handles[1], ptr(grp.ores[1]), 0, stream()))
+    check(L.ls_wire_finish(grp.handles[0], ptr(g0), n, stream()))
+    check(L.ls_wire_finish(grp.handles[1], ptr(g1), n, stream()))
+    torch.cuda.synchronize()
+    for r in range(world):                                   # the pinned copy shows it without a synchronising call
+        assert L.ls_wire_poll_status(grp.handles[r], None) == -4
     status = ctypes.c_int(0)
     rc = L.ls_wire_status(grp.handles[0], ctypes.byref(status))
     assert rc == -4 and status.value != 0                    # LS_ETIMEOUT
     assert b"gave up" in L.ls_last_error()
     assert L.ls_wire_status(grp.handles[0], None) == 0       # cleared; context still usable
-    # bring rank 1 level with rank 0's epoch, then a complete step works
-    g1 = torch.randn(n, device="cuda")
-    check(L.ls_wire_send(grp.handles[1], ptr(g1), n, None, stream()))
-    check(L.ls_wire_reduce(grp.handles[1], None, 0, stream()))
+    assert torch.equal(g0, keep0) and torch.equal(g1, keep1)                      # nothing decoded
+    assert not grp.ores[0].any() and not grp.ores[1].any()                        # owner residuals untouched
+    assert torch.equal(grp.slots(0, 1), ag_before)                                # nothing gathered
+    for r in range(world):
+        check(L.ls_wire_reset(grp.handles[r]))
+        grp.res[r].zero_(), grp.ores[r].zero_()
+        assert L.ls_wire_poll_status(grp.handles[r], None) == 0
     gs = [torch.randn(n, device="cuda") for _ in range(world)]
-    want, _, _ = cref.wire_step([g.cpu().numpy() for g in gs], unit=256)
+    res_c = [np.zeros(grp.kpadded, np.float32) for _ in range(world)]
+    ores_c = [np.zeros(grp.kpadded // world, np.float32) for _ in range(world)]
+    want, _, _ = cref.wire_step([g.cpu().numpy() for g in gs], res_c, ores_c, unit=256)
     grp.step(gs)
     assert np.array_equal(gs[0].cpu().numpy(), want) and np.array_equal(gs[1].cpu().numpy(), want)
+    assert np.array_equal(grp.res[0].cpu().numpy(), res_c[0]) and np.array_equal(grp.ores[1].cpu().numpy(), ores_c[1])
+    assert L.ls_wire_set_timeout_us(grp.handles[0], 0) < 0
+    grp.close()
+
+
+def test_wire_object_raises_on_the_call_after_a_time_out(wire):
+    # Wire.__call__ reads the pinned status copy before it queues more work: a step that
+    # timed out turns into an exception on the next call, without an extra synchronisation
+    import ctypes
+    from lockstep_b200._lib import check, lib
+    L = lib()
+    n = 4096
+    grp = wire.LocalWireGroup(2, n)
+    x = torch.randn(n, device="cuda")
+    w = wire.Wire("mxfp4", n, world=2, rank=0, timeout=0.002)
+    w._h = grp.handles[0]                                     # rank 0 of a two-rank wire whose peer never shows up
+    check(L.ls_wire_set_timeout_us(w._h, 2000))
+    w.send(x)
+    w.reduce()
+    w.finish(x)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="LS_ETIMEOUT"):
+        w(x)
+    w._h = None
     grp.close()

@@ -1,0 +1,174 @@
+"""Training-step harness for the FP4 linear layer (benchmark code, not part of the package).
+
+A small decoder-only language model with the layer plan lockstep's train.py uses for
+its own measurements (pre-norm residual blocks, one fused query/key/value projection,
+a GELU feed-forward of width 4 x d, learned position embeddings, an output head tied
+to the token embedding, cross-entropy on the next token), so that tokens/s is measured
+where the reference measures it.  Everything that is not one of the four block
+projections is torch's: attention, layer norm, softmax, the optimizer.
+
+The four projections of every block come from `make_linear`:
+  "dense"   nn.Linear (cuBLAS bf16 under autocast)             -- the comparison point
+  "ste"     MXFP4Linear, straight-through bf16 backward        -- lockstep's fp4_linear.py
+  "mxfp4"   MXFP4Linear with MXFP4 dgrad / wgrad as well
+
+Gradient sync follows train.py:100-105,124-138: all gradients live in one flat fp32
+buffer that a `wire.Wire` averages in place after the backward pass.
+"""
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+def make_linear(kind):
+    from lockstep_b200 import fp4_linear
+    if kind == "dense":
+        return lambda fan_in, fan_out: nn.Linear(fan_in, fan_out, bias=False)
+    return lambda fan_in, fan_out: fp4_linear.MXFP4Linear(fan_in, fan_out, bias=False, backward=kind)
+
+
+class CausalSelfAttention(nn.Module):
+    def __init__(self, width, heads, linear):
+        super().__init__()
+        self.heads = heads
+        self.qkv = linear(width, 3 * width)
+        self.proj = linear(width, width)
+
+    def forward(self, x):
+        batch, steps, width = x.shape
+        qkv = self.qkv(x).view(batch, steps, 3, self.heads, width // self.heads)
+        q, k, v = qkv.permute(2, 0, 3, 1, 4)                      # each [batch, heads, steps, head_dim]
+        mixed = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return self.proj(mixed.transpose(1, 2).reshape(batch, steps, width))
+
+
+class FeedForward(nn.Module):
+    def __init__(self, width, linear):
+        super().__init__()
+        self.fc = linear(width, 4 * width)
+        self.out = linear(4 * width, width)
+
+    def forward(self, x):
+        return self.out(F.gelu(self.fc(x)))
+
+
+class Block(nn.Module):
+    def __init__(self, width, heads, linear):
+        super().__init__()
+        self.ln1 = nn.LayerNorm(width)
+        self.attn = CausalSelfAttention(width, heads, linear)
+        self.ln2 = nn.LayerNorm(width)
+        self.mlp = FeedForward(width, linear)
+
+    def forward(self, x):
+        x = x + self.attn(self.ln1(x))
+        return x + self.mlp(self.ln2(x))
+
+
+class Decoder(nn.Module):
+    def __init__(self, layers, width, heads, context, vocab, linear):
+        super().__init__()
+        self.vocab = vocab
+        self.tokens = nn.Embedding(vocab, width)
+        self.positions = nn.Embedding(context, width)
+        self.blocks = nn.ModuleList([Block(width, heads, linear) for _ in range(layers)])
+        self.norm = nn.LayerNorm(width)
+        # N(0, 0.02) for every matrix; the two projections that write into the residual
+        # stream are scaled down by sqrt(2 * layers), as train.py:66-69 does
+        shrink = 1.0 / math.sqrt(2 * layers)
+        for name, p in self.named_parameters():
+            if p.dim() < 2:
+                continue
+            residual_writer = name.endswith("attn.proj.weight") or name.endswith("mlp.out.weight")
+            nn.init.normal_(p, std=0.02 * (shrink if residual_writer else 1.0))
+
+    def forward(self, ids, targets):
+        where = torch.arange(ids.shape[1], device=ids.device)
+        h = self.tokens(ids) + self.positions(where)
+        for block in self.blocks:
+            h = block(h)
+        logits = F.linear(self.norm(h), self.tokens.weight)          # tied head, dense
+        return F.cross_entropy(logits.float().view(-1, self.vocab), targets.reshape(-1))
+
+
+class Trainer:
+    """Model + fused AdamW + a flat fp32 gradient buffer averaged by a Wire after backward."""
+
+    def __init__(self, kind="mxfp4", layers=12, width=1024, heads=16, context=1024, batch=16, vocab=32000,
+                 device="cuda", wire_method="mxfp4ef", world=1, rank=0):
+        from lockstep_b200 import wire
+        torch.manual_seed(0)
+        self.model = Decoder(layers, width, heads, context, vocab, make_linear(kind)).to(device)
+        self.params = list(self.model.parameters())
+        self.flat = torch.zeros(sum(p.numel() for p in self.params), device=device)
+        at = 0
+        for p in self.params:                                  # every gradient is a view of the flat buffer
+            p.grad = self.flat[at:at + p.numel()].view_as(p)
+            at += p.numel()
+        self.sync = wire.Wire(wire_method, self.flat.numel(), world, rank) if wire_method else None
+        decay = [p for p in self.params if p.dim() >= 2]
+        rest = [p for p in self.params if p.dim() < 2]
+        self.opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}],
+                                     lr=6e-4, betas=(0.9, 0.95), fused=True)
+        gen = torch.Generator(device=device).manual_seed(0)
+        ids = torch.randint(0, vocab, (batch, context + 1), device=device, generator=gen)
+        self.x, self.y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+        self.tokens_per_step = batch * context
+
+    def step(self):
+        self.flat.zero_()
+        with torch.autocast("cuda", torch.bfloat16):
+            loss = self.model(self.x, self.y)
+        loss.backward()
+        if self.sync is not None:
+            self.sync(self.flat)
+        torch.nn.utils.clip_grad_norm_(self.params, 1.0)
+        self.opt.step()
+        return loss
+
+    def time(self, steps=5, warmup=2):
+        """(seconds per step by CUDA events, last loss)."""
+        for _ in range(warmup):
+            loss = self.step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            loss = self.step()
+        b.record()
+        torch.cuda.synchronize()
+        if self.sync is not None:
+            self.sync.status()
+        return a.elapsed_time(b) / steps / 1e3, float(loss.detach())
+
+    def close(self):
+        if self.sync is not None:
+            self.sync.close()
+
+
+def training_step_time(kind="mxfp4", steps=5, warmup=2, **kw):
+    t = Trainer(kind, **kw)
+    out = t.time(steps, warmup)
+    t.close()
+    return out
+
+
+def report(device, steps=5, warmup=2):
+    """The `train_step` object of the benchmark line: tokens/s of the 12-layer configuration
+    with each kind of block projection, gradient sync through the FP4 wire included."""
+    out = {}
+    for kind in ("dense", "ste", "mxfp4"):
+        torch.cuda.empty_cache()
+        t = Trainer(kind, device=device)
+        sec, loss = t.time(steps, warmup)
+        out[kind] = {"tokens_per_s": t.tokens_per_step / sec, "ms_per_step": sec * 1e3, "loss": loss}
+        t.close()
+        del t
+    return {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 vocab32000, bf16 autocast, fused AdamW, "
+                     "synthetic ids seed 0; gradients in one flat fp32 buffer averaged by Wire('mxfp4ef') every step",
+            "block_linears": out,
+            "mxfp4_vs_dense": out["mxfp4"]["tokens_per_s"] / out["dense"]["tokens_per_s"],
+            "ste_vs_dense": out["ste"]["tokens_per_s"] / out["dense"]["tokens_per_s"]}
