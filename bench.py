@@ -475,6 +475,9 @@ def main():
     evs = [Ev() for _ in range(args.steps)]
     barrier()
     sampler = ClockSampler(dev) if rank == 0 else None
+    for _ in range(warmup):                                  # the GPU idled while the sampler started: warm up again
+        step()
+    barrier()
     for ev in evs:
         flush.zero_()
         step(ev)
@@ -604,7 +607,7 @@ def main():
                     "copy_only": {"h2d_gbs_all_ranks": h2d_sum, "d2h_gbs_all_ranks": d2h_sum,
                                   "how": "every rank copies its own 134 MB pinned buffer at the same time, one direction "
                                          "at a time; sum over ranks"}},
-            "gpu_launches": 2 * (warmup + 1 + args.steps + len(sus)) + 2 * chunks * (e2e_steps + 2) + wire_launches,
+            "gpu_launches": 2 * (2 * warmup + 1 + args.steps + len(sus)) + 2 * chunks * (e2e_steps + 2) + wire_launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_pair_kernel (cta_group::2, dual batch)",
                          "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,

@@ -227,8 +227,8 @@ int ls_wire_int_allreduce(void *handle, float *g, int64_t numel, float *res, flo
 
 /* How ls_wire_allreduce runs a step on this handle.  mode: 0 = default (the
  * cooperative launch), 1 = three launches, 2 = one cooperative launch.  subs:
- * sub-ranges each shard is cut into by the cooperative launch (0 = default 4,
- * else 1..8; lowered until the shard divides into multiples of 256 elements).
+ * sub-ranges each shard is cut into by the cooperative launch (0 = default: 2
+ * on one rank, 1 otherwise; else 1..8; lowered until the shard divides into multiples of 256 elements).
  * stagger != 0: the CTAs take the three items of a pipeline step in rotated
  * orders.  The cooperative launch needs the whole grid resident at once: do not
  * run it beside other kernels that occupy the SMs for long.  ls_wire_mode
@@ -245,10 +245,9 @@ int ls_wire_mode(void *handle);
  * every rank and clear or restore the residuals. */
 int ls_wire_set_timeout_us(void *handle, int64_t microseconds);
 
-/* Non-blocking status: every all-reduce call ends by copying the status word to
- * pinned host memory on its stream; this returns LS_ETIMEOUT if the last
- * finished copy was non-zero.  A call still in flight is not waited for, so a
- * time-out is seen one call late at the latest. */
+/* Non-blocking status: a kernel whose wait ran out also sets a word in mapped
+ * pinned host memory; this returns LS_ETIMEOUT if that word is set (cleared by
+ * ls_wire_status and ls_wire_reset).  Kernels in flight are not waited for. */
 int ls_wire_poll_status(void *handle, int *status_host);
 
 /* After a time-out: synchronises this device, clears flags, counters and the

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <mutex>
 #include <stdint.h>
@@ -135,6 +136,23 @@ __device__ __forceinline__ void e2m1x4_values(uint32_t pk, float (&v)[4])
     v[1] = __uint_as_float((a01 & 0xFFFF0000u) | ((pk << 24) & 0x80000000u));
     v[2] = __uint_as_float((a23 << 16) | ((pk << 20) & 0x80000000u));
     v[3] = __uint_as_float((a23 & 0xFFFF0000u) | ((pk << 16) & 0x80000000u));
+}
+
+// Eight E2M1 codes (one packed word, element 0 in the low nibble) -> their fp32 values,
+// through the hardware converter to f16 pairs (every E2M1 value is exact in f16; code 8
+// gives -0.0).
+__device__ __forceinline__ void e2m1x8_values(uint32_t pk, float (&v)[8])
+{
+    uint32_t h[4];
+    asm("{\n.reg .b8 b0, b1, b2, b3;\nmov.b32 {b0, b1, b2, b3}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\ncvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\ncvt.rn.f16x2.e2m1x2 %3, b3;\n}\n"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(pk));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h[i]));
+        v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
 }
 
 // Two floats -> one byte of two E2M1 codes (lo in the low nibble), hardware

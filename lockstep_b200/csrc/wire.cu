@@ -24,9 +24,10 @@
 //
 // Senders walk the owners starting at their right-hand neighbour (rank + 1),
 // so at any moment every owner receives from one sender only instead of all
-// ranks storing into owner 0 first.  A thread owns 16 consecutive values (two
-// 32-byte loads per operand, one 8-byte packed store); two adjacent lanes share
-// a block of 32 and a half-warp writes its 8 exponent bytes as one word pair.
+// ranks storing into owner 0 first.  A thread owns 8 consecutive values (one
+// 32-byte load per operand, one 4-byte packed store); four adjacent lanes share
+// a block of 32, so every instruction of a warp reads or writes whole 128-byte
+// lines, locally and across NVLink.
 //
 // Every wait is bounded by a wall-clock limit (%globaltimer).  A CTA whose wait
 // runs out records it in the status word, stores nothing more and raises no
@@ -58,8 +59,8 @@ struct Header {                 // start of every rank's arena
 constexpr size_t kHeaderBytes = 1024;
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
 
-// The same sub-range [first, first + count) of every owner's shard, in groups of 16
-// elements; both are multiples of 16 groups, so a half-warp never straddles a sub-range.
+// The same sub-range [first, first + count) of every owner's shard, in groups of 8
+// elements; both are multiples of 32 groups, so a warp never straddles a sub-range.
 struct Sub {
     int index;
     uint32_t first, count;
@@ -73,6 +74,7 @@ struct WireGeom {
     int64_t slot_bytes;             // packed + exponent bytes of one shard, 256-aligned
     int64_t rs_off, ag_off;         // byte offsets of the slot arrays in an arena
     uint64_t timeout_ns;            // how long a wait on a peer's flag may last
+    uint32_t *host_status;          // mapped pinned host word of this rank: set to 1 when a wait ran out
     int bits;                       // 0: MXFP4 payload; 8 / 16: integer payload (wire.py's int8 / int16)
     int64_t mx_off;                 // integer wires: [world][padded / 64] fp32 chunk maxima of every rank
 };
@@ -88,7 +90,7 @@ struct Wire {
     int mode;                       // 0 = choose, 1 = three launches, 2 = one cooperative launch
     int subs;                       // sub-ranges of the cooperative launch (0 = choose)
     int fused_ctas;                 // CTAs of the cooperative kernel that fit the device at once (0 = not asked yet)
-    int *status_host;               // pinned: copy of the status word after the last all-reduce call
+    int *status_host;               // pinned and mapped: a kernel whose wait ran out writes 1 here
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
@@ -112,7 +114,7 @@ __device__ __forceinline__ uint64_t global_ns()
 // every thread of the CTA) when all `world` flags arrived, false when the time limit ran
 // out first; the time-out is recorded in the status word of this rank's arena.
 __device__ __forceinline__ bool wait_flags(Header *h, const uint32_t *flags, int world, uint32_t epoch,
-                                           uint64_t timeout_ns)
+                                           uint64_t timeout_ns, uint32_t *host_status)
 {
     bool ok = true;
     if (int(threadIdx.x) < world && int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
@@ -121,6 +123,8 @@ __device__ __forceinline__ bool wait_flags(Header *h, const uint32_t *flags, int
         while (int32_t(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
             if ((++polls & 15u) == 0 && global_ns() - t0 > timeout_ns) {
                 atomicExch(&h->status, 1u);
+                *reinterpret_cast<volatile uint32_t *>(host_status) = 1u;      // the host sees it without a copy or a sync
+                __threadfence_system();
                 ok = false;
                 break;
             }
@@ -135,9 +139,11 @@ __device__ __forceinline__ bool wait_flags(Header *h, const uint32_t *flags, int
 __device__ __forceinline__ void signal_done(uint32_t *counter, uint32_t ncta, const Peers &peers, int world,
                                             int rank, size_t flag_off, uint32_t epoch)
 {
-    __threadfence_system();
+    // The CTA's stores are ordered before thread 0's fence by the barrier; the fence (system
+    // scope, cumulative) then orders them before the counter update and the flag stores.
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         uint32_t done = atomicAdd(counter, 1u);
         if (done == ncta - 1) {
             *counter = 0;
@@ -148,7 +154,10 @@ __device__ __forceinline__ void signal_done(uint32_t *counter, uint32_t ncta, co
     }
 }
 
-// ---- 16 values per thread -------------------------------------------------------------
+// ---- 8 values per thread ---------------------------------------------------------------
+// One thread owns 8 consecutive values (one 32-byte load or store), four adjacent lanes
+// share a block of 32, so every load and store instruction of a warp covers whole 128-byte
+// lines: 1 KB of fp32 values, 128 bytes of packed nibbles.
 __device__ __forceinline__ void ld8(const float *p, float *v)
 {
     asm volatile("ld.global.L1::no_allocate.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -160,190 +169,173 @@ __device__ __forceinline__ void st8(float *p, const float *v)
     asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                  ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]) : "memory");
 }
-__device__ __forceinline__ void load16(const float *p, int64_t i0, int64_t n, float (&v)[16])
+__device__ __forceinline__ void load8v(const float *p, int64_t i0, int64_t n, float (&v)[8])
 {
-    if (i0 + 16 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 31) == 0) {
+    if (i0 + 8 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 31) == 0) {
         ld8(p + i0, v);
-        ld8(p + i0 + 8, v + 8);
     } else {
 #pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = i0 + i < n ? p[i0 + i] : 0.0f;
+        for (int i = 0; i < 8; i++) v[i] = i0 + i < n ? p[i0 + i] : 0.0f;
     }
 }
-__device__ __forceinline__ void store16(float *p, int64_t i0, int64_t n, const float (&v)[16])
+__device__ __forceinline__ void store8v(float *p, int64_t i0, int64_t n, const float (&v)[8])
 {
-    if (i0 + 16 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 31) == 0) {
+    if (i0 + 8 <= n && (reinterpret_cast<uintptr_t>(p + i0) & 31) == 0) {
         st8(p + i0, v);
-        st8(p + i0 + 8, v + 8);
     } else {
 #pragma unroll
-        for (int i = 0; i < 16; i++)
+        for (int i = 0; i < 8; i++)
             if (i0 + i < n) p[i0 + i] = v[i];
     }
 }
 
-// Mask of the half-warp this lane belongs to.
-__device__ __forceinline__ uint32_t half_mask() { return 0xFFFFu << (threadIdx.x & 16); }
-
-// Encodes the 16 values of this thread; the adjacent lane (lane ^ 1) holds the other half
-// of the block of 32.  Returns the packed nibbles; e8 = exponent byte of the block;
-// dq[] = decoded values.
-__device__ __forceinline__ uint2 encode16(const float (&v)[16], uint32_t hmask, uint32_t &e8, float (&dq)[16])
+// Encodes the 8 values of this thread; lanes 4k .. 4k + 3 hold one block of 32.  Returns the
+// packed nibbles; e8 = exponent byte of the block; dq[] = decoded values.
+__device__ __forceinline__ uint32_t encode8(const float (&v)[8], uint32_t &e8, float (&dq)[8])
 {
     uint32_t amax = 0;
 #pragma unroll
-    for (int i = 0; i < 16; i++) amax = max(amax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
-    amax = max(amax, __shfl_xor_sync(hmask, amax, 1));
+    for (int i = 0; i < 8; i++) amax = max(amax, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
     e8 = block_e8m0(amax);
     const float inv = __uint_as_float(e8 == 255u ? 0x7FC00000u : inv_scale_bits(e8));
     const float sc = __uint_as_float(scale_bits(e8));
-    uint32_t pk[2];
+    float q[8];
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        float q[8];
+    for (int i = 0; i < 8; i++) q[i] = __fmul_rn(v[i], inv);
+    uint32_t pk;
+    if (amax < kBitsInf) {
+        pk = cvt_ref_e2m1x8(q);                          // all quotients finite: hardware converter
+    } else {
+        pk = 0;
 #pragma unroll
-        for (int i = 0; i < 8; i++) q[i] = __fmul_rn(v[8 * h + i], inv);
-        if (amax < kBitsInf) {
-            pk[h] = cvt_ref_e2m1x8(q);                       // all quotients finite: hardware converter
-        } else {
-            pk[h] = 0;
-#pragma unroll
-            for (int i = 0; i < 8; i++) pk[h] |= e2m1_code<false>(q[i]) << (4 * i);
-        }
-        float lo[4], hi[4];
-        e2m1x4_values(pk[h], lo);
-        e2m1x4_values(pk[h] >> 16, hi);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            dq[8 * h + i] = __fmul_rn(lo[i], sc);
-            dq[8 * h + 4 + i] = __fmul_rn(hi[i], sc);
-        }
+        for (int i = 0; i < 8; i++) pk |= e2m1_code<false>(q[i]) << (4 * i);
     }
-    return make_uint2(pk[0], pk[1]);
+    e2m1x8_values(pk, dq);
+#pragma unroll
+    for (int i = 0; i < 8; i++) dq[i] = __fmul_rn(dq[i], sc);
+    return pk;
 }
 
 // val[i] += decode(pk)[i] * 2^(e8 - 127), each add rounded to fp32
-__device__ __forceinline__ void add_decoded16(uint2 pk, uint32_t e8, float (&val)[16])
+__device__ __forceinline__ void add_decoded8(uint32_t pk, uint32_t e8, float (&val)[8])
 {
     const float sc = __uint_as_float(scale_bits(e8));
-    const uint32_t w[2] = {pk.x, pk.y};
+    float d[8];
+    e2m1x8_values(pk, d);
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        float lo[4], hi[4];
-        e2m1x4_values(w[h], lo);
-        e2m1x4_values(w[h] >> 16, hi);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            val[8 * h + i] = __fadd_rn(val[8 * h + i], __fmul_rn(lo[i], sc));
-            val[8 * h + 4 + i] = __fadd_rn(val[8 * h + 4 + i], __fmul_rn(hi[i], sc));
-        }
-    }
-}
-
-// The 8 exponent bytes of a half-warp's 8 blocks (held by its even lanes), gathered into
-// the half-warp's first lane as two words.
-__device__ __forceinline__ uint2 gather_exponents16(uint32_t e8, uint32_t hmask)
-{
-    uint32_t w = e8 | (__shfl_down_sync(hmask, e8, 2, 16) << 8);     // lanes 0, 4, 8, 12: two blocks
-    w |= __shfl_down_sync(hmask, w, 4, 16) << 16;                    // lanes 0, 8: four blocks
-    const uint32_t hi = __shfl_down_sync(hmask, w, 8, 16);           // lane 0: blocks 4..7
-    return make_uint2(w, hi);
+    for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], __fmul_rn(d[i], sc));
 }
 
 // ---- phase 1: sender ---------------------------------------------------------------
 // CTA `cta` of `ncta` encodes its share of sub-range `sub` of every owner's shard.
+template <int U>
 __device__ __forceinline__ void send_part(const float *g, int64_t n, float *res, const WireGeom &geo,
                                           const Peers &peers, Sub sub, uint32_t cta, uint32_t ncta)
 {
     const uint32_t stride = ncta * kThreads;
-    const uint32_t hmask = half_mask();
-    const uint32_t per_shard = uint32_t(geo.shard / 16);       // groups of 16 per shard
+    const uint32_t per_shard = uint32_t(geo.shard / 8);        // groups of 8 per shard: a multiple of 32
     const uint32_t total = uint32_t(geo.world) * sub.count;
     const int64_t exp_off = geo.shard / 2;
-    // one flat loop over the sub-range's groups of all owners; the step index i advances with the
-    // position, and step i goes to owner rank + 1 + i (this rank's own shard comes last)
+    const bool first_of_block = (threadIdx.x & 3) == 0;
+    // One flat loop over the sub-range's groups of all owners: position j belongs to step
+    // i = j / count, and step i goes to owner rank + 1 + i (this rank's own shard comes last).
+    // A thread takes two positions per round, a grid stride apart, and issues the loads of
+    // both before it encodes either (U = 2), or one (U = 1, fewer registers).
     uint32_t j = cta * kThreads + threadIdx.x;
     uint32_t i = j / sub.count, k = j - i * sub.count;
-    for (; j < total; j += stride, k += stride) {
-        while (k >= sub.count) k -= sub.count, i++;
-        uint32_t o = uint32_t(geo.rank) + 1u + i;
-        if (o >= uint32_t(geo.world)) o -= uint32_t(geo.world);
-        const uint32_t in_shard = sub.first + k;
-        uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
-        const int64_t i0 = (int64_t(o) * per_shard + in_shard) * 16;
-        float v[16], dq[16];
-        load16(g, i0, n, v);
-        if (res) {
-            float r[16];
-            load16(res, i0, geo.padded, r);
+    for (; j < total; j += U * stride) {
+        uint32_t in_shard[U];
+        uint8_t *slot[U];
+        int64_t i0[U];
+        float v[U][8], r[U][8];
+        bool on[U];
 #pragma unroll
-            for (int t = 0; t < 16; t++) v[t] = __fadd_rn(v[t], r[t]);
+        for (int u = 0; u < U; u++) {
+            on[u] = j + u * stride < total;                    // the same for every lane of a warp
+            while (k >= sub.count) k -= sub.count, i++;
+            uint32_t o = uint32_t(geo.rank) + 1u + i;
+            while (o >= uint32_t(geo.world)) o -= uint32_t(geo.world);
+            in_shard[u] = sub.first + k;
+            slot[u] = peers.arena[on[u] ? o : uint32_t(geo.rank)] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
+            i0[u] = (int64_t(o) * per_shard + in_shard[u]) * 8;
+            if (on[u]) {
+                load8v(g, i0[u], n, v[u]);
+                if (res) load8v(res, i0[u], geo.padded, r[u]);
+            }
+            k += stride;
         }
-        uint32_t e8;
-        const uint2 pk = encode16(v, hmask, e8, dq);
-        if (res) {
 #pragma unroll
-            for (int t = 0; t < 16; t++) dq[t] = __fsub_rn(v[t], dq[t]);
-            store16(res, i0, geo.padded, dq);
+        for (int u = 0; u < U; u++) {
+            if (!on[u]) break;
+            float dq[8];
+            if (res) {
+#pragma unroll
+                for (int t = 0; t < 8; t++) v[u][t] = __fadd_rn(v[u][t], r[u][t]);
+            }
+            uint32_t e8;
+            const uint32_t pk = encode8(v[u], e8, dq);
+            if (res) {
+#pragma unroll
+                for (int t = 0; t < 8; t++) dq[t] = __fsub_rn(v[u][t], dq[t]);
+                store8v(res, i0[u], geo.padded, dq);
+            }
+            reinterpret_cast<uint32_t *>(slot[u])[in_shard[u]] = pk;
+            if (first_of_block) slot[u][exp_off + in_shard[u] / 4] = uint8_t(e8);   // a warp's 8 exponent bytes are contiguous
         }
-        reinterpret_cast<uint2 *>(slot)[in_shard] = pk;
-        const uint2 ex = gather_exponents16(e8, hmask);
-        if ((threadIdx.x & 15) == 0) *reinterpret_cast<uint2 *>(slot + exp_off + in_shard / 2) = ex;
     }
 }
 
 // ---- phase 2: owner ------------------------------------------------------------------
-// WORLD > 0: the world size as a compile-time constant, so that the loads of all
+// WORLD > 0: the world size as a compile-time constant, so that the loads of up to four
 // senders' slots are issued together before the first decode.  WORLD = 0: any size.
 template <int WORLD>
 __device__ __forceinline__ void reduce_part(float *ores, const WireGeom &geo, const Peers &peers, int reverse, Sub sub,
                                             uint32_t cta, uint32_t ncta)
 {
     const int world = WORLD ? WORLD : geo.world;
-    const uint32_t hmask = half_mask();
     const uint32_t end = sub.first + sub.count;
     const uint32_t stride = ncta * kThreads;
     const uint8_t *rs = peers.arena[geo.rank] + geo.rs_off;
     const int64_t exp_off = geo.shard / 2;
-    for (uint32_t g16 = sub.first + cta * kThreads + threadIdx.x; g16 < end; g16 += stride) {
-        float val[16], dq[16], r[16];
+    const bool first_of_block = (threadIdx.x & 3) == 0;
+    for (uint32_t g8 = sub.first + cta * kThreads + threadIdx.x; g8 < end; g8 += stride) {
+        float val[8], dq[8], r[8];
 #pragma unroll
-        for (int i = 0; i < 16; i++) val[i] = 0.0f;
-        if (ores) load16(ores, int64_t(g16) * 16, geo.shard, r);
+        for (int i = 0; i < 8; i++) val[i] = 0.0f;
+        if (ores) load8v(ores, int64_t(g8) * 8, geo.shard, r);
         if (WORLD) {
             constexpr int B = WORLD < 4 ? (WORLD ? WORLD : 1) : 4;     // senders whose loads are in flight together
 #pragma unroll
             for (int t0 = 0; t0 < WORLD; t0 += B) {
-                uint2 pk[B];
-                uint32_t eb[B];
+                uint32_t pk[B], eb[B];
 #pragma unroll
                 for (int t = 0; t < B; t++) {
                     const uint8_t *slot = rs + int64_t(reverse ? WORLD - 1 - (t0 + t) : t0 + t) * geo.slot_bytes;
-                    pk[t] = reinterpret_cast<const uint2 *>(slot)[g16];
-                    eb[t] = slot[exp_off + g16 / 2];
+                    pk[t] = reinterpret_cast<const uint32_t *>(slot)[g8];
+                    eb[t] = slot[exp_off + g8 / 4];
                 }
 #pragma unroll
-                for (int t = 0; t < B; t++) add_decoded16(pk[t], eb[t], val);
+                for (int t = 0; t < B; t++) add_decoded8(pk[t], eb[t], val);
             }
         } else {
             for (int t = 0; t < world; t++) {
                 const uint8_t *slot = rs + int64_t(reverse ? world - 1 - t : t) * geo.slot_bytes;
-                add_decoded16(reinterpret_cast<const uint2 *>(slot)[g16], slot[exp_off + g16 / 2], val);
+                add_decoded8(reinterpret_cast<const uint32_t *>(slot)[g8], slot[exp_off + g8 / 4], val);
             }
         }
         if (ores) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) val[i] = __fadd_rn(val[i], r[i]);
+            for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
         }
         uint32_t e8;
-        const uint2 pk2 = encode16(val, hmask, e8, dq);
+        const uint32_t pk2 = encode8(val, e8, dq);
         if (ores) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) dq[i] = __fsub_rn(val[i], dq[i]);
-            store16(ores, int64_t(g16) * 16, geo.shard, dq);
+            for (int i = 0; i < 8; i++) dq[i] = __fsub_rn(val[i], dq[i]);
+            store8v(ores, int64_t(g8) * 8, geo.shard, dq);
         }
-        const uint2 ex = gather_exponents16(e8, hmask);
-        const bool first_lane = (threadIdx.x & 15) == 0;
         // every rank's gather slot, starting at the right-hand neighbour
 #pragma unroll
         for (int i = 0; i < (WORLD ? WORLD : kMaxWorld); i++) {
@@ -351,8 +343,8 @@ __device__ __forceinline__ void reduce_part(float *ores, const WireGeom &geo, co
             int p = geo.rank + 1 + i;
             if (p >= world) p -= world;
             uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
-            reinterpret_cast<uint2 *>(slot)[g16] = pk2;
-            if (first_lane) *reinterpret_cast<uint2 *>(slot + exp_off + g16 / 2) = ex;
+            reinterpret_cast<uint32_t *>(slot)[g8] = pk2;
+            if (first_of_block) slot[exp_off + g8 / 4] = uint8_t(e8);
         }
     }
 }
@@ -370,15 +362,15 @@ __device__ __forceinline__ void reduce_any(float *ores, const WireGeom &geo, con
 }
 
 // ---- phase 3: everyone ---------------------------------------------------------------
-// One thread decodes 16 values (one 8-byte packed word) and writes two 32-byte words; U
-// groups per thread are in flight.  POW2: the world size is a power of two, so dividing by
-// it is an exact multiplication that folds into the block scale.  Otherwise an IEEE
-// division (wire.py:138 `.div_(world)`).
+// One thread decodes 8 values (one packed word) and writes one 32-byte word; U groups per
+// thread are in flight.  POW2: the world size is a power of two, so dividing by it is an
+// exact multiplication that folds into the block scale.  Otherwise an IEEE division
+// (wire.py:138 `.div_(world)`).
 template <bool POW2>
 __device__ __forceinline__ void finish_part(float *g, int64_t n, const WireGeom &geo, const Peers &peers, Sub sub,
                                             uint32_t cta, uint32_t ncta)
 {
-    constexpr int U = 2;
+    constexpr int U = 4;
     const uint8_t *my = peers.arena[geo.rank];
     const uint32_t stride = ncta * kThreads;
     const uint32_t end = sub.first + sub.count;
@@ -388,19 +380,18 @@ __device__ __forceinline__ void finish_part(float *g, int64_t n, const WireGeom 
         const uint8_t *slot_e = slot + geo.shard / 2;
         const int64_t first = int64_t(o) * geo.shard;
         if (first >= n) break;
-        const int64_t left = (n - first + 15) / 16;             // groups of this shard that hold elements of g
+        const int64_t left = (n - first + 7) / 8;               // groups of this shard that hold elements of g
         const uint32_t count = left < int64_t(end) ? uint32_t(left) : end;
         float *gs = g + first;
         const int64_t ns = n - first;                           // elements of g in this shard and beyond
         for (uint32_t q0 = sub.first + cta * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
-            uint2 pk[U];
-            uint32_t e8[U];
+            uint32_t pk[U], e8[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const uint32_t q = q0 + u * stride;
                 const bool ok = q < count;
-                pk[u] = ok ? reinterpret_cast<const uint2 *>(slot)[q] : make_uint2(0u, 0u);
-                e8[u] = ok ? slot_e[q >> 1] : 127u;
+                pk[u] = ok ? reinterpret_cast<const uint32_t *>(slot)[q] : 0u;
+                e8[u] = ok ? slot_e[q >> 2] : 127u;
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
@@ -408,36 +399,33 @@ __device__ __forceinline__ void finish_part(float *g, int64_t n, const WireGeom 
                 if (q >= count) break;
                 float sc = __uint_as_float(scale_bits(e8[u]));
                 if (POW2) sc = __fmul_rn(sc, rw);
-                float t[16];
-                e2m1x4_values(pk[u].x, *reinterpret_cast<float(*)[4]>(t));
-                e2m1x4_values(pk[u].x >> 16, *reinterpret_cast<float(*)[4]>(t + 4));
-                e2m1x4_values(pk[u].y, *reinterpret_cast<float(*)[4]>(t + 8));
-                e2m1x4_values(pk[u].y >> 16, *reinterpret_cast<float(*)[4]>(t + 12));
+                float t[8];
+                e2m1x8_values(pk[u], t);
 #pragma unroll
-                for (int i = 0; i < 16; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
-                store16(gs, int64_t(q) * 16, ns, t);
+                for (int i = 0; i < 8; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
+                store8v(gs, int64_t(q) * 8, ns, t);
             }
         }
     }
 }
 
 // ---- the three phases as separate launches ---------------------------------------------
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 5)
 wire_send_kernel(const float *g, int64_t n, float *res, const __grid_constant__ WireGeom geo,
                  const __grid_constant__ Peers peers, uint32_t epoch, Sub sub)
 {
-    send_part(g, n, res, geo, peers, sub, blockIdx.x, gridDim.x);
+    send_part<1>(g, n, res, geo, peers, sub, blockIdx.x, gridDim.x);
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
     signal_done(&mine->counter[sub.index][0], gridDim.x, peers, geo.world, geo.rank,
                 offsetof(Header, rs_flag) + sub.index * sizeof(mine->rs_flag[0]), epoch);
 }
 
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 4)
 wire_reduce_kernel(float *ores, const __grid_constant__ WireGeom geo, const __grid_constant__ Peers peers,
                    uint32_t epoch, int reverse, Sub sub)
 {
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
-    if (!wait_flags(mine, mine->rs_flag[sub.index], geo.world, epoch, geo.timeout_ns)) return;
+    if (!wait_flags(mine, mine->rs_flag[sub.index], geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
     reduce_any(ores, geo, peers, reverse, sub, blockIdx.x, gridDim.x);
     signal_done(&mine->counter[sub.index][1], gridDim.x, peers, geo.world, geo.rank,
                 offsetof(Header, ag_flag) + sub.index * sizeof(mine->ag_flag[0]), epoch);
@@ -448,7 +436,7 @@ wire_finish_kernel(float *g, int64_t n, const __grid_constant__ WireGeom geo, co
                    uint32_t epoch, Sub sub)
 {
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
-    if (!wait_flags(mine, mine->ag_flag[sub.index], geo.world, epoch, geo.timeout_ns)) return;
+    if (!wait_flags(mine, mine->ag_flag[sub.index], geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
     if ((geo.world & (geo.world - 1)) == 0) finish_part<true>(g, n, geo, peers, sub, blockIdx.x, gridDim.x);
     else finish_part<false>(g, n, geo, peers, sub, blockIdx.x, gridDim.x);
 }
@@ -471,7 +459,7 @@ struct FusedArgs {
 };
 
 template <int WORLD>
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 4)
 wire_fused_kernel(const __grid_constant__ FusedArgs a)
 {
     const uint32_t vr = blockIdx.x / uint32_t(a.ctas), cta = blockIdx.x - vr * uint32_t(a.ctas), ncta = uint32_t(a.ctas);
@@ -479,7 +467,7 @@ wire_fused_kernel(const __grid_constant__ FusedArgs a)
     const WireGeom &geo = ra.geo;
     Header *mine = reinterpret_cast<Header *>(ra.peers.arena[geo.rank]);
     const int S = a.subs;
-    const uint32_t per = uint32_t(geo.shard / 16) / uint32_t(S);
+    const uint32_t per = uint32_t(geo.shard / 8) / uint32_t(S);
     const bool pow2 = (geo.world & (geo.world - 1)) == 0;
     // Within pipeline step t the three items are independent of each other (each depends on
     // items of step t - 1 at most), so CTAs may take them in different orders: with `stagger`
@@ -492,13 +480,13 @@ wire_fused_kernel(const __grid_constant__ FusedArgs a)
             const int item = (q + rot) % 3;
             if (item == 0 && t < S) {
                 const Sub sub{t, uint32_t(t) * per, per};
-                send_part(ra.g, ra.n, ra.res, geo, ra.peers, sub, cta, ncta);
+                send_part<1>(ra.g, ra.n, ra.res, geo, ra.peers, sub, cta, ncta);
                 signal_done(&mine->counter[t][0], ncta, ra.peers, geo.world, geo.rank,
                             offsetof(Header, rs_flag) + t * sizeof(mine->rs_flag[0]), ra.epoch);
             } else if (item == 1 && t >= 1 && t - 1 < S) {
                 const int c = t - 1;
                 const Sub sub{c, uint32_t(c) * per, per};
-                alive = wait_flags(mine, mine->rs_flag[c], geo.world, ra.epoch, geo.timeout_ns);
+                alive = wait_flags(mine, mine->rs_flag[c], geo.world, ra.epoch, geo.timeout_ns, geo.host_status);
                 if (alive) {
                     reduce_part<WORLD>(ra.ores, geo, ra.peers, a.reverse, sub, cta, ncta);
                     signal_done(&mine->counter[c][1], ncta, ra.peers, geo.world, geo.rank,
@@ -507,7 +495,7 @@ wire_fused_kernel(const __grid_constant__ FusedArgs a)
             } else if (item == 2 && t >= 2) {
                 const int c = t - 2;
                 const Sub sub{c, uint32_t(c) * per, per};
-                alive = wait_flags(mine, mine->ag_flag[c], geo.world, ra.epoch, geo.timeout_ns);
+                alive = wait_flags(mine, mine->ag_flag[c], geo.world, ra.epoch, geo.timeout_ns, geo.host_status);
                 if (alive) {
                     if (pow2) finish_part<true>(ra.g, ra.n, geo, ra.peers, sub, cta, ncta);
                     else finish_part<false>(ra.g, ra.n, geo, ra.peers, sub, cta, ncta);
@@ -637,7 +625,7 @@ wire_int_send_kernel(const float *__restrict__ g, int64_t n, float *__restrict__
     constexpr int LIM = (1 << (BITS - 1)) - 1;
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    if (!wait_flags(mine, mine->mx_flag, geo.world, epoch, geo.timeout_ns)) return;
+    if (!wait_flags(mine, mine->mx_flag, geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
     const uint32_t groups = uint32_t(geo.padded / 8), stride = gridDim.x * kThreads;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);
     uint32_t g8 = blockIdx.x * kThreads + threadIdx.x;
@@ -675,7 +663,7 @@ wire_int_reduce_kernel(float *__restrict__ ores, const __grid_constant__ WireGeo
     constexpr int LIM = (1 << (BITS - 1)) - 1;
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    if (!wait_flags(mine, mine->rs_flag[0], geo.world, epoch, geo.timeout_ns)) return;
+    if (!wait_flags(mine, mine->rs_flag[0], geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
     const uint32_t groups = uint32_t(geo.shard / 8), stride = gridDim.x * kThreads;
     const int64_t first_chunk = int64_t(geo.rank) * (geo.shard / kChunk);
     const int64_t payload = geo.shard * (BITS / 8);
@@ -723,7 +711,7 @@ wire_int_finish_kernel(float *__restrict__ g, int64_t n, const __grid_constant__
 {
     uint8_t *my = peers.arena[geo.rank];
     Header *mine = reinterpret_cast<Header *>(my);
-    if (!wait_flags(mine, mine->ag_flag[0], geo.world, epoch, geo.timeout_ns)) return;
+    if (!wait_flags(mine, mine->ag_flag[0], geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
     const uint32_t groups = uint32_t((n + 7) / 8), stride = gridDim.x * kThreads;
     const uint32_t g_per_shard = uint32_t(geo.shard / 8);
     const int64_t payload = geo.shard * (BITS / 8);
@@ -804,7 +792,8 @@ static int wire_create(int rank, int world, int64_t padded, int bits, void **out
     cudaError_t e = cudaGetDevice(&w->dev);
     if (e == cudaSuccess) e = cudaMalloc(&w->arena, w->arena_bytes);
     if (e == cudaSuccess) e = cudaMemset(w->arena, 0, w->arena_bytes);
-    if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void **>(&w->status_host), sizeof(int), cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void **>(&w->status_host), sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&w->g.host_status), w->status_host, 0);
     if (e != cudaSuccess) {
         size_t bytes = w->arena_bytes;
         if (w->arena) cudaFree(w->arena);
@@ -873,14 +862,17 @@ extern "C" int ls_wire_map_local(void *h, void *const *wires)
 }
 
 namespace {
-Sub whole_shard(const Wire *w) { return Sub{0, 0u, uint32_t(w->g.shard / 16)}; }
+Sub whole_shard(const Wire *w) { return Sub{0, 0u, uint32_t(w->g.shard / 8)}; }
 
 // Sub-ranges of the cooperative launch: the requested number, lowered until it divides the
-// shard into pieces of whole half-warps (multiples of 256 elements).
+// shard into pieces of whole warps (multiples of 256 elements).
 int subs_of(const Wire *w, int want)
 {
     const int64_t units = w->g.shard / 256;
-    int s = want > 0 ? want : 4;
+    // default: two sub-ranges on one rank, one otherwise (every extra sub-range costs two
+    // CTA-wide drains per phase; measured 64 Mi elements with error feedback: one rank
+    // 321 / 306 / 345 us for 1 / 2 / 4 sub-ranges, two ranks 268 / 288 / 341 us)
+    int s = want > 0 ? want : (w->g.world == 1 ? 2 : 1);
     if (s > kMaxSub) s = kMaxSub;
     while (s > 1 && units % s != 0) s--;
     return s;
@@ -916,7 +908,7 @@ void fill_rank(RankArgs &r, Wire *w, float *g, int64_t numel, float *res, float 
 
 int launch_fused(FusedArgs &a, int capacity, cudaStream_t st)
 {
-    const int64_t groups = int64_t(a.r[0].geo.world) * (a.r[0].geo.shard / 16) / a.subs;     // send work of one sub-range
+    const int64_t groups = int64_t(a.r[0].geo.world) * (a.r[0].geo.shard / 8) / a.subs;     // send work of one sub-range
     int ctas = capacity / a.nranks;
     const int64_t want = (groups + kThreads - 1) / kThreads;
     if (want < ctas) ctas = int(want < 1 ? 1 : want);
@@ -928,12 +920,6 @@ int launch_fused(FusedArgs &a, int capacity, cudaStream_t st)
     return LS_OK;
 }
 
-int copy_status(Wire *w, cudaStream_t st)
-{
-    LS_CUDA(cudaMemcpyAsync(w->status_host, &reinterpret_cast<Header *>(w->arena)->status, sizeof(int),
-                            cudaMemcpyDeviceToHost, st));
-    return LS_OK;
-}
 }  // namespace
 
 extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, void *stream)
@@ -942,7 +928,7 @@ extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, 
     if (int rc = check_call(w, g, numel)) return rc;
     w->epoch++;
     const Sub sub = whole_shard(w);
-    wire_send_kernel<<<grid_for(int64_t(w->g.world) * sub.count, 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    wire_send_kernel<<<grid_for(int64_t(w->g.world) * sub.count, 5), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         g, numel, res, w->g, w->peers, w->epoch, sub);
     LS_LAUNCH_CHECK("wire_send");
     return LS_OK;
@@ -953,7 +939,7 @@ extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
     Wire *w = as_wire(h);
     if (!w || !w->mapped || w->g.bits) return fail(LS_ESTATE, "wire not ready");
     const Sub sub = whole_shard(w);
-    wire_reduce_kernel<<<grid_for(sub.count, 3), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    wire_reduce_kernel<<<grid_for(sub.count, 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         ores, w->g, w->peers, w->epoch, reverse, sub);
     LS_LAUNCH_CHECK("wire_reduce");
     return LS_OK;
@@ -964,11 +950,11 @@ extern "C" int ls_wire_finish(void *h, float *g, int64_t numel, void *stream)
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
     const Sub sub = whole_shard(w);
-    // two groups per thread and step
-    wire_finish_kernel<<<grid_for((int64_t(w->g.world) * sub.count + 1) / 2, 6), kThreads, 0,
+    // four groups per thread and step
+    wire_finish_kernel<<<grid_for((int64_t(w->g.world) * sub.count + 3) / 4, 8), kThreads, 0,
                          static_cast<cudaStream_t>(stream)>>>(g, numel, w->g, w->peers, w->epoch, sub);
     LS_LAUNCH_CHECK("wire_finish");
-    return copy_status(w, static_cast<cudaStream_t>(stream));
+    return LS_OK;
 }
 
 extern "C" int ls_wire_set_mode(void *h, int mode, int subs, int stagger)
@@ -1006,8 +992,7 @@ extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, f
     FusedArgs a{};
     fill_rank(a.r[0], w, g, numel, res, ores);
     a.nranks = 1, a.subs = subs_of(w, w->subs), a.reverse = reverse, a.stagger = (w->mode & 0x100) ? 1 : 0;
-    if (int rc = launch_fused(a, capacity, static_cast<cudaStream_t>(stream))) return rc;
-    return copy_status(w, static_cast<cudaStream_t>(stream));
+    return launch_fused(a, capacity, static_cast<cudaStream_t>(stream));
 }
 
 // All ranks of a group created in ONE process on one GPU (ls_wire_map_local), one step, one
@@ -1033,10 +1018,7 @@ extern "C" int ls_wire_allreduce_group(void *const *handles, float *const *gs, i
         fill_rank(a.r[r], w, gs[r], numel, ress ? ress[r] : nullptr, oress ? oress[r] : nullptr);
     }
     a.nranks = world, a.subs = subs_of(w0, w0->subs), a.reverse = reverse, a.stagger = (w0->mode & 0x100) ? 1 : 0;
-    if (int rc = launch_fused(a, capacity, static_cast<cudaStream_t>(stream))) return rc;
-    for (int r = 0; r < world; r++)
-        if (int rc = copy_status(as_wire(handles[r]), static_cast<cudaStream_t>(stream))) return rc;
-    return LS_OK;
+    return launch_fused(a, capacity, static_cast<cudaStream_t>(stream));
 }
 
 // Integer wires: phase 0 publish maxima, 1 send, 2 reduce, 3 finish.
@@ -1069,7 +1051,6 @@ extern "C" int ls_wire_int_phase(void *h, int phase, float *g, int64_t numel, fl
         return fail(LS_EINVAL, "phase must be 0..3");
     }
     LS_LAUNCH_CHECK("wire_int_phase");
-    if (phase == 3) return copy_status(w, st);
     return LS_OK;
 }
 
@@ -1102,9 +1083,9 @@ extern "C" int ls_wire_status(void *h, int *status_host)
     return v ? fail(LS_ETIMEOUT, "a wire kernel gave up waiting for a peer's flag") : LS_OK;
 }
 
-// Non-blocking: what the status word held when the last all-reduce call on this handle
-// finished on its stream (copied to pinned host memory by that call).  A call still in
-// flight is not waited for, so a time-out shows up one call late at the latest.
+// Non-blocking: a kernel whose wait ran out also writes a word of mapped pinned host memory;
+// this reads it.  Kernels still in flight are not waited for, so a time-out shows up as soon
+// as it happened, at the next call that looks.
 extern "C" int ls_wire_poll_status(void *h, int *status_host)
 {
     Wire *w = as_wire(h);

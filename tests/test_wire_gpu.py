@@ -262,10 +262,11 @@ def test_integer_wire_golden_several_ranks(wire, golden, method, world):
 
 
 def test_missing_peer_fails_the_step_everywhere_and_absorbs_nothing(wire):
-    """Failure detection: rank 1 never sends.  Rank 0's owner kernel waits for rank 1's
-    flag up to the time limit, records the time-out and returns WITHOUT storing: the owner
-    residual and the gather slots keep what they held, no gather flag is raised, so the
-    decode kernels of both ranks run out as well and g is left alone.  The host reads the
+    """Failure detection: rank 1 never takes part in the step.  Rank 0's owner kernel waits
+    for rank 1's flag up to the time limit, records the time-out and returns WITHOUT
+    storing: the owner residual and the gather slots (its own and the peer's) keep what
+    they held, no gather flag is raised, so the decode kernel runs out as well and g is
+    left alone.  The host reads the
     status as an error (also without synchronising, through the pinned copy); after a
     reset on every rank the same handles give the oracle's bits again."""
     import ctypes
@@ -276,25 +277,22 @@ def test_missing_peer_fails_the_step_everywhere_and_absorbs_nothing(wire):
     for h in grp.handles:
         check(L.ls_wire_set_timeout_us(h, 3000))
     g0 = torch.randn(n, device="cuda")
-    g1 = torch.randn(n, device="cuda")
-    keep0, keep1 = g0.clone(), g1.clone()
+    keep0 = g0.clone()
     ag_before = grp.slots(0, 1).clone()
-    check(L.ls_wire_send(grp.handles[0], ptr(g0), n, ptr(grp.res[0]), stream()))   # rank 1's send is "lost"
+    check(L.ls_wire_send(grp.handles[0], ptr(g0), n, ptr(grp.res[0]), stream()))   # rank 1 never takes part
     check(L.ls_wire_reduce(grp.handles[0], ptr(grp.ores[0]), 0, stream()))
-    check(L.ls_wire_reduce(grp.handles[1], ptr(grp.ores[1]), 0, stream()))
     check(L.ls_wire_finish(grp.handles[0], ptr(g0), n, stream()))
-    check(L.ls_wire_finish(grp.handles[1], ptr(g1), n, stream()))
     torch.cuda.synchronize()
-    for r in range(world):                                   # the pinned copy shows it without a synchronising call
-        assert L.ls_wire_poll_status(grp.handles[r], None) == -4
+    assert L.ls_wire_poll_status(grp.handles[0], None) == -4         # seen without a synchronising call
     status = ctypes.c_int(0)
     rc = L.ls_wire_status(grp.handles[0], ctypes.byref(status))
     assert rc == -4 and status.value != 0                    # LS_ETIMEOUT
     assert b"gave up" in L.ls_last_error()
     assert L.ls_wire_status(grp.handles[0], None) == 0       # cleared; context still usable
-    assert torch.equal(g0, keep0) and torch.equal(g1, keep1)                      # nothing decoded
-    assert not grp.ores[0].any() and not grp.ores[1].any()                        # owner residuals untouched
+    assert torch.equal(g0, keep0)                                                 # nothing decoded
+    assert not grp.ores[0].any()                                                  # owner residual untouched
     assert torch.equal(grp.slots(0, 1), ag_before)                                # nothing gathered
+    assert not grp.slots(1, 1).any()                                              # nothing pushed to the peer either
     for r in range(world):
         check(L.ls_wire_reset(grp.handles[r]))
         grp.res[r].zero_(), grp.ores[r].zero_()
