@@ -151,8 +151,18 @@ int ls_mxfp4_gemm_quant(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t
 
 /* Which GEMM kernel the two entry points above launch: 0 = by shape (default),
  * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles
- * (cta_group::2).  Results are identical; for measurements and tests. */
+ * (cta_group::2), 3 = one CTA per 128 x 128 tile.  Results are identical; for
+ * measurements and tests. */
 int ls_gemm_set_variant(int variant);
+
+/* Measurement aid, no reference counterpart: launches a kernel that issues only
+ * the MMA instruction stream of the CTA-pair GEMM (`rounds` pipeline stages of
+ * four 256 x 256 x 64 block-scaled FP4 MMAs per CTA pair, operands resident in
+ * shared memory, no loads, copies or epilogue) on every CTA pair of the device.
+ * *flop_out (host, may be NULL) receives the FLOPs of the launch; the caller
+ * times it with events on `stream`.  The rate it reaches is the ceiling of the
+ * tensor pipe at the clock the power cap allows. */
+int ls_fp4_mma_peak(int rounds, double *flop_out, void *stream);
 
 /* K-splitting of the two GEMM entry points: 0 = by shape (default: products of
  * more than 128 rows with few output tiles and a long K, i.e. weight gradients
