@@ -616,6 +616,19 @@ def main():
     if not args.no_wire:
         allreduce, wire_launches = wire_leg(args, dev, rank, world, barrier, pk)
 
+    train = None
+    if not args.no_train and not args.small:                 # every rank takes part (the sync is a collective)
+        import train_bench
+        torch.cuda.empty_cache()
+        train = train_bench.report(dev, world=world, rank=rank)
+        tt = torch.tensor([train["sync"]["after_backward_ms"], train["sync"]["sent_under_backward_ms"]], device=dev,
+                          dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            train["sync"]["after_backward_ms"], train["sync"]["sent_under_backward_ms"] = tt.tolist()
+            train["block_linears"]["mxfp4"]["ms_per_step"] = tt[0].item()
+            train["block_linears"]["mxfp4"]["tokens_per_s"] = world * 16 * 1024 / (tt[0].item() * 1e-3)
+
     t = torch.tensor([step_ms, e2e_ms, sus_ms, copies.get("h2d_gbs", 0.0), copies.get("d2h_gbs", 0.0)],
                      device=dev, dtype=torch.float64)
     tmin = t.clone()
@@ -678,10 +691,8 @@ def main():
         }
         if allreduce:
             line["allreduce"] = allreduce
-        if world == 1 and not args.no_train and not args.small:
-            import train_bench
-            torch.cuda.empty_cache()
-            line["train_step"] = train_bench.report(dev)
+        if train is not None:
+            line["train_step"] = train
         if world == 1 and not args.no_sweep and not args.small:
             torch.cuda.empty_cache()
             line["sweep_skinny"] = {"lines": run_sweep(m_list=(1, 16)),

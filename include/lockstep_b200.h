@@ -151,8 +151,8 @@ int ls_mxfp4_gemm_quant(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t
 
 /* Which GEMM kernel the two entry points above launch: 0 = by shape (default),
  * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles
- * (cta_group::2), 3 = one CTA per 128 x 128 tile.  Results are identical; for
- * measurements and tests. */
+ * (cta_group::2), 3 / 5 = one CTA per 128 x 128 / 128 x 64 tile.  Results are
+ * identical; for measurements and tests. */
 int ls_gemm_set_variant(int variant);
 
 /* Measurement aid, no reference counterpart: launches a kernel that issues only
@@ -163,6 +163,12 @@ int ls_gemm_set_variant(int variant);
  * times it with events on `stream`.  The rate it reaches is the ceiling of the
  * tensor pipe at the clock the power cap allows. */
 int ls_fp4_mma_peak(int rounds, double *flop_out, void *stream);
+
+/* Products of at most 128 rows are launched with programmatic stream
+ * serialization (default on): the kernel's set-up overlaps the tail of the
+ * kernel before it in the stream, and it waits for that kernel before its first
+ * load.  0 switches this off (ordinary launches).  For measurements. */
+int ls_gemm_set_pdl(int on);
 
 /* K-splitting of the two GEMM entry points: 0 = by shape (default: products of
  * more than 128 rows with few output tiles and a long K, i.e. weight gradients

@@ -32,6 +32,7 @@ _SIGS = {
     "ls_gemm_status": (c_int, [c_vp]),
     "ls_gemm_set_variant": (c_int, [c_int]),
     "ls_gemm_set_splits": (c_int, [c_int]),
+    "ls_gemm_set_pdl": (c_int, [c_int]),
     "ls_fp4_mma_peak": (c_int, [c_int, ctypes.POINTER(ctypes.c_double), c_vp]),
     "ls_mxfp4_linear_noalloc": (c_int, [c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp, c_vp]),
     "ls_wire_handle_bytes": (c_i64, []),

@@ -35,18 +35,23 @@ constexpr int kTmemCols = 512;
 
 template <int BN>
 struct Cfg {
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    // Narrow tiles (64 columns) are for short-M products, which are weight streams: the
+    // number of SMs that load and the bytes each keeps in flight matter, the tile shape does
+    // not.  Their stages are small, so there are more of them.
+    static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : 8;
     static constexpr int A_BYTES = BM * BKB;
     static constexpr int B_BYTES = BN * BKB;
     static constexpr int SFA_BYTES = 1024;                 // 128 rows x 8 k-blocks
-    static constexpr int SFB_BYTES = (BN / 128) * 1024;
+    static constexpr int SFB_TILES = BN >= 128 ? BN / 128 : 1;   // 128-row scale tiles of W that a tile touches
+    static constexpr int SFB_BYTES = SFB_TILES * 1024;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
     static constexpr int OVL = BN == 256 ? 32 : 0;        // columns shared by the two accumulators
     static constexpr int ACC1 = BN - OVL;                 // first column of the second accumulator
     static constexpr int SFA_COL = 2 * BN - OVL;          // 8 columns
-    static constexpr int SFB_COL = SFA_COL + 8;           // BN / 16 columns
-    static_assert(SFB_COL + BN / 16 <= kTmemCols, "tensor memory overflow");
+    static constexpr int SFB_COL = SFA_COL + 8;           // 8 columns per 128 rows of W
+    static_assert(SFB_COL + SFB_TILES * 8 <= kTmemCols, "tensor memory overflow");
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static_assert(SMEM <= 227 * 1024, "shared memory overflow");
 };
 
 struct GemmParams {
@@ -232,7 +237,7 @@ __device__ __forceinline__ void store_chunk(const Epi &p, void *cbase, bool bf16
 template <int CTAS, int ATOMS, int SFB_ATOMS>
 __device__ __forceinline__ void issue_stage(uint32_t acc, uint64_t adesc, uint64_t bdesc, uint64_t sfa_desc,
                                             uint64_t sfb_desc, uint32_t sfa_t, uint32_t sfb_t, uint32_t idesc,
-                                            bool first_of_tile, bool skip_cp, bool skip_mma)
+                                            bool first_of_tile, bool skip_cp, bool skip_mma, uint32_t sfb_sub = 0)
 {
     constexpr int SFB_COLS = 4 * SFB_ATOMS;                 // columns per k-tile
     if (!skip_cp) {
@@ -250,7 +255,7 @@ __device__ __forceinline__ void issue_stage(uint32_t acc, uint64_t adesc, uint64
             constexpr uint32_t kId[2] = {0u, 2u};           // byte of the scale column used by this MMA
             const uint32_t id = kId[kb & 1];
             ptx::mma_mxf4<CTAS>(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc | (id << 29) | (id << 4),
-                                sfa_t + 4 * (kb >> 1) + (id << 30), sfb_t + SFB_COLS * (kb >> 1) + (id << 30),
+                                sfa_t + 4 * (kb >> 1) + (id << 30), sfb_t + sfb_sub + SFB_COLS * (kb >> 1) + (id << 30),
                                 (kb == 0 && first_of_tile) ? 0u : 1u);
         }
     }
@@ -303,6 +308,12 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
+    // Programmatic dependent launch: this grid may have started while the kernel before it in
+    // the stream was still running (its set-up above overlaps that kernel's tail), and the
+    // kernel after it may start its own set-up now.  Nothing that depends on earlier kernels
+    // has been touched so far; the producer waits for them before its first load, and every
+    // store of this kernel follows from those loads.  (Both are no-ops in an ordinary launch.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -310,6 +321,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
             ptx::prefetch_tmap(&tm_a0);
             ptx::prefetch_tmap(&tm_a1);
             ptx::prefetch_tmap(&tm_b);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             uint32_t it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -326,14 +338,15 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     const uint32_t sf_bytes = 512u * atoms;
                     const uint32_t st = smem_base + s * C::STAGE_BYTES;
                     // scale tiles of W rows past N do not exist; their products are never stored
-                    const int b_atoms = min(BN / 128, n_atoms - nt * (BN / 128));
+                    const int sfb_tile0 = nt * BN / 128;                  // first 128-row scale tile of this column tile
+                    const int b_atoms = min(C::SFB_TILES, n_atoms - sfb_tile0);
                     ptx::mbar_expect_tx(full_bar(s), uint32_t(p.a_box_bytes) + C::B_BYTES + sf_bytes * (1 + b_atoms));
                     ptx::tma_load_2d(st, tma, kt * BKB, mt * BM, full_bar(s));
                     ptx::tma_load_2d(st + C::A_BYTES, &tm_b, kt * BKB, nt * BN, full_bar(s));
                     ptx::bulk_load(st + C::A_BYTES + C::B_BYTES, sfa + int64_t(kt) * 1024, sf_bytes, full_bar(s));
                     for (int r = 0; r < b_atoms; r++)
                         ptx::bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + r * 1024,
-                                       p.sfb + (int64_t(nt * (BN / 128) + r) * k_atoms + 2 * kt) * 512,
+                                       p.sfb + (int64_t(sfb_tile0 + r) * k_atoms + 2 * kt) * 512,
                                        sf_bytes, full_bar(s));
                 }
             }
@@ -356,6 +369,11 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 ptx::tc_fence_after();
                 const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0);
                 const int kt0 = kt_begin(split_of(t)), kt1 = kt_end(split_of(t));
+                // A 64-column tile uses one half of a 128-row scale tile of W: the rows 32 c .. 32 c + 31
+                // of a scale tile sit in column c of its group of four, so the second half starts at
+                // column 2.
+                const int nt_of = (t / p.splits) / p.nbatch / m_tiles;
+                const uint32_t sfb_sub = BN >= 128 ? 0u : uint32_t((nt_of * BN) % 128) / 32u;
                 for (int kt = kt0; kt < kt1; kt++, it++) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
@@ -363,11 +381,11 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     ptx::tc_fence_after();
                     const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);       // stage offset in 16-byte units
                     if (2 * kt + 2 <= k_atoms)
-                        issue_stage<1, 2, BN / 128>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
-                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false);
+                        issue_stage<1, 2, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                        tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
                     else
-                        issue_stage<1, 1, BN / 128>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
-                                                    tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false);
+                        issue_stage<1, 1, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                        tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
                     ptx::tc_commit(empty_bar(s));
                 }
                 if (ok) ptx::tc_commit(acc_full_bar);
@@ -405,16 +423,18 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
 #pragma unroll 1                                    // code size: the body already holds two chunks
             for (int i = 0; i < CH; i += 2) {
                 ptx::tmem_ld_wait(ra);
-                ptx::tmem_ld32(acc + 32 * ((first + i + 1) % CH), rb);
+                if (i + 1 < CH) ptx::tmem_ld32(acc + 32 * ((first + i + 1) % CH), rb);
                 if (i == 0) {                               // first chunk drained: the next tile may start
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(acc_free_bar);
                 }
                 emit((first + i) % CH, ra);
-                ptx::tmem_ld_wait(rb);
-                if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * ((first + i + 2) % CH), ra);
-                emit((first + i + 1) % CH, rb);
+                if (i + 1 < CH) {
+                    ptx::tmem_ld_wait(rb);
+                    if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * ((first + i + 2) % CH), ra);
+                    emit((first + i + 1) % CH, rb);
+                }
             }
         }
     }
@@ -774,6 +794,8 @@ int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kby
     return LS_OK;
 }
 
+std::atomic<int> g_gemm_pdl{1};       // 1: the single-CTA kernel is launched with programmatic stream serialization
+
 template <int BN>
 int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
            cudaStream_t st)
@@ -791,8 +813,17 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
     }
     int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.nbatch * p.splits;
     int grid = tiles < sm_count() ? tiles : sm_count();
-    mxfp4_gemm_kernel<BN><<<grid, kGemmThreads, C::SMEM, st>>>(ta0, ta1, tb, p);
-    LS_LAUNCH_CHECK("mxfp4_gemm");
+    // launched with programmatic stream serialization: see the note in the kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(grid), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = g_gemm_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+    cfg.attrs = at, cfg.numAttrs = 1;
+    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_kernel<BN>, ta0, ta1, tb, p));
     return LS_OK;
 }
 
@@ -974,8 +1005,19 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     // Single-CTA kernel: 128-column tiles when 256-column tiles would leave more than half
     // the SMs without one (the weight stream of a short-M product needs the SMs' loads in
     // flight more than it needs wide tiles).
-    const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256) * nbatch;
-    const int bn = pair ? 256 : (variant == 3 || (variant == 0 && tiles256 * 2 <= sm_count())) ? 128 : 256;
+    // Narrower still (64 columns) while the tiles of the wider shape would not occupy half
+    // the SMs: N = K = 4096 has 32 tiles of 128 columns but 64 of 64.
+    const int64_t m_tiles_ = (M + BM - 1) / BM;
+    auto tiles_of = [&](int w_) { return m_tiles_ * ((N + w_ - 1) / w_) * nbatch; };
+    int bn = 256;
+    if (!pair) {
+        if (variant == 3) bn = 128;
+        else if (variant == 5) bn = 64;
+        else if (variant == 0) {
+            if (tiles_of(256) * 2 <= sm_count()) bn = 128;
+            if (bn == 128 && tiles_of(128) * 2 <= sm_count()) bn = 64;
+        }
+    }
     if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
@@ -1031,8 +1073,9 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     if (pair) {
         if (int rc = launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
     } else {
-        if (int rc = bn == 128 ? launch<128>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))
-                               : launch<256>(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream)))
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (int rc = bn == 64 ? launch<64>(ta0, ta1, tb, p, st)
+                   : bn == 128 ? launch<128>(ta0, ta1, tb, p, st) : launch<256>(ta0, ta1, tb, p, st))
             return rc;
     }
     if (p.splits > 1) {
@@ -1080,8 +1123,14 @@ extern "C" int ls_gemm_status(int *status_host)
 
 extern "C" int ls_gemm_set_variant(int variant)
 {
-    if (variant < 0 || variant > 3) return fail(LS_EINVAL, "variant must be 0..3");
+    if (variant < 0 || variant > 5 || variant == 4) return fail(LS_EINVAL, "variant must be 0..3 or 5");
     g_gemm_variant.store(variant, std::memory_order_relaxed);
+    return LS_OK;
+}
+
+extern "C" int ls_gemm_set_pdl(int on)
+{
+    g_gemm_pdl.store(on ? 1 : 0, std::memory_order_relaxed);
     return LS_OK;
 }
 

@@ -135,7 +135,9 @@ def test_skinny_shapes(mods, M, N, K):
 
 
 @pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2), (3, 40, 300, 1152, 2), (1, 700, 520, 1024, 1), (3, 300, 264, 512, 2),
-                                                  (2, 300, 520, 4096, 5), (2, 1024, 1024, 16384, 0)])
+                                                  (2, 300, 520, 4096, 5), (2, 1024, 1024, 16384, 0),
+                                                  (5, 16, 4096, 512, 1), (5, 1, 1000, 1152, 1), (5, 100, 300, 1152, 2),
+                                                  (5, 128, 264, 640, 3), (5, 40, 8192, 256, 1), (5, 130, 200, 384, 1)])
 def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
     # power-of-two scales on an integer grid: every partial sum is exact, so a split
     # product must equal the unsplit one bit for bit, on both kernels and both batches
@@ -165,7 +167,7 @@ def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
         for got, ref in ((c, want[0]), (c1, want[0]), (c2, want[1]), (cb, want[1])):
             _check(got, ref.float().to(got.dtype), f"{M}x{N}x{K} splits {splits}")
     assert (guard == 777.0).all()
-    assert L.ls_gemm_set_splits(17) < 0 and L.ls_gemm_set_splits(-1) < 0
+    assert L.ls_gemm_set_splits(17) < 0 and L.ls_gemm_set_splits(-1) < 0 and L.ls_gemm_set_variant(4) < 0 and L.ls_gemm_set_variant(6) < 0
 
 
 @pytest.mark.parametrize("M,N,K,dt", [(256, 512, 384, torch.bfloat16), (130, 256, 256, torch.bfloat16),
@@ -295,3 +297,49 @@ def test_linearity_full_size(mods):
     for x, c in ((x1, c1), (x2, c2)):
         xc, xs = ref_port.quantize(x[rows.cuda()].cpu())
         _check(c[rows.cuda()], ref_port.gemm_fake_quant(xc, xs, wc, wsc, torch.float32), "config 2 rows")
+
+
+def test_dependent_launch_chain_matches_ordinary_launches(mods):
+    # Short-M products are launched with programmatic stream serialization: a chain in which each
+    # product reads what the one before wrote (re-quantized) must give the same bits either way,
+    # eagerly and replayed from a CUDA graph
+    fp4, mg, _ = mods
+    from lockstep_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn(16, 1024, device="cuda", generator=g).bfloat16()
+    ws = [fp4.quantize_mxfp4_packed((torch.randn(1024, 1024, device="cuda", generator=g) * 0.05).bfloat16()) for _ in range(6)]
+
+    def chain(h):
+        for pw, sw in ws:
+            ph, sh = fp4.quantize_mxfp4_packed(h)
+            h = mg.mxfp4_gemm_packed(ph, pw, sh, sw)
+        return h
+
+    def gemm_only_chain(ph, sh):
+        outs = []
+        for pw, sw in ws:                                    # back-to-back GEMM launches, nothing in between
+            outs.append(mg.mxfp4_gemm_packed(ph, pw, sh, sw))
+        return outs
+
+    try:
+        assert L.ls_gemm_set_pdl(0) == 0
+        want = chain(x)
+        ph, sh = fp4.quantize_mxfp4_packed(x)
+        want_outs = gemm_only_chain(ph, sh)
+        assert L.ls_gemm_set_pdl(1) == 0
+        got = chain(x)
+        got_outs = gemm_only_chain(ph, sh)
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            replayed = gemm_only_chain(ph, sh)
+            replayed_chain = chain(x)
+        graph.replay()
+        torch.cuda.synchronize()
+        mg.gemm_status()
+    finally:
+        L.ls_gemm_set_pdl(1)
+    assert torch.equal(got, want) and torch.equal(replayed_chain, want)
+    for a, b, c in zip(want_outs, got_outs, replayed):
+        assert torch.equal(a, b) and torch.equal(a, c)

@@ -83,3 +83,20 @@ def test_tiny_decoder_trains():
         _, loss1 = t.time(steps=8, warmup=0)
         t.close()
         assert np.isfinite(loss1) and loss1 < loss0           # the loss goes down on a repeated batch
+
+
+def test_bucketed_sync_sends_under_backward_and_trains_alike():
+    # the flat gradient buffer averaged by one Wire after backward (train.py:124-138) against the
+    # bucketed form whose send phases run on a side stream during backward
+    import train_bench
+    kw = dict(layers=2, width=256, heads=4, context=128, batch=8, vocab=512)
+    losses = {}
+    for overlap in (False, True):
+        t = train_bench.Trainer("mxfp4", overlap=overlap, buckets=3, **kw)
+        assert (len(t.parts) == 3) == overlap
+        _, first = t.time(steps=1, warmup=0)
+        _, last = t.time(steps=10, warmup=0)
+        t.close()
+        assert np.isfinite(last) and last < first
+        losses[overlap] = last
+    assert abs(losses[True] - losses[False]) <= 0.05 * abs(losses[False])

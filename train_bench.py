@@ -95,36 +95,83 @@ class Decoder(nn.Module):
 
 
 class Trainer:
-    """Model + fused AdamW + a flat fp32 gradient buffer averaged by a Wire after backward."""
+    """Model + fused AdamW + a flat fp32 gradient buffer averaged by the FP4 wire.
+
+    overlap=False: one Wire over the whole buffer, called after the backward pass
+    (train.py:124-138).  overlap=True: the buffer is cut into `buckets` contiguous slices at
+    parameter boundaries, each with its own Wire; as soon as the last gradient of a slice
+    has been accumulated, that slice's send phase (encode + push to the owners) is queued
+    on a side stream and runs under the rest of the backward pass; the owner and decode
+    phases follow after the backward pass."""
 
     def __init__(self, kind="mxfp4", layers=12, width=1024, heads=16, context=1024, batch=16, vocab=32000,
-                 device="cuda", wire_method="mxfp4ef", world=1, rank=0):
+                 device="cuda", wire_method="mxfp4ef", world=1, rank=0, overlap=False, buckets=4):
         from lockstep_b200 import wire
         torch.manual_seed(0)
         self.model = Decoder(layers, width, heads, context, vocab, make_linear(kind)).to(device)
         self.params = list(self.model.parameters())
         self.flat = torch.zeros(sum(p.numel() for p in self.params), device=device)
-        at = 0
+        at, spans = 0, []
         for p in self.params:                                  # every gradient is a view of the flat buffer
             p.grad = self.flat[at:at + p.numel()].view_as(p)
+            spans.append((at, at + p.numel()))
             at += p.numel()
-        self.sync = wire.Wire(wire_method, self.flat.numel(), world, rank) if wire_method else None
+        self.overlap = bool(overlap and wire_method)
+        self.sync, self.parts = None, []
+        if wire_method and not self.overlap:
+            self.sync = wire.Wire(wire_method, self.flat.numel(), world, rank)
+        elif self.overlap:
+            # contiguous groups of parameters of about equal size; a slice starts on a 32-byte boundary
+            target, lo, members = self.flat.numel() / buckets, 0, []
+            for i, (a, b) in enumerate(spans):
+                members.append(i)
+                last = i == len(spans) - 1
+                if last or (b - lo >= target and b % 8 == 0 and len(self.parts) < buckets - 1):
+                    w = wire.Wire(wire_method, b - lo, world, rank)
+                    w.set_mode("launches", device=torch.device(device) if not isinstance(device, torch.device) else device)
+                    self.parts.append({"wire": w, "grad": self.flat[lo:b], "members": members, "pending": 0,
+                                       "sent": torch.cuda.Event()})
+                    lo, members = b, []
+            self.side = torch.cuda.Stream()
+            self.ready = torch.cuda.Event()
+            for part in self.parts:
+                for i in part["members"]:
+                    self.params[i].register_post_accumulate_grad_hook(self._hook(part))
         decay = [p for p in self.params if p.dim() >= 2]
         rest = [p for p in self.params if p.dim() < 2]
         self.opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}],
                                      lr=6e-4, betas=(0.9, 0.95), fused=True)
-        gen = torch.Generator(device=device).manual_seed(0)
+        gen = torch.Generator(device=device).manual_seed(rank)
         ids = torch.randint(0, vocab, (batch, context + 1), device=device, generator=gen)
         self.x, self.y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
         self.tokens_per_step = batch * context
 
+    def _hook(self, part):
+        def fire(_param):
+            part["pending"] -= 1
+            if part["pending"] == 0:                          # the slice is final: send it under the rest of backward
+                main = torch.cuda.current_stream()
+                self.ready.record(main)
+                with torch.cuda.stream(self.side):
+                    self.side.wait_event(self.ready)
+                    part["wire"].send(part["grad"])
+                    part["sent"].record(self.side)
+        return fire
+
     def step(self):
         self.flat.zero_()
+        for part in self.parts:
+            part["pending"] = len(part["members"])
         with torch.autocast("cuda", torch.bfloat16):
             loss = self.model(self.x, self.y)
         loss.backward()
         if self.sync is not None:
             self.sync(self.flat)
+        main = torch.cuda.current_stream()
+        for part in reversed(self.parts):                      # the order the slices were sent in
+            main.wait_event(part["sent"])
+            part["wire"].reduce()
+            part["wire"].finish(part["grad"])
         torch.nn.utils.clip_grad_norm_(self.params, 1.0)
         self.opt.step()
         return loss
@@ -140,13 +187,15 @@ class Trainer:
             loss = self.step()
         b.record()
         torch.cuda.synchronize()
-        if self.sync is not None:
-            self.sync.status()
+        for w in [self.sync] + [part["wire"] for part in self.parts]:
+            if w is not None:
+                w.status()
         return a.elapsed_time(b) / steps / 1e3, float(loss.detach())
 
     def close(self):
-        if self.sync is not None:
-            self.sync.close()
+        for w in [self.sync] + [part["wire"] for part in self.parts]:
+            if w is not None:
+                w.close()
 
 
 def training_step_time(kind="mxfp4", steps=5, warmup=2, **kw):
@@ -156,19 +205,29 @@ def training_step_time(kind="mxfp4", steps=5, warmup=2, **kw):
     return out
 
 
-def report(device, steps=5, warmup=2):
+def report(device, steps=5, warmup=2, world=1, rank=0):
     """The `train_step` object of the benchmark line: tokens/s of the 12-layer configuration
-    with each kind of block projection, gradient sync through the FP4 wire included."""
+    with each kind of block projection (one rank only), and the step time with the gradient
+    sync after the backward pass against the bucketed sync that sends under it."""
     out = {}
-    for kind in ("dense", "ste", "mxfp4"):
+    kinds = ("dense", "ste", "mxfp4") if world == 1 else ("mxfp4",)
+    for kind in kinds:
         torch.cuda.empty_cache()
-        t = Trainer(kind, device=device)
+        t = Trainer(kind, device=device, world=world, rank=rank)
         sec, loss = t.time(steps, warmup)
-        out[kind] = {"tokens_per_s": t.tokens_per_step / sec, "ms_per_step": sec * 1e3, "loss": loss}
+        out[kind] = {"tokens_per_s": world * t.tokens_per_step / sec, "ms_per_step": sec * 1e3, "loss": loss}
         t.close()
         del t
-    return {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 vocab32000, bf16 autocast, fused AdamW, "
-                     "synthetic ids seed 0; gradients in one flat fp32 buffer averaged by Wire('mxfp4ef') every step",
-            "block_linears": out,
-            "mxfp4_vs_dense": out["mxfp4"]["tokens_per_s"] / out["dense"]["tokens_per_s"],
-            "ste_vs_dense": out["ste"]["tokens_per_s"] / out["dense"]["tokens_per_s"]}
+    torch.cuda.empty_cache()
+    t = Trainer("mxfp4", device=device, world=world, rank=rank, overlap=True)
+    sec, loss = t.time(steps, warmup)
+    t.close()
+    res = {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 per rank vocab32000, bf16 autocast, fused AdamW, "
+                    "synthetic ids seeded by rank; gradients in one flat fp32 buffer averaged by Wire('mxfp4ef') every step",
+           "block_linears": out,
+           "sync": {"after_backward_ms": out["mxfp4"]["ms_per_step"], "sent_under_backward_ms": sec * 1e3,
+                    "buckets": len(t.parts), "loss": loss}}
+    if world == 1:
+        res["mxfp4_vs_dense"] = out["mxfp4"]["tokens_per_s"] / out["dense"]["tokens_per_s"]
+        res["ste_vs_dense"] = out["ste"]["tokens_per_s"] / out["dense"]["tokens_per_s"]
+    return res
