@@ -530,7 +530,7 @@ def main():
             ceil["cublaslt_nvfp4_error"] = repr(e)[:200]
         trip = {"gemm": [], "mma_only": [], "cublaslt": []}
 
-        def timed(fn, key):
+        def time_one(fn, key):
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -538,10 +538,10 @@ def main():
             b.record()
             trip[key].append((a, b))
         for _ in range(60):
-            timed(lambda: dual_gemm.dual_mxfp4_packed(pkq[:m], pkq[m:], w_pk, sfq[:halfq], sfq[halfq:], w_sf), "gemm")
-            timed(lambda: _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream())), "mma_only")
+            time_one(lambda: dual_gemm.dual_mxfp4_packed(pkq[:m], pkq[m:], w_pk, sfq[:halfq], sfq[halfq:], w_sf), "gemm")
+            time_one(lambda: _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream())), "mma_only")
             if lib_args:
-                timed(lambda: torch._scaled_mm(*lib_args, out_dtype=torch.bfloat16), "cublaslt")
+                time_one(lambda: torch._scaled_mm(*lib_args, out_dtype=torch.bfloat16), "cublaslt")
         torch.cuda.synchronize()
         mxfp4_gemm.gemm_status()
         med = {k: sorted(a.elapsed_time(b) for a, b in v)[len(v) // 2] for k, v in trip.items() if v}

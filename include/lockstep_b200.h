@@ -243,11 +243,13 @@ int ls_wire_int_allreduce(void *handle, float *g, int64_t numel, float *res, flo
 
 /* How ls_wire_allreduce runs a step on this handle.  mode: 0 = default (the
  * cooperative launch), 1 = three launches, 2 = one cooperative launch.  subs:
- * sub-ranges each shard is cut into by the cooperative launch (0 = default: 2
- * on one rank, 1 otherwise; else 1..8; lowered until the shard divides into multiples of 256 elements).
+ * sub-ranges each shard is cut into by the cooperative launch (0 = default: 2,
+ * 1 on two ranks; else 1..8; lowered until the shard divides into multiples of
+ * 256 elements).
  * stagger != 0: the CTAs take the three items of a pipeline step in rotated
- * orders.  The cooperative launch needs the whole grid resident at once: do not
- * run it beside other kernels that occupy the SMs for long.  ls_wire_mode
+ * orders (also the default from three ranks up when subs is 0).  The
+ * cooperative launch needs the whole grid resident at once: do not run it
+ * beside other kernels that occupy the SMs for long.  ls_wire_mode
  * returns the mode in force (1 or 2).  No reference counterpart. */
 int ls_wire_set_mode(void *handle, int mode, int subs, int stagger);
 int ls_wire_mode(void *handle);

@@ -869,10 +869,14 @@ Sub whole_shard(const Wire *w) { return Sub{0, 0u, uint32_t(w->g.shard / 8)}; }
 int subs_of(const Wire *w, int want)
 {
     const int64_t units = w->g.shard / 256;
-    // default: two sub-ranges on one rank, one otherwise (every extra sub-range costs two
-    // CTA-wide drains per phase; measured 64 Mi elements with error feedback: one rank
-    // 321 / 306 / 345 us for 1 / 2 / 4 sub-ranges, two ranks 268 / 288 / 341 us)
-    int s = want > 0 ? want : (w->g.world == 1 ? 2 : 1);
+    // default: two sub-ranges, one on two ranks.  Every part boundary drains the CTA (barrier,
+    // fence, flag), so more sub-ranges cost more than their overlap wins.  Measured, 64 Mi
+    // elements with error feedback, 1 / 2 / 4 sub-ranges: one rank 321 / 306 / 345 us, two
+    // ranks 268 / 288 / 341 us, four ranks 281 / 294 / 358 us and 266 us for two sub-ranges
+    // with the CTAs taking a step's three items in rotated orders (the default from three
+    // ranks up).  Letting the warps of a CTA pass the boundaries on their own (no barrier)
+    // was slower still: the early warps' polling competes with the others' memory traffic.
+    int s = want > 0 ? want : (w->g.world == 2 ? 1 : 2);
     if (s > kMaxSub) s = kMaxSub;
     while (s > 1 && units % s != 0) s--;
     return s;
@@ -887,6 +891,14 @@ const void *fused_entry(int world)
     case 8: return reinterpret_cast<const void *>(wire_fused_kernel<8>);
     default: return reinterpret_cast<const void *>(wire_fused_kernel<0>);
     }
+}
+
+// Rotated item orders: asked for explicitly, or by default from three ranks up when the
+// number of sub-ranges was left to the library too.
+int stagger_of(const Wire *w)
+{
+    if (w->mode & 0x100) return 1;
+    return (w->subs == 0 && w->g.world >= 3) ? 1 : 0;
 }
 
 // CTAs of the cooperative kernel that can be resident on this device at once.
@@ -991,7 +1003,7 @@ extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, f
     w->epoch++;
     FusedArgs a{};
     fill_rank(a.r[0], w, g, numel, res, ores);
-    a.nranks = 1, a.subs = subs_of(w, w->subs), a.reverse = reverse, a.stagger = (w->mode & 0x100) ? 1 : 0;
+    a.nranks = 1, a.subs = subs_of(w, w->subs), a.reverse = reverse, a.stagger = stagger_of(w);
     return launch_fused(a, capacity, static_cast<cudaStream_t>(stream));
 }
 
@@ -1017,7 +1029,7 @@ extern "C" int ls_wire_allreduce_group(void *const *handles, float *const *gs, i
         w->epoch++;
         fill_rank(a.r[r], w, gs[r], numel, ress ? ress[r] : nullptr, oress ? oress[r] : nullptr);
     }
-    a.nranks = world, a.subs = subs_of(w0, w0->subs), a.reverse = reverse, a.stagger = (w0->mode & 0x100) ? 1 : 0;
+    a.nranks = world, a.subs = subs_of(w0, w0->subs), a.reverse = reverse, a.stagger = stagger_of(w0);
     return launch_fused(a, capacity, static_cast<cudaStream_t>(stream));
 }
 
