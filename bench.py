@@ -294,7 +294,7 @@ def wire_leg(args, dev, rank, world, barrier, pk):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     exact = bool(flag.item() == 1.0)
 
-    wn = (8 << 20) if args.small else (64 << 20)
+    wn = args.wire_elements or ((8 << 20) if args.small else (64 << 20))
     wsteps = max(3, min(args.steps, 30))
     gw = torch.Generator(device=dev).manual_seed(100 + rank)
     z = torch.randn(wn, device=dev, generator=gw)
@@ -397,6 +397,7 @@ def main():
     ap.add_argument("--e2e-chunks", type=int, default=2, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--no-wire", action="store_true", help="skip the all-reduce leg")
     ap.add_argument("--no-train", action="store_true", help="skip the FP4-linear training-step leg")
+    ap.add_argument("--wire-elements", type=int, default=0, help="elements per rank of the all-reduce leg (profiling runs)")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M <= 16 rows of the shape sweep")
     ap.add_argument("--no-sustained", action="store_true", help="time only the K steps (profiling runs)")
     ap.add_argument("--small", action="store_true", help="1024-row batches (profiling under ncu)")
@@ -485,14 +486,56 @@ def main():
     step_ms = sum(ev.e[0].elapsed_time(ev.e[2]) for ev in evs)
     quant_ms_k = sum(ev.e[0].elapsed_time(ev.e[1]) for ev in evs) / args.steps
     gemm_ms_k = sum(ev.e[1].elapsed_time(ev.e[2]) for ev in evs) / args.steps
-    sus = []
+    # Ceilings measured inside the same region, so that they see the same power state as the step:
+    # every 8th step is followed by (1) the MMA-only kernel (the pair kernel's instruction stream of
+    # block-scaled FP4 MMAs on operands resident in shared memory: no loads, no scale copies, no
+    # epilogue) and (2) cuBLASLt's block-scaled FP4 GEMM as torch exposes it (NVFP4: block 16, E4M3
+    # scales; this torch build has no MXFP4 recipe) on 8192^3, the same FLOPs as one dual launch.
+    import ctypes
+    from lockstep_b200 import _lib
+    sus, ceil, trip = [], {}, {"mma_only": [], "cublaslt": []}
     if not args.no_sustained:
-        n_sus = int(min(4000, max(args.steps, SUSTAINED_SECONDS / max(step_ms / args.steps * 1e-3 + 60e-6, 1e-5))))
+        L = _lib.lib()
+        flop = ctypes.c_double()
+        lib_args = None
+        if rank == 0 and not args.small:
+            try:
+                la = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
+                lb = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
+                lsa = torch.randint(0x30, 0x40, (N * (K // 16),), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+                lsb = torch.randint(0x30, 0x40, (N * (K // 16),), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+                torch._scaled_mm(la, lb.t(), lsa, lsb, out_dtype=torch.bfloat16)
+                lib_args = (la, lb.t(), lsa, lsb)
+            except Exception as e:                           # not offered by this build / device
+                ceil["cublaslt_nvfp4_error"] = repr(e)[:200]
+            _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream()))
+            torch.cuda.synchronize()
+
+        def time_one(fn, key):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            trip[key].append((a, b))
+        n_sus = int(min(4000, max(args.steps, SUSTAINED_SECONDS / max(step_ms / args.steps * 1e-3 + 80e-6, 1e-5))))
         sus = [Ev() for _ in range(n_sus)]
-        for ev in sus:
+        for i, ev in enumerate(sus):
             flush.zero_()
             step(ev)
+            if rank == 0 and not args.small and i % 8 == 4:
+                time_one(lambda: _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream())), "mma_only")
+                if lib_args:
+                    time_one(lambda: torch._scaled_mm(*lib_args, out_dtype=torch.bfloat16), "cublaslt")
         barrier()
+        med = {k: sorted(a.elapsed_time(b) for a, b in v)[len(v) // 2] for k, v in trip.items() if v}
+        if "mma_only" in med:
+            ceil["mma_only_tflops"] = flop.value / med["mma_only"] / 1e9
+            ceil["how"] = (f"inside the sustained region: after every 8th step one MMA-only launch ({len(trip['mma_only'])} in all) "
+                           "and one cuBLASLt NVFP4 8192^3 GEMM, each after an L2 flush; medians")
+        if "cublaslt" in med:
+            ceil["cublaslt_nvfp4_tflops"] = 2 * N * N * K / med["cublaslt"] / 1e9
+        del lib_args
     clocks = sampler.stop() if sampler else None
     mxfp4_gemm.gemm_status()
     timed = sus if sus else evs
@@ -504,54 +547,6 @@ def main():
     if clocks is not None:
         clocks["region"] = (f"{args.steps} + {len(sus)} timed steps (about {SUSTAINED_SECONDS} s of this load); "
                             "median SM clock over the samples under load")
-
-    # ---- ceilings measured in this run, interleaved with the GEMM launch so that all see one power
-    # state: (1) the MMA-only kernel (the pair kernel's instruction stream of block-scaled FP4 MMAs on
-    # operands resident in shared memory: no loads, no scale copies, no epilogue), (2) cuBLASLt's
-    # block-scaled FP4 GEMM as torch exposes it (NVFP4: block 16, E4M3 scales; this torch build has no
-    # MXFP4 recipe) on 8192^3, the same FLOPs as one dual launch.
-    import ctypes
-    from lockstep_b200 import _lib
-    ceil = {}
-    if not args.small:
-        L = _lib.lib()
-        flop = ctypes.c_double()
-        pkq, sfq = fp4.quantize_mxfp4_packed(both)
-        halfq = sfq.numel() // 2
-        lib_args = None
-        try:
-            la = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
-            lb = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
-            lsa = torch.randint(0x30, 0x40, (N * (K // 16),), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
-            lsb = torch.randint(0x30, 0x40, (N * (K // 16),), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
-            torch._scaled_mm(la, lb.t(), lsa, lsb, out_dtype=torch.bfloat16)
-            lib_args = (la, lb.t(), lsa, lsb)
-        except Exception as e:                               # not offered by this build / device
-            ceil["cublaslt_nvfp4_error"] = repr(e)[:200]
-        trip = {"gemm": [], "mma_only": [], "cublaslt": []}
-
-        def time_one(fn, key):
-            flush.zero_()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            fn()
-            b.record()
-            trip[key].append((a, b))
-        for _ in range(60):
-            time_one(lambda: dual_gemm.dual_mxfp4_packed(pkq[:m], pkq[m:], w_pk, sfq[:halfq], sfq[halfq:], w_sf), "gemm")
-            time_one(lambda: _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream())), "mma_only")
-            if lib_args:
-                time_one(lambda: torch._scaled_mm(*lib_args, out_dtype=torch.bfloat16), "cublaslt")
-        torch.cuda.synchronize()
-        mxfp4_gemm.gemm_status()
-        med = {k: sorted(a.elapsed_time(b) for a, b in v)[len(v) // 2] for k, v in trip.items() if v}
-        ceil.update({"gemm_ms": med["gemm"], "gemm_tflops": flops_step / med["gemm"] / 1e9,
-                     "mma_only_tflops": flop.value / med["mma_only"] / 1e9,
-                     "how": "60 rounds of [dual GEMM launch, MMA-only kernel, cuBLASLt NVFP4 8192^3], each after an "
-                            "L2 flush, medians"})
-        if "cublaslt" in med:
-            ceil["cublaslt_nvfp4_tflops"] = 2 * N * N * K / med["cublaslt"] / 1e9
-        del pkq, sfq, lib_args
 
     # ---- end to end: pinned host buffers in, pinned host buffers out, every step.
     # Row chunks of both batches flow through three streams (copy in, compute, copy out)
@@ -669,18 +664,17 @@ def main():
                     "copy_only": {"h2d_gbs_all_ranks": h2d_sum, "d2h_gbs_all_ranks": d2h_sum,
                                   "how": "every rank copies its own 134 MB pinned buffer at the same time, one direction "
                                          "at a time; sum over ranks"}},
-            "gpu_launches": 2 * (2 * warmup + 1 + args.steps + len(sus)) + (121 if ceil else 0) + 2 * chunks * (e2e_steps + 2) + wire_launches,
+            "gpu_launches": 2 * (2 * warmup + 1 + args.steps + len(sus)) + len(trip["mma_only"]) + 2 * chunks * (e2e_steps + 2) + wire_launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "mxfp4_gemm_pair_kernel (cta_group::2, dual batch)",
                          "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
                          "timed": f"median launch duration over the {len(timed)} steps of the sustained region (events "
                                   "around the launch, on its stream)",
-                         "peak_source": ("block-scaled FP4 MMA-only kernel measured in this run, interleaved with the GEMM "
+                         "peak_source": ("block-scaled FP4 MMA-only kernel measured in this run inside the same timed region "
                                          "(ls_fp4_mma_peak: the pair kernel's MMA stream on operands resident in shared memory)"
                                          if ceil.get("mma_only_tflops") else
                                          f"4 x {pk['source']} bf16 burst {pk['bf16']} (small run: no FP4 figure measured)"),
-                         "interleaved": ceil or None,
-                         "frac_interleaved": (ceil["gemm_tflops"] / ceil["mma_only_tflops"]) if ceil.get("mma_only_tflops") else None,
+                         "ceilings": ceil or None,
                          "frac_of_4x_bf16_burst": gemm_tflops / bf16x4,
                          "bf16_peaks": f"{pk['source']}: burst {pk['bf16']}, sustained {pk['bf16_sustained']} TFLOP/s",
                          "frac_of_spec": gemm_tflops / FP4_SPEC_TFLOPS, "spec_tflops": FP4_SPEC_TFLOPS,

@@ -149,6 +149,20 @@ int ls_mxfp4_gemm_quant(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t
                         void *c, int out_dtype, int act, uint8_t *q_packed, uint8_t *q_sf, int64_t M,
                         int64_t N, int64_t K, void *stream);
 
+/* Operands in the form of mxfp4_gemm.py:74-87 (mxfp4_gemm_fp8): E4M3 bytes that
+ * hold E2M1 values, a [M, K] K-contiguous, b [K, N] N-contiguous, b_scale
+ * [K/32, N].  Hopper needs that expansion; the B200 tensor cores take E2M1
+ * directly at twice the FP8 rate, so these re-encode the bytes (exactly) to the
+ * packed form ls_mxfp4_gemm reads:
+ *   ls_e4m3_to_packed    src [rows, K]          -> packed [rows, K/2]   K % 16 == 0
+ *   ls_e4m3_to_packed_t  src [K, N]             -> packed [N, K/2]      K % 32 == 0
+ *   ls_scales_to_sf_t    scale [K/32, rows] f32 -> scale-factor bytes of a [rows, K] operand
+ * A byte that is not one of the 16 images sets bit 1 of the error word that
+ * ls_gemm_status reports (LS_EINVAL); the call itself does not synchronise. */
+int ls_e4m3_to_packed(const uint8_t *src, int64_t rows, int64_t K, uint8_t *packed, void *stream);
+int ls_e4m3_to_packed_t(const uint8_t *src, int64_t K, int64_t N, uint8_t *packed, void *stream);
+int ls_scales_to_sf_t(const float *scale, int64_t rows, int64_t K, uint8_t *sf, int32_t *bad, void *stream);
+
 /* Which GEMM kernel the two entry points above launch: 0 = by shape (default),
  * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles
  * (cta_group::2), 3 / 5 = one CTA per 128 x 128 / 128 x 64 tile.  Results are
@@ -181,7 +195,7 @@ int ls_gemm_set_splits(int splits);
 
 /* Synchronises the device's error word to the host: returns LS_ETIMEOUT (and
  * clears the word) if any GEMM kernel since the last call abandoned a bounded
- * wait, LS_OK otherwise.  `status_host` (host int, may be NULL) receives the
+ * wait, LS_EINVAL if an E4M3 operand was off the E2M1 grid, LS_OK otherwise.  `status_host` (host int, may be NULL) receives the
  * raw word.  Blocks until prior work on the default stream is done. */
 int ls_gemm_status(int *status_host);
 

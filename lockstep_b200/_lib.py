@@ -58,6 +58,9 @@ _SIGS = {
     "ls_wire_reset": (c_int, [c_vp]),
     "ls_wire_debug_slots": (c_int, [c_vp, c_int, c_vp, ctypes.POINTER(c_i64), c_vp]),
     "ls_scales_to_sf": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "ls_scales_to_sf_t": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "ls_e4m3_to_packed": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
+    "ls_e4m3_to_packed_t": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
 }
 
 LS_F32, LS_BF16 = 0, 1

@@ -1118,7 +1118,9 @@ extern "C" int ls_gemm_status(int *status_host)
     LS_CUDA(cudaMemcpy(&v, err, sizeof(int), cudaMemcpyDeviceToHost));
     if (v) LS_CUDA(cudaMemset(err, 0, sizeof(int)));
     if (status_host) *status_host = v;
-    return v ? fail(LS_ETIMEOUT, "a GEMM kernel gave up waiting on a barrier") : LS_OK;
+    if (v & 1) return fail(LS_ETIMEOUT, "a GEMM kernel gave up waiting on a barrier");
+    if (v & 2) return fail(LS_EINVAL, "an E4M3 operand held a byte that is not an E2M1 value");
+    return LS_OK;
 }
 
 extern "C" int ls_gemm_set_variant(int variant)

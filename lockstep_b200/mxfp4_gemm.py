@@ -68,34 +68,29 @@ def mxfp4_gemm_packed_quant(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloa
     return c, q, q_sf
 
 
-_E4M3_TO_CODE = None
-
-
-def _e4m3_to_codes(x_fp8):
-    """Inverse of fp4.codes_to_e4m3 for bytes on the E2M1 grid."""
-    global _E4M3_TO_CODE
-    if _E4M3_TO_CODE is None or _E4M3_TO_CODE.device != x_fp8.device:
-        t = torch.full((256,), 255, dtype=torch.uint8)
-        t[fp4.E2M1_TO_E4M3.long()] = torch.arange(16, dtype=torch.uint8)
-        _E4M3_TO_CODE = t.to(x_fp8.device)
-    return _E4M3_TO_CODE[x_fp8.view(torch.uint8).long()]
-
-
 def mxfp4_gemm_fp8(a_fp8, b_fp8, a_scale, b_scale, out_dtype=torch.bfloat16):
     """a_fp8 [M, K] K-contiguous, b_fp8 [K, N] N-contiguous, both E4M3 bytes
     holding E2M1 values; a_scale [M, K//32], b_scale [K//32, N]
-    (mxfp4_gemm.py:74-87).  The operands are re-encoded to packed E2M1 (the
-    tensor core takes them natively) and go through the packed kernel."""
+    (mxfp4_gemm.py:74-87).  The reference expands FP4 to FP8 because Hopper's
+    tensor cores have no FP4 type; here two small kernels re-encode the bytes to
+    packed E2M1 (exactly; b is transposed on the way, its scales go straight to
+    the scale-factor layout) and the product runs on the MXFP4 tensor-core kernel
+    at the FP4 rate.  Nothing synchronises: a byte that is not an E2M1 value is
+    reported by `gemm_status()`."""
     need_cuda(a_fp8, b_fp8, a_scale, b_scale)
     M, K = a_fp8.shape
     K2, N = b_fp8.shape
     assert K == K2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
     assert a_scale.shape == (M, K // 32) and b_scale.shape == (K // 32, N)
-    a_codes = _e4m3_to_codes(a_fp8)
-    b_codes = _e4m3_to_codes(b_fp8.t().contiguous())
-    assert int(torch.maximum(a_codes.max(), b_codes.max())) < 16, "operands must hold E2M1 values"
-    return mxfp4_gemm_packed(fp4.pack_fp4(a_codes), fp4.pack_fp4(b_codes), a_scale,
-                             b_scale.t().contiguous(), out_dtype)
+    a_fp8, b_fp8 = aligned(a_fp8), aligned(b_fp8)
+    dev = a_fp8.device
+    a_pk = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    b_pk = torch.empty((N, K // 2), dtype=torch.uint8, device=dev)
+    check(lib().ls_e4m3_to_packed(ptr(a_fp8), M, K, ptr(a_pk), stream()))
+    check(lib().ls_e4m3_to_packed_t(ptr(b_fp8), K, N, ptr(b_pk), stream()))
+    sfb = torch.empty(fp4.sf_bytes(N, K), dtype=torch.uint8, device=dev)
+    check(lib().ls_scales_to_sf_t(ptr(aligned(b_scale.float())), N, K, ptr(sfb), None, stream()))
+    return mxfp4_gemm_packed(a_pk, b_pk, a_scale, sfb, out_dtype)
 
 
 def gemm_status():

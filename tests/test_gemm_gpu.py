@@ -239,22 +239,40 @@ def test_unaligned_views_are_accepted(mods):
     assert torch.equal(fp4.pack_fp4(codes), pa)
 
 
-def test_fp8_entry(mods):
+@pytest.mark.parametrize("M,N,K", [(128, 256, 256), (130, 200, 384), (16, 1000, 1152), (300, 72, 128)])
+def test_fp8_entry(mods, M, N, K):
     # reference signature (mxfp4_gemm.py:74-87): A [M, K] and B [K, N] as E4M3 bytes, b_scale [K/32, N];
     # expected value from the oracle's fp64 product of the dequantized operands
     fp4, mg, _ = mods
-    M, N, K = 128, 256, 256
     g = torch.Generator(device="cuda").manual_seed(3)
     ac = fp4.random_codes((M, K), device="cuda")
     bc = fp4.random_codes((K, N), device="cuda")
+    ac[0, :16] = torch.arange(16, dtype=torch.uint8, device="cuda")           # every code, negative zero included
+    bc[:16, 0] = torch.arange(16, dtype=torch.uint8, device="cuda")
     sa = torch.exp2(torch.randint(-2, 3, (M, K // 32), device="cuda", generator=g).float())
     sb = torch.exp2(torch.randint(-2, 3, (K // 32, N), device="cuda", generator=g).float())
     c = mg.mxfp4_gemm_fp8(fp4.codes_to_e4m3(ac), fp4.codes_to_e4m3(bc), sa, sb, out_dtype=torch.float32)
     mg.gemm_status()
     want = ref_port.gemm_fp64(ac.cpu(), sa.cpu(), bc.t().contiguous().cpu(), sb.t().contiguous().cpu())
-    assert torch.equal(c.cpu().double(), want)              # power-of-two scales, small K: every sum is exact
+    assert torch.equal(c.cpu().double(), want)              # power-of-two scales, short K: every sum is exact
     cb = mg.mxfp4_gemm_fp8(fp4.codes_to_e4m3(ac), fp4.codes_to_e4m3(bc), sa, sb)
     assert cb.dtype == torch.bfloat16 and torch.equal(cb.cpu(), want.float().bfloat16())
+
+
+def test_fp8_entry_reports_bytes_off_the_e2m1_grid(mods):
+    fp4, mg, _ = mods
+    M, N, K = 128, 128, 128
+    a = fp4.codes_to_e4m3(fp4.random_codes((M, K), device="cuda"))
+    b = fp4.codes_to_e4m3(fp4.random_codes((K, N), device="cuda"))
+    ones = torch.ones(M, K // 32, device="cuda")
+    for bad_a in (True, False):
+        aa, bb = a.clone(), b.clone()
+        (aa if bad_a else bb).view(torch.uint8)[5, 7] = 0x31              # 0.5625: an E4M3 value, not an E2M1 one
+        mg.mxfp4_gemm_fp8(aa, bb, ones, ones.t().contiguous())
+        with pytest.raises(RuntimeError, match="E2M1"):
+            mg.gemm_status()
+    mg.mxfp4_gemm_fp8(a, b, ones, ones.t().contiguous())
+    mg.gemm_status()                                        # clean again
 
 
 def test_dual_matches_two_singles_and_oracle(mods):
