@@ -74,6 +74,14 @@ int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int b
 int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
                         uint8_t *packed, float *scale, uint8_t *sf, void *stream);
 
+/* ls_quantize_mxfp4_t of act(x): act = 1 quantizes GELU(x) (0.5 x (1 + erf(x / sqrt 2)), computed
+ * in fp32 and rounded to bf16 as an elementwise pass would leave it) without that pass: the
+ * activation of lockstep's feed-forward block (train.py:53) is needed transposed for the
+ * weight gradient of the projection after it and need not exist in HBM.  bf16 input only;
+ * act = 0 is ls_quantize_mxfp4_t.  No single lockstep function does this. */
+int ls_quantize_mxfp4_t_act(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, int act,
+                            uint8_t *packed, float *scale, uint8_t *sf, void *stream);
+
 /* Both orientations of one tensor from one read of x [R, C]: what
  * ls_quantize_mxfp4 (packed + scale-factor bytes of x, blocks along C) and
  * ls_quantize_mxfp4_t (of x^T, blocks along R) would write.  For a linear layer

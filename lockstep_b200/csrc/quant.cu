@@ -251,7 +251,10 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <typename T, bool RNE>
+// ACT = 1 (bf16 only): the values quantized are GELU(x) rounded to bf16, as if an elementwise
+// pass had come first -- applied to the tile once it is in shared memory, so that the
+// activation of a feed-forward layer never has to exist in HBM for its weight gradient.
+template <typename T, bool RNE, int ACT = 0>
 __global__ void __launch_bounds__(kThreads)
 quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__restrict__ packed,
                   float *__restrict__ scale, uint8_t *__restrict__ sf, uint8_t *__restrict__ row_packed,
@@ -300,6 +303,19 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
             cp_async_wait<0>();
         }
         __syncthreads();
+        if constexpr (ACT == 1 && sizeof(T) == 2) {
+            uint32_t *words = reinterpret_cast<uint32_t *>(tile_smem + b * kTR * CHUNKS);
+#pragma unroll 4
+            for (int i = threadIdx.x; i < kTR * CHUNKS * 4; i += kThreads) {
+                const uint32_t u = words[i];
+                float lo = __uint_as_float(u << 16), hi = __uint_as_float(u & 0xFFFF0000u);
+                lo = (lo * 0.5f) * (1.0f + erff(lo * 0.70710678118654752440f));
+                hi = (hi * 0.5f) * (1.0f + erff(hi * 0.70710678118654752440f));
+                const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                words[i] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+            __syncthreads();
+        }
         const T *tile = reinterpret_cast<const T *>(tile_smem + b * kTR * CHUNKS);
         const int64_t r0 = (t / tiles_x) * kTR, c0 = (t % tiles_x) * TC;
         auto emit = [&](int64_t col, int rb, uint32_t e8, const uint32_t (&pk)[4]) {
@@ -735,8 +751,9 @@ extern "C" int ls_round_e2m1(const float *q, int64_t n, int rounding, uint8_t *c
 
 namespace {
 int quantize_t_impl(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, uint8_t *packed, float *scale,
-                    uint8_t *sf, uint8_t *row_packed, uint8_t *row_sf, void *stream)
+                    uint8_t *sf, uint8_t *row_packed, uint8_t *row_sf, void *stream, int act = 0)
 {
+    if (act != 0 && (act != 1 || x_dtype != LS_BF16)) return fail(LS_EINVAL, "activation %d needs bf16 input (0 none, 1 GELU)", act);
     if (int rc = check_device()) return rc;
     if (x_dtype != LS_F32 && x_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported dtype %d", x_dtype);
     if (rounding != LS_ROUND_REF && rounding != LS_ROUND_RNE) return fail(LS_EINVAL, "bad rounding %d", rounding);
@@ -758,6 +775,8 @@ int quantize_t_impl(const void *x, int x_dtype, int64_t R, int64_t C, int roundi
             LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
             LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
             LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
+            LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
+            LS_CUDA(cudaFuncSetAttribute(quantize_t_kernel<__nv_bfloat16, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTSmem));
             attr_set[dev] = true;
         }
     }
@@ -770,8 +789,12 @@ int quantize_t_impl(const void *x, int x_dtype, int64_t R, int64_t C, int roundi
     int rc;
     if (x_dtype == LS_BF16) {
         auto xp = static_cast<const __nv_bfloat16 *>(x);
-        rc = rne ? launch(quantize_t_kernel<__nv_bfloat16, true>, xp, kTRowBytes / 2)
-                 : launch(quantize_t_kernel<__nv_bfloat16, false>, xp, kTRowBytes / 2);
+        if (act == 1)
+            rc = rne ? launch(quantize_t_kernel<__nv_bfloat16, true, 1>, xp, kTRowBytes / 2)
+                     : launch(quantize_t_kernel<__nv_bfloat16, false, 1>, xp, kTRowBytes / 2);
+        else
+            rc = rne ? launch(quantize_t_kernel<__nv_bfloat16, true>, xp, kTRowBytes / 2)
+                     : launch(quantize_t_kernel<__nv_bfloat16, false>, xp, kTRowBytes / 2);
     } else {
         auto xp = static_cast<const float *>(x);
         rc = rne ? launch(quantize_t_kernel<float, true>, xp, kTRowBytes / 4)
@@ -787,6 +810,12 @@ extern "C" int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_
                                    uint8_t *packed, float *scale, uint8_t *sf, void *stream)
 {
     return quantize_t_impl(x, x_dtype, R, C, rounding, packed, scale, sf, nullptr, nullptr, stream);
+}
+
+extern "C" int ls_quantize_mxfp4_t_act(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, int act,
+                                       uint8_t *packed, float *scale, uint8_t *sf, void *stream)
+{
+    return quantize_t_impl(x, x_dtype, R, C, rounding, packed, scale, sf, nullptr, nullptr, stream, act);
 }
 
 extern "C" int ls_quantize_mxfp4_both(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,

@@ -102,6 +102,20 @@ def quantize_mxfp4_packed_t(x: torch.Tensor, rounding: str = "ref", want_scale: 
     return (packed, sf, scale) if want_scale else (packed, sf)
 
 
+def quantize_mxfp4_packed_t_gelu(x: torch.Tensor, rounding: str = "ref"):
+    """(extension) quantize_mxfp4_packed_t(gelu(x)) for bf16 x [R, C] without the elementwise
+    pass: the activation is applied to the tile inside the kernel.  R % 128 == 0."""
+    need_cuda(x)
+    assert x.dim() == 2 and x.shape[0] % 128 == 0 and x.dtype == torch.bfloat16
+    x = aligned(x)
+    R, C = x.shape
+    packed = torch.empty((C, R // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(C, R), dtype=torch.uint8, device=x.device)
+    check(lib().ls_quantize_mxfp4_t_act(ptr(x), _lib.dtype_code(x.dtype), R, C, _ROUNDING[rounding], 1,
+                                        ptr(packed), None, ptr(sf), stream()))
+    return packed, sf
+
+
 def quantize_mxfp4_both(x: torch.Tensor, rounding: str = "ref"):
     """(extension) quantize_mxfp4_packed(x) and quantize_mxfp4_packed_t(x) from one read
     of x [R, C]: returns (packed, sf, packed_t, sf_t).  R % 128 == 0 and C % 128 == 0."""

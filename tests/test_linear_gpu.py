@@ -100,3 +100,40 @@ def test_bucketed_sync_sends_under_backward_and_trains_alike():
         assert np.isfinite(last) and last < first
         losses[overlap] = last
     assert abs(losses[True] - losses[False]) <= 0.05 * abs(losses[False])
+
+
+@pytest.mark.parametrize("mode", ["ste", "mxfp4"])
+def test_fused_mlp_matches_the_unfused_composition(mode):
+    # out(gelu(fc(x))) with the activation quantized in the first GEMM's epilogue against two
+    # MXFP4Linear modules around F.gelu: outputs and all three gradients within the GEMM tolerance
+    from lockstep_b200 import fp4_linear
+    T, D = 512, 256
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    gy = torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    fused = fp4_linear.MXFP4MLP(D, 4 * D, backward=mode).cuda()
+    fc = fp4_linear.MXFP4Linear(D, 4 * D, backward=mode).cuda()
+    out = fp4_linear.MXFP4Linear(4 * D, D, backward=mode).cuda()
+    with torch.no_grad():
+        fc.weight.copy_(fused.fc.weight)
+        out.weight.copy_(fused.out.weight)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ya = fused(xa)
+    ya.backward(gy)
+    yb = out(torch.nn.functional.gelu(fc(xb)))
+    yb.backward(gy)
+    tol = 2e-2 if mode == "mxfp4" else 5e-3        # an MXFP4 backward re-quantizes slightly different values
+    _close(ya, yb, "fused mlp forward", 2e-3)
+    _close(xa.grad, xb.grad, "fused mlp dX", tol)
+    _close(fused.fc.weight.grad, fc.weight.grad, "fused mlp dW fc", tol)
+    _close(fused.out.weight.grad, out.weight.grad, "fused mlp dW out", tol)
+
+
+def test_transposed_quantizer_with_gelu_equals_two_passes():
+    from lockstep_b200 import fp4
+    g = torch.Generator(device="cuda").manual_seed(8)
+    c = (torch.randn(256, 384, device="cuda", generator=g) * 2).bfloat16()
+    want_p, want_sf = fp4.quantize_mxfp4_packed_t(torch.nn.functional.gelu(c))
+    got_p, got_sf = fp4.quantize_mxfp4_packed_t_gelu(c)
+    differ = (got_p != want_p).float().mean().item()          # erf of this library against torch's kernel
+    assert differ <= 1e-3, differ

@@ -55,13 +55,22 @@ class FeedForward(nn.Module):
         return self.out(F.gelu(self.fc(x)))
 
 
+def make_mlp(kind, fused):
+    """The feed-forward half of a block: two linears around GELU, or (fused) the MXFP4 module
+    that quantizes the activation in the first GEMM's epilogue.  Parameter names are the same."""
+    from lockstep_b200 import fp4_linear
+    if fused and kind != "dense":
+        return lambda width: fp4_linear.MXFP4MLP(width, 4 * width, backward=kind)
+    return lambda width: FeedForward(width, make_linear(kind))
+
+
 class Block(nn.Module):
-    def __init__(self, width, heads, linear):
+    def __init__(self, width, heads, linear, mlp):
         super().__init__()
         self.ln1 = nn.LayerNorm(width)
         self.attn = CausalSelfAttention(width, heads, linear)
         self.ln2 = nn.LayerNorm(width)
-        self.mlp = FeedForward(width, linear)
+        self.mlp = mlp(width)
 
     def forward(self, x):
         x = x + self.attn(self.ln1(x))
@@ -69,12 +78,12 @@ class Block(nn.Module):
 
 
 class Decoder(nn.Module):
-    def __init__(self, layers, width, heads, context, vocab, linear):
+    def __init__(self, layers, width, heads, context, vocab, linear, mlp):
         super().__init__()
         self.vocab = vocab
         self.tokens = nn.Embedding(vocab, width)
         self.positions = nn.Embedding(context, width)
-        self.blocks = nn.ModuleList([Block(width, heads, linear) for _ in range(layers)])
+        self.blocks = nn.ModuleList([Block(width, heads, linear, mlp) for _ in range(layers)])
         self.norm = nn.LayerNorm(width)
         # N(0, 0.02) for every matrix; the two projections that write into the residual
         # stream are scaled down by sqrt(2 * layers), as train.py:66-69 does
@@ -105,10 +114,10 @@ class Trainer:
     phases follow after the backward pass."""
 
     def __init__(self, kind="mxfp4", layers=12, width=1024, heads=16, context=1024, batch=16, vocab=32000,
-                 device="cuda", wire_method="mxfp4ef", world=1, rank=0, overlap=False, buckets=4):
+                 device="cuda", wire_method="mxfp4ef", world=1, rank=0, overlap=False, buckets=4, fused_mlp=True):
         from lockstep_b200 import wire
         torch.manual_seed(0)
-        self.model = Decoder(layers, width, heads, context, vocab, make_linear(kind)).to(device)
+        self.model = Decoder(layers, width, heads, context, vocab, make_linear(kind), make_mlp(kind, fused_mlp)).to(device)
         self.params = list(self.model.parameters())
         self.flat = torch.zeros(sum(p.numel() for p in self.params), device=device)
         at, spans = 0, []
@@ -210,12 +219,13 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
     with each kind of block projection (one rank only), and the step time with the gradient
     sync after the backward pass against the bucketed sync that sends under it."""
     out = {}
-    kinds = ("dense", "ste", "mxfp4") if world == 1 else ("mxfp4",)
-    for kind in kinds:
+    runs = (("dense", "dense", True), ("ste", "ste", True), ("mxfp4", "mxfp4", True),
+            ("mxfp4_unfused_mlp", "mxfp4", False)) if world == 1 else (("mxfp4", "mxfp4", True),)
+    for name, kind, fused in runs:
         torch.cuda.empty_cache()
-        t = Trainer(kind, device=device, world=world, rank=rank)
+        t = Trainer(kind, device=device, world=world, rank=rank, fused_mlp=fused)
         sec, loss = t.time(steps, warmup)
-        out[kind] = {"tokens_per_s": world * t.tokens_per_step / sec, "ms_per_step": sec * 1e3, "loss": loss}
+        out[name] = {"tokens_per_s": world * t.tokens_per_step / sec, "ms_per_step": sec * 1e3, "loss": loss}
         t.close()
         del t
     torch.cuda.empty_cache()
@@ -225,6 +235,7 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
     res = {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 per rank vocab32000, bf16 autocast, fused AdamW, "
                     "synthetic ids seeded by rank; gradients in one flat fp32 buffer averaged by Wire('mxfp4ef') every step",
            "block_linears": out,
+           "fused_mlp": "ste / mxfp4: the feed-forward half is fp4_linear.MXFP4MLP (GELU + quantize in the first GEMM's epilogue)",
            "sync": {"after_backward_ms": out["mxfp4"]["ms_per_step"], "sent_under_backward_ms": sec * 1e3,
                     "buckets": len(t.parts), "loss": loss}}
     if world == 1:
