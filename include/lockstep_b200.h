@@ -81,6 +81,10 @@ int ls_quantize_mxfp4_t(const void *x, int x_dtype, int64_t R, int64_t C, int ro
  * act = 0 is ls_quantize_mxfp4_t.  No single lockstep function does this. */
 int ls_quantize_mxfp4_t_act(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, int act,
                             uint8_t *packed, float *scale, uint8_t *sf, void *stream);
+/* Likewise ls_quantize_mxfp4_both of act(x): both orientations of GELU(x) from one read of x. */
+int ls_quantize_mxfp4_both_act(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, int act,
+                               uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
+                               void *stream);
 
 /* Both orientations of one tensor from one read of x [R, C]: what
  * ls_quantize_mxfp4 (packed + scale-factor bytes of x, blocks along C) and

@@ -818,12 +818,25 @@ extern "C" int ls_quantize_mxfp4_t_act(const void *x, int x_dtype, int64_t R, in
     return quantize_t_impl(x, x_dtype, R, C, rounding, packed, scale, sf, nullptr, nullptr, stream, act);
 }
 
-extern "C" int ls_quantize_mxfp4_both(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
-                                      uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
-                                      void *stream)
+static int quantize_both_impl(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, int act,
+                              uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf, void *stream)
 {
     if (C % 128 != 0) return fail(LS_EINVAL, "C=%lld must be a multiple of 128", (long long)C);
     if (!row_packed || !row_sf || !t_packed || !t_sf) return fail(LS_EINVAL, "null output");
     if (!aligned16(row_packed)) return fail(LS_EALIGN, "row_packed must be 16-byte aligned");
-    return quantize_t_impl(x, x_dtype, R, C, rounding, t_packed, nullptr, t_sf, row_packed, row_sf, stream);
+    return quantize_t_impl(x, x_dtype, R, C, rounding, t_packed, nullptr, t_sf, row_packed, row_sf, stream, act);
+}
+
+extern "C" int ls_quantize_mxfp4_both(const void *x, int x_dtype, int64_t R, int64_t C, int rounding,
+                                      uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
+                                      void *stream)
+{
+    return quantize_both_impl(x, x_dtype, R, C, rounding, 0, row_packed, row_sf, t_packed, t_sf, stream);
+}
+
+extern "C" int ls_quantize_mxfp4_both_act(const void *x, int x_dtype, int64_t R, int64_t C, int rounding, int act,
+                                          uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
+                                          void *stream)
+{
+    return quantize_both_impl(x, x_dtype, R, C, rounding, act, row_packed, row_sf, t_packed, t_sf, stream);
 }

@@ -116,11 +116,13 @@ def quantize_mxfp4_packed_t_gelu(x: torch.Tensor, rounding: str = "ref"):
     return packed, sf
 
 
-def quantize_mxfp4_both(x: torch.Tensor, rounding: str = "ref"):
+def quantize_mxfp4_both(x: torch.Tensor, rounding: str = "ref", act=None):
     """(extension) quantize_mxfp4_packed(x) and quantize_mxfp4_packed_t(x) from one read
-    of x [R, C]: returns (packed, sf, packed_t, sf_t).  R % 128 == 0 and C % 128 == 0."""
+    of x [R, C]: returns (packed, sf, packed_t, sf_t).  R % 128 == 0 and C % 128 == 0.
+    act="gelu" (bf16 x) quantizes gelu(x) instead, without the elementwise pass."""
     need_cuda(x)
     assert x.dim() == 2 and x.shape[0] % 128 == 0 and x.shape[1] % 128 == 0, "both dimensions must be multiples of 128"
+    assert act in (None, "gelu") and (act is None or x.dtype == torch.bfloat16)
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.float()
     x = aligned(x)
@@ -129,8 +131,8 @@ def quantize_mxfp4_both(x: torch.Tensor, rounding: str = "ref"):
     sf = torch.empty(sf_bytes(R, C), dtype=torch.uint8, device=x.device)
     packed_t = torch.empty((C, R // 2), dtype=torch.uint8, device=x.device)
     sf_t = torch.empty(sf_bytes(C, R), dtype=torch.uint8, device=x.device)
-    check(lib().ls_quantize_mxfp4_both(ptr(x), _lib.dtype_code(x.dtype), R, C, _ROUNDING[rounding],
-                                       ptr(packed), ptr(sf), ptr(packed_t), ptr(sf_t), stream()))
+    check(lib().ls_quantize_mxfp4_both_act(ptr(x), _lib.dtype_code(x.dtype), R, C, _ROUNDING[rounding], 1 if act else 0,
+                                           ptr(packed), ptr(sf), ptr(packed_t), ptr(sf_t), stream()))
     return packed, sf, packed_t, sf_t
 
 

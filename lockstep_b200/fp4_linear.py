@@ -121,77 +121,64 @@ FP4Linear = MXFP4Linear
 
 class _MXFP4MLP(torch.autograd.Function):
     """out(gelu(fc(x))) of lockstep's block (train.py:53, two _MXFP4Matmul around F.gelu) with
-    the activation kept in MXFP4 between the two GEMMs: the first GEMM's epilogue applies GELU
-    and emits the packed codes and scale bytes the second GEMM reads, so neither gelu(fc(x))
-    nor a quantize pass over it touches HBM.  The pre-activation is written (bf16) because
-    the backward pass needs it; the activation itself is recomputed there (straight-through
-    mode) or quantized transposed straight from the pre-activation (MXFP4 mode)."""
+    MXFP4 backward GEMMs and the activation never written to HBM: the quantizer of the second
+    GEMM's input applies GELU to the first GEMM's output as it reads it and emits both
+    orientations (rows for the forward product, columns for the weight gradient), so the
+    elementwise GELU pass and the tensor it would produce disappear.  The backward pass takes
+    GELU's derivative from the saved pre-activation.
+    (Doing the GELU and the quantization in the first GEMM's epilogue instead --
+    mxfp4_gemm_packed_quant -- was measured slower inside a training step: with K = 1024 that
+    GEMM is bound by its epilogue already, and erf for 67 M outputs on eight epilogue warps
+    per SM costs more than a bandwidth-bound pass with full occupancy.)"""
 
     @staticmethod
-    def forward(ctx, x, w1, w2, backward_mode):
+    def forward(ctx, x, w1, w2):
         k = _need_kernel()
-        mx = backward_mode == "mxfp4" and any(ctx.needs_input_grad[:3])
-        ctx.mx = mx
-        if mx:
-            (px, sx), (pxt, sxt) = _quant_both(x)
-            (pw1, sw1), (pw1t, sw1t) = _quant_both(w1)
-            (pw2, sw2), (pw2t, sw2t) = _quant_both(w2)
+        (px, sx), (pxt, sxt) = _quant_both(x)
+        (pw1, sw1), (pw1t, sw1t) = _quant_both(w1)
+        (pw2, sw2), (pw2t, sw2t) = _quant_both(w2)
+        c = k(px, pw1, sx, sw1, out_dtype=x.dtype)                # pre-activation [T, H]
+        if c.dtype == torch.bfloat16 and c.shape[0] % 128 == 0 and c.shape[1] % 128 == 0:
+            ph, sh, pht, sht = fp4.quantize_mxfp4_both(c, act="gelu")
         else:
-            px, sx = fp4.quantize_mxfp4_packed(x)
-            pw1, sw1 = fp4.quantize_mxfp4_packed(w1)
-            pw2, sw2 = fp4.quantize_mxfp4_packed(w2)
-        c, hq, hsf = mxfp4_gemm.mxfp4_gemm_packed_quant(px, pw1, sx, sw1, out_dtype=x.dtype, act="gelu")
-        y = k(hq, pw2, hsf, sw2, out_dtype=x.dtype)
-        if mx:
-            ctx.save_for_backward(pxt, sxt, pw1t, sw1t, pw2t, sw2t, c)
-            ctx.dtypes = (x.dtype, w1.dtype, w2.dtype)
-        else:
-            ctx.save_for_backward(x, w1, w2, c)
+            (ph, sh), (pht, sht) = _quant_both(torch.nn.functional.gelu(c))
+        y = k(ph, pw2, sh, sw2, out_dtype=x.dtype)
+        ctx.save_for_backward(pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c)
+        ctx.dtypes = (x.dtype, w1.dtype, w2.dtype)
         return y
 
     @staticmethod
     def backward(ctx, gy):
-        gelu_backward = torch.ops.aten.gelu_backward
-        if not ctx.mx:                                            # fp4_linear.py:42-45 twice, around gelu's backward
-            x, w1, w2, c = ctx.saved_tensors
-            h = torch.nn.functional.gelu(c)
-            gh = gy @ w2.to(gy.dtype)
-            gw2 = (gy.t() @ h.to(gy.dtype)).to(w2.dtype)
-            gc = gelu_backward(gh.to(c.dtype), c)
-            gx = (gc @ w1.to(gc.dtype)).to(x.dtype)
-            gw1 = (gc.t() @ x.to(gc.dtype)).to(w1.dtype)
-            return gx, gw1, gw2, None
         k = _need_kernel()
-        pxt, sxt, pw1t, sw1t, pw2t, sw2t, c = ctx.saved_tensors
+        pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c = ctx.saved_tensors
         x_dtype, w1_dtype, w2_dtype = ctx.dtypes
         (pg, sg), (pgt, sgt) = _quant_both(gy.contiguous())
-        gh = k(pg, pw2t, sg, sw2t, out_dtype=x_dtype)             # [T, 4D], contract over D
-        if c.dtype == torch.bfloat16 and c.shape[0] % 128 == 0:
-            pht, sht = fp4.quantize_mxfp4_packed_t_gelu(c)        # gelu(c).T along tokens, no pass over gelu(c)
-        else:
-            pht, sht = _quant_t(torch.nn.functional.gelu(c))
-        gw2 = k(pgt, pht, sgt, sht, out_dtype=torch.float32)      # [D, 4D], contract over tokens
-        gc = gelu_backward(gh, c)
+        gh = k(pg, pw2t, sg, sw2t, out_dtype=x_dtype)             # [T, H], contract over the output width
+        gw2 = k(pgt, pht, sgt, sht, out_dtype=torch.float32)      # [D, H], contract over tokens
+        gc = torch.ops.aten.gelu_backward(gh, c)
         (pgc, sgc), (pgct, sgct) = _quant_both(gc)
-        gx = k(pgc, pw1t, sgc, sw1t, out_dtype=x_dtype)           # [T, D], contract over 4D
-        gw1 = k(pgct, pxt, sgct, sxt, out_dtype=torch.float32)    # [4D, D], contract over tokens
-        return gx, gw1.to(w1_dtype), gw2.to(w2_dtype), None
+        gx = k(pgc, pw1t, sgc, sw1t, out_dtype=x_dtype)           # [T, D], contract over H
+        gw1 = k(pgct, pxt, sgct, sxt, out_dtype=torch.float32)    # [H, D], contract over tokens
+        return gx, gw1.to(w1_dtype), gw2.to(w2_dtype)
 
 
 class MXFP4MLP(nn.Module):
-    """(extension) The feed-forward half of a block, out(gelu(fc(x))), with both projections
-    in MXFP4 and the activation quantized in the first GEMM's epilogue.  `fc` and `out` are
-    ordinary MXFP4Linear modules (same parameters as the unfused form)."""
+    """(extension) The feed-forward half of a block, out(gelu(fc(x))).  With backward="mxfp4"
+    the activation stays in MXFP4 between the two GEMMs and is never written to HBM (see
+    _MXFP4MLP); with backward="ste" the reference's straight-through backward needs the
+    activation in bf16 anyway, so the module is the plain composition.  `fc` and `out` are
+    ordinary MXFP4Linear modules (same parameters either way)."""
 
     def __init__(self, width, hidden, backward="ste"):
         super().__init__()
-        assert hidden % 128 == 0, "the quantizing epilogue needs a hidden width that is a multiple of 128"
         self.fc = MXFP4Linear(width, hidden, backward=backward)
         self.out = MXFP4Linear(hidden, width, backward=backward)
         self.backward_mode = backward
 
     def forward(self, x):
+        if self.backward_mode != "mxfp4" or not torch.is_grad_enabled():
+            return self.out(torch.nn.functional.gelu(self.fc(x)))
         dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
         with torch.autocast("cuda", enabled=False):
-            y = _MXFP4MLP.apply(x.reshape(-1, x.shape[-1]).to(dt), self.fc.weight, self.out.weight, self.backward_mode)
+            y = _MXFP4MLP.apply(x.reshape(-1, x.shape[-1]).to(dt), self.fc.weight, self.out.weight)
         return y.view(*x.shape[:-1], -1)

@@ -57,7 +57,7 @@ class FeedForward(nn.Module):
 
 def make_mlp(kind, fused):
     """The feed-forward half of a block: two linears around GELU, or (fused) the MXFP4 module
-    that quantizes the activation in the first GEMM's epilogue.  Parameter names are the same."""
+    that keeps the activation in MXFP4 between its two GEMMs.  Parameter names are the same."""
     from lockstep_b200 import fp4_linear
     if fused and kind != "dense":
         return lambda width: fp4_linear.MXFP4MLP(width, 4 * width, backward=kind)
@@ -235,7 +235,8 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
     res = {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 per rank vocab32000, bf16 autocast, fused AdamW, "
                     "synthetic ids seeded by rank; gradients in one flat fp32 buffer averaged by Wire('mxfp4ef') every step",
            "block_linears": out,
-           "fused_mlp": "ste / mxfp4: the feed-forward half is fp4_linear.MXFP4MLP (GELU + quantize in the first GEMM's epilogue)",
+           "fused_mlp": "mxfp4: the feed-forward half is fp4_linear.MXFP4MLP (GELU applied inside the quantizer of the second "
+                        "GEMM's input; the activation never exists in HBM)",
            "sync": {"after_backward_ms": out["mxfp4"]["ms_per_step"], "sent_under_backward_ms": sec * 1e3,
                     "buckets": len(t.parts), "loss": loss}}
     if world == 1:
