@@ -86,6 +86,18 @@ int ls_quantize_mxfp4_both_act(const void *x, int x_dtype, int64_t R, int64_t C,
                                uint8_t *row_packed, uint8_t *row_sf, uint8_t *t_packed, uint8_t *t_sf,
                                void *stream);
 
+/* LayerNorm over the last dimension fused with ls_quantize_mxfp4 of its output: the input of
+ * the qkv and fc projections of lockstep's block (train.py:50,53: linear(ln(x))) in one pass.
+ *   x       [rows, D] LS_F32 or LS_BF16;  gamma, beta [D] fp32 (NULL: 1 and 0)
+ *   y_bf16  [rows, D] the normalized rows rounded to bf16 (what the backward pass needs), or NULL
+ *   packed  [rows, D/2], sf: MXFP4 of exactly those bf16 values (block 32, reference rounding)
+ *   mean, rstd [rows] fp32 statistics for LayerNorm's backward, or NULL
+ * D % 256 == 0, D <= 8192.  LayerNorm is computed in fp32 (as torch does under autocast).
+ * No single lockstep function does this. */
+int ls_layernorm_quantize(const void *x, int x_dtype, const float *gamma, const float *beta, float eps,
+                          int64_t rows, int64_t D, void *y_bf16, uint8_t *packed, uint8_t *sf, float *mean,
+                          float *rstd, void *stream);
+
 /* Both orientations of one tensor from one read of x [R, C]: what
  * ls_quantize_mxfp4 (packed + scale-factor bytes of x, blocks along C) and
  * ls_quantize_mxfp4_t (of x^T, blocks along R) would write.  For a linear layer

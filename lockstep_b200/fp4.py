@@ -102,6 +102,27 @@ def quantize_mxfp4_packed_t(x: torch.Tensor, rounding: str = "ref", want_scale: 
     return (packed, sf, scale) if want_scale else (packed, sf)
 
 
+def layernorm_quantize(x: torch.Tensor, weight, bias, eps: float = 1e-5):
+    """(extension) layer_norm(x) over the last dim, rounded to bf16, and its MXFP4 form in one
+    pass.  x [rows, D] fp32 or bf16; returns (y bf16 [rows, D], packed [rows, D // 2], sf,
+    mean [rows], rstd [rows]).  D % 256 == 0 and D <= 8192."""
+    need_cuda(x)
+    assert x.dim() == 2 and x.dtype in (torch.float32, torch.bfloat16)
+    rows, D = x.shape
+    assert D % 256 == 0 and D <= 8192, "D must be a multiple of 256, at most 8192"
+    x = aligned(x)
+    w = None if weight is None else aligned(weight.float())
+    b = None if bias is None else aligned(bias.float())
+    y = torch.empty((rows, D), dtype=torch.bfloat16, device=x.device)
+    packed = torch.empty((rows, D // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty(sf_bytes(rows, D), dtype=torch.uint8, device=x.device)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    check(lib().ls_layernorm_quantize(ptr(x), _lib.dtype_code(x.dtype), ptr(w), ptr(b), float(eps), rows, D,
+                                      ptr(y), ptr(packed), ptr(sf), ptr(mean), ptr(rstd), stream()))
+    return y, packed, sf, mean, rstd
+
+
 def quantize_mxfp4_packed_t_gelu(x: torch.Tensor, rounding: str = "ref"):
     """(extension) quantize_mxfp4_packed_t(gelu(x)) for bf16 x [R, C] without the elementwise
     pass: the activation is applied to the tile inside the kernel.  R % 128 == 0."""

@@ -119,6 +119,77 @@ class MXFP4Linear(nn.Linear):
 FP4Linear = MXFP4Linear
 
 
+def _ln_backward(g_y, x, mean, rstd, gamma, beta):
+    """LayerNorm's backward from the statistics the fused forward kept (torch's kernel)."""
+    rows, D = x.shape
+    return torch.ops.aten.native_layer_norm_backward(g_y.to(x.dtype), x, [D], mean.view(rows, 1), rstd.view(rows, 1),
+                                                     gamma, beta, [True, gamma is not None, beta is not None])
+
+
+class _NormMatmul(torch.autograd.Function):
+    """linear(layer_norm(x)) (train.py:50: qkv(ln1(x))) with the normalization and the
+    quantization of its output in one kernel: the fp32 normalized tensor, its cast to bf16 and
+    the quantizer's read of it disappear; what remains of layer_norm(x) in HBM is the bf16
+    copy the backward pass needs."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, w, eps, backward_mode):
+        k = _need_kernel()
+        y, py, sy, mean, rstd = fp4.layernorm_quantize(x, gamma, beta, eps)
+        mx = backward_mode == "mxfp4" and any(ctx.needs_input_grad[:4])
+        ctx.mx = mx
+        if mx:
+            pyt, syt = _quant_t(y)
+            (pw, sw), (pwt, swt) = _quant_both(w)
+            ctx.save_for_backward(x, gamma, beta, mean, rstd, pyt, syt, pwt, swt)
+            ctx.w_dtype = w.dtype
+        else:
+            pw, sw = fp4.quantize_mxfp4_packed(w)
+            ctx.save_for_backward(x, gamma, beta, mean, rstd, y, w)
+        return k(py, pw, sy, sw, out_dtype=torch.bfloat16)
+
+    @staticmethod
+    def backward(ctx, gy):
+        if not ctx.mx:
+            x, gamma, beta, mean, rstd, y, w = ctx.saved_tensors
+            g_y = gy @ w.to(gy.dtype)
+            gw = (gy.t() @ y.to(gy.dtype)).to(w.dtype)
+        else:
+            k = _need_kernel()
+            x, gamma, beta, mean, rstd, pyt, syt, pwt, swt = ctx.saved_tensors
+            (pg, sg), (pgt, sgt) = _quant_both(gy.contiguous())
+            g_y = k(pg, pwt, sg, swt, out_dtype=torch.bfloat16)
+            gw = k(pgt, pyt, sgt, syt, out_dtype=torch.float32).to(ctx.w_dtype)
+        gx, ggamma, gbeta = _ln_backward(g_y, x, mean, rstd, gamma, beta)
+        return gx, ggamma, gbeta, gw, None, None
+
+
+def _fusable_norm(x, width):
+    """The fused LayerNorm + quantize kernel rounds the normalized rows to bf16: it stands in
+    for layer_norm + cast exactly when the projection would run in bf16 (autocast)."""
+    return (x.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+            and x.dtype in (torch.float32, torch.bfloat16) and width % 256 == 0 and width <= 8192)
+
+
+class MXFP4NormLinear(nn.Module):
+    """(extension) linear(layer_norm(x)) with both in this library: `norm` is an ordinary
+    nn.LayerNorm, `linear` an ordinary MXFP4Linear (same parameters as the unfused pair)."""
+
+    def __init__(self, width, out_features, backward="ste", eps=1e-5):
+        super().__init__()
+        self.norm = nn.LayerNorm(width, eps=eps)
+        self.linear = MXFP4Linear(width, out_features, backward=backward)
+
+    def forward(self, x):
+        width = x.shape[-1]
+        if not _fusable_norm(x, width):
+            return self.linear(self.norm(x))
+        with torch.autocast("cuda", enabled=False):
+            y = _NormMatmul.apply(x.reshape(-1, width).contiguous(), self.norm.weight, self.norm.bias, self.linear.weight,
+                                  self.norm.eps, self.linear.backward_mode)
+        return y.view(*x.shape[:-1], -1)
+
+
 class _MXFP4MLP(torch.autograd.Function):
     """out(gelu(fc(x))) of lockstep's block (train.py:53, two _MXFP4Matmul around F.gelu) with
     MXFP4 backward GEMMs and the activation never written to HBM: the quantizer of the second
@@ -132,9 +203,15 @@ class _MXFP4MLP(torch.autograd.Function):
     per SM costs more than a bandwidth-bound pass with full occupancy.)"""
 
     @staticmethod
-    def forward(ctx, x, w1, w2):
+    def forward(ctx, x, w1, w2, gamma=None, beta=None, eps=None):
         k = _need_kernel()
-        (px, sx), (pxt, sxt) = _quant_both(x)
+        ctx.normed = eps is not None
+        if ctx.normed:                                            # out(gelu(fc(layer_norm(x)))): see _NormMatmul
+            xin = x
+            x, px, sx, mean, rstd = fp4.layernorm_quantize(xin, gamma, beta, eps)
+            pxt, sxt = _quant_t(x)
+        else:
+            (px, sx), (pxt, sxt) = _quant_both(x)
         (pw1, sw1), (pw1t, sw1t) = _quant_both(w1)
         (pw2, sw2), (pw2t, sw2t) = _quant_both(w2)
         c = k(px, pw1, sx, sw1, out_dtype=x.dtype)                # pre-activation [T, H]
@@ -143,14 +220,17 @@ class _MXFP4MLP(torch.autograd.Function):
         else:
             (ph, sh), (pht, sht) = _quant_both(torch.nn.functional.gelu(c))
         y = k(ph, pw2, sh, sw2, out_dtype=x.dtype)
-        ctx.save_for_backward(pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c)
+        if ctx.normed:
+            ctx.save_for_backward(pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c, xin, gamma, beta, mean, rstd)
+        else:
+            ctx.save_for_backward(pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c)
         ctx.dtypes = (x.dtype, w1.dtype, w2.dtype)
         return y
 
     @staticmethod
     def backward(ctx, gy):
         k = _need_kernel()
-        pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c = ctx.saved_tensors
+        pxt, sxt, pw1t, sw1t, pw2t, sw2t, pht, sht, c = ctx.saved_tensors[:9]
         x_dtype, w1_dtype, w2_dtype = ctx.dtypes
         (pg, sg), (pgt, sgt) = _quant_both(gy.contiguous())
         gh = k(pg, pw2t, sg, sw2t, out_dtype=x_dtype)             # [T, H], contract over the output width
@@ -159,7 +239,11 @@ class _MXFP4MLP(torch.autograd.Function):
         (pgc, sgc), (pgct, sgct) = _quant_both(gc)
         gx = k(pgc, pw1t, sgc, sw1t, out_dtype=x_dtype)           # [T, D], contract over H
         gw1 = k(pgct, pxt, sgct, sxt, out_dtype=torch.float32)    # [H, D], contract over tokens
-        return gx, gw1.to(w1_dtype), gw2.to(w2_dtype)
+        if not ctx.normed:
+            return gx, gw1.to(w1_dtype), gw2.to(w2_dtype)
+        xin, gamma, beta, mean, rstd = ctx.saved_tensors[9:]
+        gxin, ggamma, gbeta = _ln_backward(gx, xin, mean, rstd, gamma, beta)
+        return gxin, gw1.to(w1_dtype), gw2.to(w2_dtype), ggamma, gbeta, None
 
 
 class MXFP4MLP(nn.Module):
@@ -169,16 +253,30 @@ class MXFP4MLP(nn.Module):
     activation in bf16 anyway, so the module is the plain composition.  `fc` and `out` are
     ordinary MXFP4Linear modules (same parameters either way)."""
 
-    def __init__(self, width, hidden, backward="ste"):
+    def __init__(self, width, hidden, backward="ste", norm=False, eps=1e-5):
         super().__init__()
+        self.norm = nn.LayerNorm(width, eps=eps) if norm else None     # norm=True: out(gelu(fc(layer_norm(x))))
         self.fc = MXFP4Linear(width, hidden, backward=backward)
         self.out = MXFP4Linear(hidden, width, backward=backward)
         self.backward_mode = backward
 
     def forward(self, x):
+        width = x.shape[-1]
         if self.backward_mode != "mxfp4" or not torch.is_grad_enabled():
-            return self.out(torch.nn.functional.gelu(self.fc(x)))
-        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+            if self.norm is not None and _fusable_norm(x, width):     # only the norm + quantize fusion applies
+                with torch.autocast("cuda", enabled=False):
+                    h = _NormMatmul.apply(x.reshape(-1, width).contiguous(), self.norm.weight, self.norm.bias,
+                                          self.fc.weight, self.norm.eps, self.backward_mode)
+                return self.out(torch.nn.functional.gelu(h)).view(*x.shape[:-1], -1)
+            h = x if self.norm is None else self.norm(x)
+            return self.out(torch.nn.functional.gelu(self.fc(h)))
+        if self.norm is not None and _fusable_norm(x, width):
+            with torch.autocast("cuda", enabled=False):
+                y = _MXFP4MLP.apply(x.reshape(-1, width).contiguous(), self.fc.weight, self.out.weight,
+                                    self.norm.weight, self.norm.bias, self.norm.eps)
+            return y.view(*x.shape[:-1], -1)
+        h = x if self.norm is None else self.norm(x)
+        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else h.dtype
         with torch.autocast("cuda", enabled=False):
-            y = _MXFP4MLP.apply(x.reshape(-1, x.shape[-1]).to(dt), self.fc.weight, self.out.weight)
+            y = _MXFP4MLP.apply(h.reshape(-1, width).to(dt), self.fc.weight, self.out.weight)
         return y.view(*x.shape[:-1], -1)

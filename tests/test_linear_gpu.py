@@ -137,3 +137,66 @@ def test_transposed_quantizer_with_gelu_equals_two_passes():
     got_p, got_sf = fp4.quantize_mxfp4_packed_t_gelu(c)
     differ = (got_p != want_p).float().mean().item()          # erf of this library against torch's kernel
     assert differ <= 1e-3, differ
+
+
+def test_layernorm_quantize_kernel_against_two_passes():
+    from lockstep_b200 import fp4
+    g = torch.Generator(device="cuda").manual_seed(12)
+    for dt, rows, D in ((torch.float32, 300, 1024), (torch.bfloat16, 129, 256), (torch.float32, 64, 4096)):
+        x = (torch.randn(rows, D, device="cuda", generator=g) * 3 + 0.5).to(dt)
+        gamma = torch.randn(D, device="cuda", generator=g) * 0.2 + 1
+        beta = torch.randn(D, device="cuda", generator=g) * 0.1
+        y, p, sf, mean, rstd = fp4.layernorm_quantize(x, gamma, beta, 1e-5)
+        ref = torch.nn.functional.layer_norm(x.float(), (D,), gamma, beta, 1e-5)
+        assert (y.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()      # bf16 rounding of the output
+        assert torch.allclose(mean, x.float().mean(1), atol=1e-5, rtol=1e-5)
+        assert torch.allclose(rstd, (x.float().var(1, unbiased=False) + 1e-5).rsqrt(), rtol=1e-4)
+        want_p, want_sf = fp4.quantize_mxfp4_packed(y)            # MXFP4 of exactly the bf16 rows it wrote
+        assert torch.equal(p, want_p)
+        valid = np.arange(rows)
+        pick = lambda t: t.cpu().numpy().reshape(-1, D // 128, 32, 4, 4)[valid // 128, :, valid % 32, (valid % 128) // 32]
+        assert np.array_equal(pick(sf), pick(want_sf))
+
+
+@pytest.mark.parametrize("mode", ["ste", "mxfp4"])
+def test_norm_fused_modules_match_the_unfused_composition(mode):
+    # linear(layer_norm(x)) and out(gelu(fc(layer_norm(x)))) with the norm fused into the quantizer,
+    # against nn.LayerNorm followed by the unfused modules, under bf16 autocast: outputs and gradients
+    from lockstep_b200 import fp4_linear
+    B, S, D = 4, 128, 256
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(B, S, D, device="cuda", generator=g)
+    gy = torch.randn(B, S, D, device="cuda", generator=g)
+    fused_l = fp4_linear.MXFP4NormLinear(D, 3 * D, backward=mode).cuda()
+    fused_m = fp4_linear.MXFP4MLP(D, 4 * D, backward=mode, norm=True).cuda()
+    norm_l, lin = torch.nn.LayerNorm(D).cuda(), fp4_linear.MXFP4Linear(D, 3 * D, backward=mode).cuda()
+    norm_m = torch.nn.LayerNorm(D).cuda()
+    fc, out = fp4_linear.MXFP4Linear(D, 4 * D, backward=mode).cuda(), fp4_linear.MXFP4Linear(4 * D, D, backward=mode).cuda()
+    with torch.no_grad():
+        for n in (fused_l.norm, fused_m.norm, norm_l, norm_m):
+            n.weight.copy_(torch.linspace(0.5, 1.5, D)), n.bias.copy_(torch.linspace(-0.1, 0.1, D))
+        lin.weight.copy_(fused_l.linear.weight), fc.weight.copy_(fused_m.fc.weight), out.weight.copy_(fused_m.out.weight)
+    tol = 2e-2 if mode == "mxfp4" else 5e-3
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    with torch.autocast("cuda", torch.bfloat16):
+        ya = fused_l(xa)
+        yb = lin(norm_l(xb))
+    assert ya.dtype == torch.bfloat16 and ya.shape == (B, S, 3 * D)
+    ya.float().backward(torch.cat([gy] * 3, -1))
+    yb.float().backward(torch.cat([gy] * 3, -1))
+    _close(ya, yb, "norm + linear forward", 2e-3)
+    _close(xa.grad, xb.grad, "norm + linear dX", tol)
+    _close(fused_l.linear.weight.grad, lin.weight.grad, "norm + linear dW", tol)
+    _close(fused_l.norm.weight.grad, norm_l.weight.grad, "norm + linear dgamma", tol)
+    _close(fused_l.norm.bias.grad, norm_l.bias.grad, "norm + linear dbeta", tol)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    with torch.autocast("cuda", torch.bfloat16):
+        ya = fused_m(xa)
+        yb = out(torch.nn.functional.gelu(fc(norm_m(xb))))
+    ya.float().backward(gy)
+    yb.float().backward(gy)
+    _close(ya, yb, "norm + mlp forward", 3e-3)
+    _close(xa.grad, xb.grad, "norm + mlp dX", tol)
+    _close(fused_m.fc.weight.grad, fc.weight.grad, "norm + mlp dW fc", tol)
+    _close(fused_m.out.weight.grad, out.weight.grad, "norm + mlp dW out", tol)
+    _close(fused_m.norm.weight.grad, norm_m.weight.grad, "norm + mlp dgamma", tol)

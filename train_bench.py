@@ -31,10 +31,13 @@ def make_linear(kind):
 
 
 class CausalSelfAttention(nn.Module):
-    def __init__(self, width, heads, linear):
+    """Pre-norm attention branch: proj(attention(qkv(norm(x)))).  `normed_qkv` builds the norm
+    and the qkv projection together (the fused LayerNorm + quantize module) or separately."""
+
+    def __init__(self, width, heads, linear, normed_qkv):
         super().__init__()
         self.heads = heads
-        self.qkv = linear(width, 3 * width)
+        self.qkv = normed_qkv(width, 3 * width)
         self.proj = linear(width, width)
 
     def forward(self, x):
@@ -43,6 +46,18 @@ class CausalSelfAttention(nn.Module):
         q, k, v = qkv.permute(2, 0, 3, 1, 4)                      # each [batch, heads, steps, head_dim]
         mixed = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return self.proj(mixed.transpose(1, 2).reshape(batch, steps, width))
+
+
+class NormThen(nn.Module):
+    """norm followed by a module: the unfused form of the fused norm + projection modules."""
+
+    def __init__(self, width, inner):
+        super().__init__()
+        self.norm = nn.LayerNorm(width)
+        self.inner = inner
+
+    def forward(self, x):
+        return self.inner(self.norm(x))
 
 
 class FeedForward(nn.Module):
@@ -55,35 +70,40 @@ class FeedForward(nn.Module):
         return self.out(F.gelu(self.fc(x)))
 
 
-def make_mlp(kind, fused):
-    """The feed-forward half of a block: two linears around GELU, or (fused) the MXFP4 module
-    that keeps the activation in MXFP4 between its two GEMMs.  Parameter names are the same."""
+def make_parts(kind, fused):
+    """(linear, normed_qkv, normed_mlp) factories for a block.  fused (MXFP4 kinds only): the
+    LayerNorm in front of qkv and fc is fused with the quantization of its output, and with
+    kind "mxfp4" the feed-forward half keeps its activation in MXFP4 between its two GEMMs."""
     from lockstep_b200 import fp4_linear
+    linear = make_linear(kind)
     if fused and kind != "dense":
-        return lambda width: fp4_linear.MXFP4MLP(width, 4 * width, backward=kind)
-    return lambda width: FeedForward(width, make_linear(kind))
+        return (linear,
+                lambda width, out: fp4_linear.MXFP4NormLinear(width, out, backward=kind),
+                lambda width: fp4_linear.MXFP4MLP(width, 4 * width, backward=kind, norm=True))
+    return (linear,
+            lambda width, out: NormThen(width, linear(width, out)),
+            lambda width: NormThen(width, FeedForward(width, linear)))
 
 
 class Block(nn.Module):
-    def __init__(self, width, heads, linear, mlp):
+    def __init__(self, width, heads, parts):
         super().__init__()
-        self.ln1 = nn.LayerNorm(width)
-        self.attn = CausalSelfAttention(width, heads, linear)
-        self.ln2 = nn.LayerNorm(width)
-        self.mlp = mlp(width)
+        linear, normed_qkv, normed_mlp = parts
+        self.attn = CausalSelfAttention(width, heads, linear, normed_qkv)
+        self.mlp = normed_mlp(width)
 
     def forward(self, x):
-        x = x + self.attn(self.ln1(x))
-        return x + self.mlp(self.ln2(x))
+        x = x + self.attn(x)
+        return x + self.mlp(x)
 
 
 class Decoder(nn.Module):
-    def __init__(self, layers, width, heads, context, vocab, linear, mlp):
+    def __init__(self, layers, width, heads, context, vocab, parts):
         super().__init__()
         self.vocab = vocab
         self.tokens = nn.Embedding(vocab, width)
         self.positions = nn.Embedding(context, width)
-        self.blocks = nn.ModuleList([Block(width, heads, linear, mlp) for _ in range(layers)])
+        self.blocks = nn.ModuleList([Block(width, heads, parts) for _ in range(layers)])
         self.norm = nn.LayerNorm(width)
         # N(0, 0.02) for every matrix; the two projections that write into the residual
         # stream are scaled down by sqrt(2 * layers), as train.py:66-69 does
@@ -91,7 +111,7 @@ class Decoder(nn.Module):
         for name, p in self.named_parameters():
             if p.dim() < 2:
                 continue
-            residual_writer = name.endswith("attn.proj.weight") or name.endswith("mlp.out.weight")
+            residual_writer = name.endswith("attn.proj.weight") or name.endswith("out.weight")
             nn.init.normal_(p, std=0.02 * (shrink if residual_writer else 1.0))
 
     def forward(self, ids, targets):
@@ -114,10 +134,10 @@ class Trainer:
     phases follow after the backward pass."""
 
     def __init__(self, kind="mxfp4", layers=12, width=1024, heads=16, context=1024, batch=16, vocab=32000,
-                 device="cuda", wire_method="mxfp4ef", world=1, rank=0, overlap=False, buckets=4, fused_mlp=True):
+                 device="cuda", wire_method="mxfp4ef", world=1, rank=0, overlap=False, buckets=4, fused=True):
         from lockstep_b200 import wire
         torch.manual_seed(0)
-        self.model = Decoder(layers, width, heads, context, vocab, make_linear(kind), make_mlp(kind, fused_mlp)).to(device)
+        self.model = Decoder(layers, width, heads, context, vocab, make_parts(kind, fused)).to(device)
         self.params = list(self.model.parameters())
         self.flat = torch.zeros(sum(p.numel() for p in self.params), device=device)
         at, spans = 0, []
@@ -219,11 +239,11 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
     with each kind of block projection (one rank only), and the step time with the gradient
     sync after the backward pass against the bucketed sync that sends under it."""
     out = {}
-    runs = (("dense", "dense", True), ("ste", "ste", True), ("mxfp4", "mxfp4", True),
-            ("mxfp4_unfused_mlp", "mxfp4", False)) if world == 1 else (("mxfp4", "mxfp4", True),)
+    runs = (("dense", "dense", False), ("ste", "ste", True), ("ste_unfused", "ste", False), ("mxfp4", "mxfp4", True),
+            ("mxfp4_unfused", "mxfp4", False)) if world == 1 else (("mxfp4", "mxfp4", True),)
     for name, kind, fused in runs:
         torch.cuda.empty_cache()
-        t = Trainer(kind, device=device, world=world, rank=rank, fused_mlp=fused)
+        t = Trainer(kind, device=device, world=world, rank=rank, fused=fused)
         sec, loss = t.time(steps, warmup)
         out[name] = {"tokens_per_s": world * t.tokens_per_step / sec, "ms_per_step": sec * 1e3, "loss": loss}
         t.close()
@@ -235,8 +255,10 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
     res = {"model": "decoder-only 12L d1024 h16 ffn4096 seq1024 batch16 per rank vocab32000, bf16 autocast, fused AdamW, "
                     "synthetic ids seeded by rank; gradients in one flat fp32 buffer averaged by Wire('mxfp4ef') every step",
            "block_linears": out,
-           "fused_mlp": "mxfp4: the feed-forward half is fp4_linear.MXFP4MLP (GELU applied inside the quantizer of the second "
-                        "GEMM's input; the activation never exists in HBM)",
+           "fused": "ste / mxfp4: LayerNorm fused with the quantization of its output in front of qkv and fc "
+                    "(fp4_linear.MXFP4NormLinear); mxfp4: the feed-forward half is fp4_linear.MXFP4MLP (GELU applied "
+                    "inside the quantizer of the second GEMM's input; the activation never exists in HBM); "
+                    "*_unfused: separate LayerNorm, GELU and quantizer passes",
            "sync": {"after_backward_ms": out["mxfp4"]["ms_per_step"], "sent_under_backward_ms": sec * 1e3,
                     "buckets": len(t.parts), "loss": loss}}
     if world == 1:
