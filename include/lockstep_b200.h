@@ -202,10 +202,11 @@ int ls_gemm_set_variant(int variant);
  * tensor pipe at the clock the power cap allows. */
 int ls_fp4_mma_peak(int rounds, double *flop_out, void *stream);
 
-/* Products of at most 128 rows are launched with programmatic stream
- * serialization (default on): the kernel's set-up overlaps the tail of the
- * kernel before it in the stream, and it waits for that kernel before its first
- * load.  0 switches this off (ordinary launches).  For measurements. */
+/* The GEMM kernels are launched with programmatic stream serialization (default
+ * on): a kernel's set-up overlaps the tail of the kernel before it in the
+ * stream (this library's quantizers release their dependents at once), and it
+ * waits for that kernel before its first load.  0 switches this off (ordinary
+ * launches).  For measurements. */
 int ls_gemm_set_pdl(int on);
 
 /* K-splitting of the two GEMM entry points: 0 = by shape (default: products of

@@ -578,6 +578,9 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
     cluster_sync();                                         // both CTAs' barriers exist before any remote arrive
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_p;
+    // programmatic dependent launch, as in the single-CTA kernel: the set-up above may have
+    // overlapped the tail of the kernel before this one (typically the quantizer of A)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (both CTAs)
@@ -592,6 +595,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             ptx::prefetch_tmap(&tm_b);
             ptx::prefetch_tmap(tsfa);
             ptx::prefetch_tmap(&tm_sfb);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -794,7 +798,7 @@ int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kby
     return LS_OK;
 }
 
-std::atomic<int> g_gemm_pdl{1};       // 1: the single-CTA kernel is launched with programmatic stream serialization
+std::atomic<int> g_gemm_pdl{1};       // 1: the GEMM kernels are launched with programmatic stream serialization
 
 template <int BN>
 int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
@@ -885,8 +889,16 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + C::BN - 1) / C::BN;
     int pairs = (p.nbatch == 2 ? m_tiles : (m_tiles + 1) / 2) * n_tiles * p.splits;
     int grid = 2 * (pairs < max_pairs ? pairs : max_pairs);
-    mxfp4_gemm_pair_kernel<<<grid, kPairThreads, C::SMEM, st>>>(ta0, ta1, tb, tsa0, tsa1, tsb, p);
-    LS_LAUNCH_CHECK("mxfp4_gemm_pair");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(grid), 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = g_gemm_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+    cfg.attrs = at, cfg.numAttrs = 1;
+    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_pair_kernel, ta0, ta1, tb, tsa0, tsa1, tsb, p));
     return LS_OK;
 }
 

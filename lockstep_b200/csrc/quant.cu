@@ -121,6 +121,9 @@ template <int BLOCK, bool RNE>
 __global__ void __launch_bounds__(kThreads)
 quantize_bf16_kernel(const uint8_t *__restrict__ x, uint32_t n16, QuantOut o)
 {
+    // lets a GEMM launched with programmatic stream serialization start its set-up under this
+    // kernel; that GEMM waits for this grid to finish before it loads anything (no-op otherwise)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = BLOCK / 16;                    // 2 or 1 lanes per block
     const uint32_t base = blockIdx.x * (kThreads * kUnroll16) + threadIdx.x;
     U8x32 v[kUnroll16];
@@ -197,6 +200,9 @@ template <int BLOCK, bool RNE>
 __global__ void __launch_bounds__(kThreads)
 quantize_f32_kernel(const uint8_t *__restrict__ x, uint32_t n8, QuantOut o)
 {
+    // lets a GEMM launched with programmatic stream serialization start its set-up under this
+    // kernel; that GEMM waits for this grid to finish before it loads anything (no-op otherwise)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int LPB = BLOCK / 8;
     constexpr int U = kUnroll / 2;
     const uint32_t base = blockIdx.x * (kThreads * U) + threadIdx.x;
@@ -260,6 +266,7 @@ quantize_t_kernel(const T *__restrict__ x, int64_t R, int64_t C, uint8_t *__rest
                   float *__restrict__ scale, uint8_t *__restrict__ sf, uint8_t *__restrict__ row_packed,
                   uint8_t *__restrict__ row_sf)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // see quantize_bf16_kernel
     // A tile sits in shared memory as rows of 16-byte chunks.  Row r is rotated by
     // 2 * (r / 32) + r % 8 chunks: the column reads below (4 row groups x 8 columns per
     // warp, all lanes at the same r % 8) and the row reads of the row-wise outputs (8
