@@ -56,6 +56,7 @@ _SIGS = {
                                         ctypes.POINTER(c_vp), c_int, c_vp]),
     "ls_wire_set_mode": (c_int, [c_vp, c_int, c_int, c_int]),
     "ls_wire_mode": (c_int, [c_vp]),
+    "ls_wire_set_dynamic": (c_int, [c_vp, c_int]),
     "ls_wire_set_timeout_us": (c_int, [c_vp, c_i64]),
     "ls_wire_poll_status": (c_int, [c_vp, c_vp]),
     "ls_wire_reset": (c_int, [c_vp]),

@@ -52,6 +52,8 @@ struct Header {                 // start of every rank's arena
     uint32_t rs_flag[kMaxSub][kMaxWorld];       // epoch of the last completed send of sub-range c from rank s
     uint32_t ag_flag[kMaxSub][kMaxWorld];       // epoch of the last completed reduce of sub-range c by owner o
     uint32_t counter[kMaxSub][2];               // CTA completion counters (send, reduce)
+    uint32_t work[2][kMaxSub][3];               // next group of (sub-range, phase) to hand out; set epoch & 1 is in
+                                                // use, the other one is cleared for the next step
     uint32_t status;                // non-zero: a wait ran out
     uint32_t mx_flag[kMaxWorld];    // integer wires: epoch of rank s's last published chunk maxima
     uint32_t counter_mx;
@@ -76,6 +78,7 @@ struct WireGeom {
     uint64_t timeout_ns;            // how long a wait on a peer's flag may last
     uint32_t *host_status;          // mapped pinned host word of this rank: set to 1 when a wait ran out
     int bits;                       // 0: MXFP4 payload; 8 / 16: integer payload (wire.py's int8 / int16)
+    int dynamic;                    // 1: groups are handed out in chunks from a counter; 0: fixed shares per warp
     int64_t mx_off;                 // integer wires: [world][padded / 64] fp32 chunk maxima of every rank
 };
 
@@ -228,63 +231,72 @@ __device__ __forceinline__ void add_decoded8(uint32_t pk, uint32_t e8, float (&v
     for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], __fmul_rn(d[i], sc));
 }
 
-// ---- phase 1: sender ---------------------------------------------------------------
-// CTA `cta` of `ncta` encodes its share of sub-range `sub` of every owner's shard.
-template <int U>
-__device__ __forceinline__ void send_part(const float *g, int64_t n, float *res, const WireGeom &geo,
-                                          const Peers &peers, Sub sub, uint32_t cta, uint32_t ncta)
+// ---- work distribution -----------------------------------------------------------------
+// The groups of a part are handed out in chunks of kRows rows of 32 (one row = one group per
+// lane) from a counter in the rank's arena: a warp takes the next chunk when it is done with
+// its last.  Against a fixed share per thread this keeps every SM busy until the part ends,
+// whichever SMs the memory system happens to serve slower (a sender of 64 Mi elements:
+// 141 -> 134 us).  `total` is a multiple of 32, so rows are whole: body(base, rows, lane) is
+// called by all 32 lanes of the warp for `rows` rows starting at group `base`.
+constexpr uint32_t kRows = 8;
+
+template <class F>
+__device__ __forceinline__ void for_each_row(uint32_t total, uint32_t *work, uint32_t cta, uint32_t ncta, F body)
 {
-    const uint32_t stride = ncta * kThreads;
+    const uint32_t lane = threadIdx.x & 31;
+    if (!work) {                                    // fixed shares: warp w of CTA c takes rows c * 8 + w, + ncta * 8, ...
+        constexpr uint32_t kWarps = kThreads / 32;
+        for (uint32_t r = cta * kWarps + (threadIdx.x >> 5); r * 32u < total; r += ncta * kWarps) body(r * 32u, 1u, lane);
+        return;
+    }
+    for (;;) {
+        uint32_t base = 0;
+        if (lane == 0) base = atomicAdd(work, kRows * 32u);
+        base = __shfl_sync(0xFFFFFFFFu, base, 0);
+        if (base >= total) break;
+        const uint32_t rows = min(kRows, (total - base) / 32u);
+        body(base, rows, lane);
+    }
+}
+
+// ---- phase 1: sender ---------------------------------------------------------------
+// Position j of a sub-range's flat group index belongs to step i = j / count, and step i goes
+// to owner rank + 1 + i (this rank's own shard comes last).  A row of 32 never straddles two
+// owners (count is a multiple of 32).
+__device__ __forceinline__ void send_part(const float *g, int64_t n, float *res, const WireGeom &geo,
+                                          const Peers &peers, Sub sub, uint32_t *work, uint32_t cta, uint32_t ncta)
+{
     const uint32_t per_shard = uint32_t(geo.shard / 8);        // groups of 8 per shard: a multiple of 32
-    const uint32_t total = uint32_t(geo.world) * sub.count;
     const int64_t exp_off = geo.shard / 2;
     const bool first_of_block = (threadIdx.x & 3) == 0;
-    // One flat loop over the sub-range's groups of all owners: position j belongs to step
-    // i = j / count, and step i goes to owner rank + 1 + i (this rank's own shard comes last).
-    // A thread takes two positions per round, a grid stride apart, and issues the loads of
-    // both before it encodes either (U = 2), or one (U = 1, fewer registers).
-    uint32_t j = cta * kThreads + threadIdx.x;
-    uint32_t i = j / sub.count, k = j - i * sub.count;
-    for (; j < total; j += U * stride) {
-        uint32_t in_shard[U];
-        uint8_t *slot[U];
-        int64_t i0[U];
-        float v[U][8], r[U][8];
-        bool on[U];
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            on[u] = j + u * stride < total;                    // the same for every lane of a warp
-            while (k >= sub.count) k -= sub.count, i++;
+    for_each_row(uint32_t(geo.world) * sub.count, work, cta, ncta, [&](uint32_t base, uint32_t rows, uint32_t lane) {
+        for (uint32_t c = 0; c < rows; c++) {
+            const uint32_t row = base + 32u * c;
+            const uint32_t i = row / sub.count;                        // uniform over the warp
             uint32_t o = uint32_t(geo.rank) + 1u + i;
-            while (o >= uint32_t(geo.world)) o -= uint32_t(geo.world);
-            in_shard[u] = sub.first + k;
-            slot[u] = peers.arena[on[u] ? o : uint32_t(geo.rank)] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
-            i0[u] = (int64_t(o) * per_shard + in_shard[u]) * 8;
-            if (on[u]) {
-                load8v(g, i0[u], n, v[u]);
-                if (res) load8v(res, i0[u], geo.padded, r[u]);
-            }
-            k += stride;
-        }
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            if (!on[u]) break;
-            float dq[8];
+            if (o >= uint32_t(geo.world)) o -= uint32_t(geo.world);
+            const uint32_t in_shard = sub.first + (row - i * sub.count) + lane;
+            uint8_t *slot = peers.arena[o] + geo.rs_off + int64_t(geo.rank) * geo.slot_bytes;
+            const int64_t i0 = (int64_t(o) * per_shard + in_shard) * 8;
+            float v[8], dq[8];
+            load8v(g, i0, n, v);
             if (res) {
+                float r[8];
+                load8v(res, i0, geo.padded, r);
 #pragma unroll
-                for (int t = 0; t < 8; t++) v[u][t] = __fadd_rn(v[u][t], r[u][t]);
+                for (int t = 0; t < 8; t++) v[t] = __fadd_rn(v[t], r[t]);
             }
             uint32_t e8;
-            const uint32_t pk = encode8(v[u], e8, dq);
+            const uint32_t pk = encode8(v, e8, dq);
             if (res) {
 #pragma unroll
-                for (int t = 0; t < 8; t++) dq[t] = __fsub_rn(v[u][t], dq[t]);
-                store8v(res, i0[u], geo.padded, dq);
+                for (int t = 0; t < 8; t++) dq[t] = __fsub_rn(v[t], dq[t]);
+                store8v(res, i0, geo.padded, dq);
             }
-            reinterpret_cast<uint32_t *>(slot[u])[in_shard[u]] = pk;
-            if (first_of_block) slot[u][exp_off + in_shard[u] / 4] = uint8_t(e8);   // a warp's 8 exponent bytes are contiguous
+            reinterpret_cast<uint32_t *>(slot)[in_shard] = pk;
+            if (first_of_block) slot[exp_off + in_shard / 4] = uint8_t(e8);   // a warp's 8 exponent bytes are contiguous
         }
-    }
+    });
 }
 
 // ---- phase 2: owner ------------------------------------------------------------------
@@ -292,121 +304,127 @@ __device__ __forceinline__ void send_part(const float *g, int64_t n, float *res,
 // senders' slots are issued together before the first decode.  WORLD = 0: any size.
 template <int WORLD>
 __device__ __forceinline__ void reduce_part(float *ores, const WireGeom &geo, const Peers &peers, int reverse, Sub sub,
-                                            uint32_t cta, uint32_t ncta)
+                                            uint32_t *work, uint32_t cta, uint32_t ncta)
 {
     const int world = WORLD ? WORLD : geo.world;
-    const uint32_t end = sub.first + sub.count;
-    const uint32_t stride = ncta * kThreads;
     const uint8_t *rs = peers.arena[geo.rank] + geo.rs_off;
     const int64_t exp_off = geo.shard / 2;
     const bool first_of_block = (threadIdx.x & 3) == 0;
-    for (uint32_t g8 = sub.first + cta * kThreads + threadIdx.x; g8 < end; g8 += stride) {
-        float val[8], dq[8], r[8];
+    for_each_row(sub.count, work, cta, ncta, [&](uint32_t base, uint32_t rows, uint32_t lane) {
+        for (uint32_t c = 0; c < rows; c++) {
+            const uint32_t g8 = sub.first + base + 32u * c + lane;
+            float val[8], dq[8], r[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) val[i] = 0.0f;
-        if (ores) load8v(ores, int64_t(g8) * 8, geo.shard, r);
-        if (WORLD) {
-            constexpr int B = WORLD < 4 ? (WORLD ? WORLD : 1) : 4;     // senders whose loads are in flight together
+            for (int i = 0; i < 8; i++) val[i] = 0.0f;
+            if (ores) load8v(ores, int64_t(g8) * 8, geo.shard, r);
+            if (WORLD) {
+                constexpr int B = WORLD < 4 ? (WORLD ? WORLD : 1) : 4;     // senders whose loads are in flight together
 #pragma unroll
-            for (int t0 = 0; t0 < WORLD; t0 += B) {
-                uint32_t pk[B], eb[B];
+                for (int t0 = 0; t0 < WORLD; t0 += B) {
+                    uint32_t pk[B], eb[B];
 #pragma unroll
-                for (int t = 0; t < B; t++) {
-                    const uint8_t *slot = rs + int64_t(reverse ? WORLD - 1 - (t0 + t) : t0 + t) * geo.slot_bytes;
-                    pk[t] = reinterpret_cast<const uint32_t *>(slot)[g8];
-                    eb[t] = slot[exp_off + g8 / 4];
+                    for (int t = 0; t < B; t++) {
+                        const uint8_t *slot = rs + int64_t(reverse ? WORLD - 1 - (t0 + t) : t0 + t) * geo.slot_bytes;
+                        pk[t] = reinterpret_cast<const uint32_t *>(slot)[g8];
+                        eb[t] = slot[exp_off + g8 / 4];
+                    }
+#pragma unroll
+                    for (int t = 0; t < B; t++) add_decoded8(pk[t], eb[t], val);
                 }
-#pragma unroll
-                for (int t = 0; t < B; t++) add_decoded8(pk[t], eb[t], val);
+            } else {
+                for (int t = 0; t < world; t++) {
+                    const uint8_t *slot = rs + int64_t(reverse ? world - 1 - t : t) * geo.slot_bytes;
+                    add_decoded8(reinterpret_cast<const uint32_t *>(slot)[g8], slot[exp_off + g8 / 4], val);
+                }
             }
-        } else {
-            for (int t = 0; t < world; t++) {
-                const uint8_t *slot = rs + int64_t(reverse ? world - 1 - t : t) * geo.slot_bytes;
-                add_decoded8(reinterpret_cast<const uint32_t *>(slot)[g8], slot[exp_off + g8 / 4], val);
+            if (ores) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
+            }
+            uint32_t e8;
+            const uint32_t pk2 = encode8(val, e8, dq);
+            if (ores) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) dq[i] = __fsub_rn(val[i], dq[i]);
+                store8v(ores, int64_t(g8) * 8, geo.shard, dq);
+            }
+            // every rank's gather slot, starting at the right-hand neighbour
+#pragma unroll
+            for (int i = 0; i < (WORLD ? WORLD : kMaxWorld); i++) {
+                if (i >= world) break;
+                int p = geo.rank + 1 + i;
+                if (p >= world) p -= world;
+                uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
+                reinterpret_cast<uint32_t *>(slot)[g8] = pk2;
+                if (first_of_block) slot[exp_off + g8 / 4] = uint8_t(e8);
             }
         }
-        if (ores) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) val[i] = __fadd_rn(val[i], r[i]);
-        }
-        uint32_t e8;
-        const uint32_t pk2 = encode8(val, e8, dq);
-        if (ores) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) dq[i] = __fsub_rn(val[i], dq[i]);
-            store8v(ores, int64_t(g8) * 8, geo.shard, dq);
-        }
-        // every rank's gather slot, starting at the right-hand neighbour
-#pragma unroll
-        for (int i = 0; i < (WORLD ? WORLD : kMaxWorld); i++) {
-            if (i >= world) break;
-            int p = geo.rank + 1 + i;
-            if (p >= world) p -= world;
-            uint8_t *slot = peers.arena[p] + geo.ag_off + int64_t(geo.rank) * geo.slot_bytes;
-            reinterpret_cast<uint32_t *>(slot)[g8] = pk2;
-            if (first_of_block) slot[exp_off + g8 / 4] = uint8_t(e8);
-        }
-    }
+    });
 }
 
 __device__ __forceinline__ void reduce_any(float *ores, const WireGeom &geo, const Peers &peers, int reverse, Sub sub,
-                                           uint32_t cta, uint32_t ncta)
+                                           uint32_t *work, uint32_t cta, uint32_t ncta)
 {
     switch (geo.world) {
-    case 1: reduce_part<1>(ores, geo, peers, reverse, sub, cta, ncta); break;
-    case 2: reduce_part<2>(ores, geo, peers, reverse, sub, cta, ncta); break;
-    case 4: reduce_part<4>(ores, geo, peers, reverse, sub, cta, ncta); break;
-    case 8: reduce_part<8>(ores, geo, peers, reverse, sub, cta, ncta); break;
-    default: reduce_part<0>(ores, geo, peers, reverse, sub, cta, ncta); break;
+    case 1: reduce_part<1>(ores, geo, peers, reverse, sub, work, cta, ncta); break;
+    case 2: reduce_part<2>(ores, geo, peers, reverse, sub, work, cta, ncta); break;
+    case 4: reduce_part<4>(ores, geo, peers, reverse, sub, work, cta, ncta); break;
+    case 8: reduce_part<8>(ores, geo, peers, reverse, sub, work, cta, ncta); break;
+    default: reduce_part<0>(ores, geo, peers, reverse, sub, work, cta, ncta); break;
     }
 }
 
 // ---- phase 3: everyone ---------------------------------------------------------------
-// One thread decodes 8 values (one packed word) and writes one 32-byte word; U groups per
-// thread are in flight.  POW2: the world size is a power of two, so dividing by it is an
-// exact multiplication that folds into the block scale.  Otherwise an IEEE division
+// One thread decodes 8 values (one packed word) and writes one 32-byte word; the loads of
+// four rows are in flight together.  POW2: the world size is a power of two, so dividing by
+// it is an exact multiplication that folds into the block scale.  Otherwise an IEEE division
 // (wire.py:138 `.div_(world)`).
 template <bool POW2>
 __device__ __forceinline__ void finish_part(float *g, int64_t n, const WireGeom &geo, const Peers &peers, Sub sub,
-                                            uint32_t cta, uint32_t ncta)
+                                            uint32_t *work, uint32_t cta, uint32_t ncta)
 {
-    constexpr int U = 4;
+    constexpr uint32_t U = 4;
+    static_assert(kRows % U == 0, "rows are decoded four at a time");
     const uint8_t *my = peers.arena[geo.rank];
-    const uint32_t stride = ncta * kThreads;
-    const uint32_t end = sub.first + sub.count;
     const float w = float(geo.world), rw = 1.0f / w;
-    for (int o = 0; o < geo.world; o++) {
-        const uint8_t *slot = my + geo.ag_off + int64_t(o) * geo.slot_bytes;
-        const uint8_t *slot_e = slot + geo.shard / 2;
-        const int64_t first = int64_t(o) * geo.shard;
-        if (first >= n) break;
-        const int64_t left = (n - first + 7) / 8;               // groups of this shard that hold elements of g
-        const uint32_t count = left < int64_t(end) ? uint32_t(left) : end;
-        float *gs = g + first;
-        const int64_t ns = n - first;                           // elements of g in this shard and beyond
-        for (uint32_t q0 = sub.first + cta * kThreads + threadIdx.x; q0 < count; q0 += U * stride) {
-            uint32_t pk[U], e8[U];
+    const int64_t exp_off = geo.shard / 2;
+    for_each_row(uint32_t(geo.world) * sub.count, work, cta, ncta, [&](uint32_t base, uint32_t rows, uint32_t lane) {
+        for (uint32_t c0 = 0; c0 < rows; c0 += U) {
+            uint32_t pk[U], e8[U], q[U];
+            int o[U];
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const uint32_t q = q0 + u * stride;
-                const bool ok = q < count;
-                pk[u] = ok ? reinterpret_cast<const uint32_t *>(slot)[q] : 0u;
-                e8[u] = ok ? slot_e[q >> 2] : 127u;
+            for (uint32_t u = 0; u < U; u++) {
+                const uint32_t row = base + 32u * (c0 + u);
+                o[u] = int(row / sub.count);                            // owner of this row's shard
+                q[u] = sub.first + (row - uint32_t(o[u]) * sub.count) + lane;
+                const bool ok = c0 + u < rows && int64_t(o[u]) * geo.shard + int64_t(q[u]) * 8 < n;
+                const uint8_t *slot = my + geo.ag_off + int64_t(ok ? o[u] : 0) * geo.slot_bytes;
+                pk[u] = ok ? reinterpret_cast<const uint32_t *>(slot)[q[u]] : 0u;
+                e8[u] = ok ? slot[exp_off + (q[u] >> 2)] : 127u;
+                if (!ok) o[u] = -1;
             }
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const uint32_t q = q0 + u * stride;
-                if (q >= count) break;
+            for (uint32_t u = 0; u < U; u++) {
+                if (o[u] < 0) continue;
                 float sc = __uint_as_float(scale_bits(e8[u]));
                 if (POW2) sc = __fmul_rn(sc, rw);
                 float t[8];
                 e2m1x8_values(pk[u], t);
 #pragma unroll
                 for (int i = 0; i < 8; i++) t[i] = POW2 ? __fmul_rn(t[i], sc) : __fdiv_rn(__fmul_rn(t[i], sc), w);
-                store8v(gs, int64_t(q) * 8, ns, t);
+                const int64_t first = int64_t(o[u]) * geo.shard;
+                store8v(g + first, int64_t(q[u]) * 8, n - first, t);
             }
         }
-    }
+    });
+}
+
+// The first kernel of a step clears the work counters of the NEXT step (the other set): the
+// step before this one, which used them last, is complete on this GPU by stream order, and
+// no other GPU touches them.
+__device__ __forceinline__ void clear_next_work(Header *mine, uint32_t epoch, uint32_t cta)
+{
+    if (cta == 0 && threadIdx.x < kMaxSub * 3) (&mine->work[(epoch + 1) & 1][0][0])[threadIdx.x] = 0;
 }
 
 // ---- the three phases as separate launches ---------------------------------------------
@@ -414,8 +432,9 @@ __global__ void __launch_bounds__(kThreads, 5)
 wire_send_kernel(const float *g, int64_t n, float *res, const __grid_constant__ WireGeom geo,
                  const __grid_constant__ Peers peers, uint32_t epoch, Sub sub)
 {
-    send_part<1>(g, n, res, geo, peers, sub, blockIdx.x, gridDim.x);
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
+    clear_next_work(mine, epoch, blockIdx.x);
+    send_part(g, n, res, geo, peers, sub, geo.dynamic ? &mine->work[epoch & 1][sub.index][0] : nullptr, blockIdx.x, gridDim.x);
     signal_done(&mine->counter[sub.index][0], gridDim.x, peers, geo.world, geo.rank,
                 offsetof(Header, rs_flag) + sub.index * sizeof(mine->rs_flag[0]), epoch);
 }
@@ -426,7 +445,7 @@ wire_reduce_kernel(float *ores, const __grid_constant__ WireGeom geo, const __gr
 {
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
     if (!wait_flags(mine, mine->rs_flag[sub.index], geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
-    reduce_any(ores, geo, peers, reverse, sub, blockIdx.x, gridDim.x);
+    reduce_any(ores, geo, peers, reverse, sub, geo.dynamic ? &mine->work[epoch & 1][sub.index][1] : nullptr, blockIdx.x, gridDim.x);
     signal_done(&mine->counter[sub.index][1], gridDim.x, peers, geo.world, geo.rank,
                 offsetof(Header, ag_flag) + sub.index * sizeof(mine->ag_flag[0]), epoch);
 }
@@ -437,8 +456,9 @@ wire_finish_kernel(float *g, int64_t n, const __grid_constant__ WireGeom geo, co
 {
     Header *mine = reinterpret_cast<Header *>(peers.arena[geo.rank]);
     if (!wait_flags(mine, mine->ag_flag[sub.index], geo.world, epoch, geo.timeout_ns, geo.host_status)) return;
-    if ((geo.world & (geo.world - 1)) == 0) finish_part<true>(g, n, geo, peers, sub, blockIdx.x, gridDim.x);
-    else finish_part<false>(g, n, geo, peers, sub, blockIdx.x, gridDim.x);
+    uint32_t *work = geo.dynamic ? &mine->work[epoch & 1][sub.index][2] : nullptr;
+    if ((geo.world & (geo.world - 1)) == 0) finish_part<true>(g, n, geo, peers, sub, work, blockIdx.x, gridDim.x);
+    else finish_part<false>(g, n, geo, peers, sub, work, blockIdx.x, gridDim.x);
 }
 
 // ---- one cooperative launch ---------------------------------------------------------
@@ -474,13 +494,14 @@ wire_fused_kernel(const __grid_constant__ FusedArgs a)
     // a third of the CTAs starts each step with the send, a third with the owner's part and a
     // third with the decode, which keeps the HBM-bound and the link-bound work mixed on every SM.
     const int rot = a.stagger ? int(cta % 3u) : 0;
+    clear_next_work(mine, ra.epoch, cta);
     bool alive = true;
     for (int t = 0; t < S + 2 && alive; t++) {
         for (int q = 0; q < 3 && alive; q++) {
             const int item = (q + rot) % 3;
             if (item == 0 && t < S) {
                 const Sub sub{t, uint32_t(t) * per, per};
-                send_part<1>(ra.g, ra.n, ra.res, geo, ra.peers, sub, cta, ncta);
+                send_part(ra.g, ra.n, ra.res, geo, ra.peers, sub, geo.dynamic ? &mine->work[ra.epoch & 1][t][0] : nullptr, cta, ncta);
                 signal_done(&mine->counter[t][0], ncta, ra.peers, geo.world, geo.rank,
                             offsetof(Header, rs_flag) + t * sizeof(mine->rs_flag[0]), ra.epoch);
             } else if (item == 1 && t >= 1 && t - 1 < S) {
@@ -488,7 +509,7 @@ wire_fused_kernel(const __grid_constant__ FusedArgs a)
                 const Sub sub{c, uint32_t(c) * per, per};
                 alive = wait_flags(mine, mine->rs_flag[c], geo.world, ra.epoch, geo.timeout_ns, geo.host_status);
                 if (alive) {
-                    reduce_part<WORLD>(ra.ores, geo, ra.peers, a.reverse, sub, cta, ncta);
+                    reduce_part<WORLD>(ra.ores, geo, ra.peers, a.reverse, sub, geo.dynamic ? &mine->work[ra.epoch & 1][c][1] : nullptr, cta, ncta);
                     signal_done(&mine->counter[c][1], ncta, ra.peers, geo.world, geo.rank,
                                 offsetof(Header, ag_flag) + c * sizeof(mine->ag_flag[0]), ra.epoch);
                 }
@@ -497,8 +518,9 @@ wire_fused_kernel(const __grid_constant__ FusedArgs a)
                 const Sub sub{c, uint32_t(c) * per, per};
                 alive = wait_flags(mine, mine->ag_flag[c], geo.world, ra.epoch, geo.timeout_ns, geo.host_status);
                 if (alive) {
-                    if (pow2) finish_part<true>(ra.g, ra.n, geo, ra.peers, sub, cta, ncta);
-                    else finish_part<false>(ra.g, ra.n, geo, ra.peers, sub, cta, ncta);
+                    uint32_t *work = geo.dynamic ? &mine->work[ra.epoch & 1][c][2] : nullptr;
+                    if (pow2) finish_part<true>(ra.g, ra.n, geo, ra.peers, sub, work, cta, ncta);
+                    else finish_part<false>(ra.g, ra.n, geo, ra.peers, sub, work, cta, ncta);
                 }
             }
         }
@@ -782,6 +804,7 @@ static int wire_create(int rank, int world, int64_t padded, int bits, void **out
     w->g.ag_off = w->g.rs_off + w->g.slot_bytes * world;
     w->g.timeout_ns = kDefaultTimeoutNs;
     w->g.bits = bits;
+    w->g.dynamic = 0;
     w->g.mx_off = w->g.ag_off + w->g.slot_bytes * world;
     w->arena_bytes = size_t(w->g.mx_off + (bits ? int64_t(world) * (padded / kChunk) * 4 : 0));
     w->mapped = false;
@@ -1070,6 +1093,14 @@ extern "C" int ls_wire_int_allreduce(void *h, float *g, int64_t numel, float *re
 {
     for (int phase = 0; phase < 4; phase++)
         if (int rc = ls_wire_int_phase(h, phase, g, numel, res, ores, stream)) return rc;
+    return LS_OK;
+}
+
+extern "C" int ls_wire_set_dynamic(void *h, int on)
+{
+    Wire *w = as_wire(h);
+    if (!w) return fail(LS_EINVAL, "null wire handle");
+    w->g.dynamic = on ? 1 : 0;
     return LS_OK;
 }
 
