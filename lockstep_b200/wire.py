@@ -10,11 +10,11 @@
            sums in fp32 in ascending sender order, re-encodes, gathers
   mxfp4ef  mxfp4 with error feedback at sender and owner
 
-The MXFP4 wires run as three hand-written kernels per step that store the
-packed bytes straight into the owner's / every rank's memory over NVLink
-(`csrc/wire.cu`); the process group only carries the IPC handles at set-up.
-The reference's own methods keep their exact arithmetic, on the GPU, over
-torch.distributed collectives.  `Wire(method, numel, world, rank)(g)` averages
+The MXFP4 and integer wires run as hand-written kernels that store the packed
+bytes straight into the owner's / every rank's memory over NVLink
+(`csrc/wire.cu`: one cooperative launch per MXFP4 step by default, or one
+launch per phase); the process group only carries the IPC handles at set-up.
+fp32 and bf16 are torch.distributed all-reduces, as in the reference.  `Wire(method, numel, world, rank)(g)` averages
 the flat fp32 gradient `g` in place, as the reference does.
 """
 
