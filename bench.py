@@ -40,7 +40,6 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 M, N, K = 4096, 8192, 8192
-FLOPS_PER_STEP = 2 * 2 * M * N * K                      # two batches
 METRIC = "dual MXFP4 GEMM TFLOPS/GPU (% FP4 peak); FP4 all-reduce algbw GB/s @1/2/4/8"
 WORKLOAD = "dual-batch packed MXFP4 GEMM: 2 x [4096x8192 bf16, quantized on the fly] @ 8192x8192 MXFP4 W -> 2 x 4096x8192 bf16"
 FP4_SPEC_TFLOPS = 9000.0
@@ -626,7 +625,6 @@ def main():
 
     t = torch.tensor([step_ms, e2e_ms, sus_ms, copies.get("h2d_gbs", 0.0), copies.get("d2h_gbs", 0.0)],
                      device=dev, dtype=torch.float64)
-    tmin = t.clone()
     if world > 1:                                             # times: max over ranks; copy rates: sum over ranks
         tsum = t.clone()
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -361,3 +361,24 @@ def test_dependent_launch_chain_matches_ordinary_launches(mods):
     assert torch.equal(got, want) and torch.equal(replayed_chain, want)
     for a, b, c in zip(want_outs, got_outs, replayed):
         assert torch.equal(a, b) and torch.equal(a, c)
+
+
+def test_mma_only_ceiling_kernel_runs_and_counts_its_flops(mods):
+    # the measurement aid behind the benchmark's roofline peak: returns the FLOPs of the launch,
+    # finishes, and leaves the error word clean
+    import ctypes
+    from lockstep_b200 import _lib
+    L = _lib.lib()
+    flop = ctypes.c_double()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    _lib.check(L.ls_fp4_mma_peak(64, ctypes.byref(flop), _lib.stream()))
+    a.record()
+    _lib.check(L.ls_fp4_mma_peak(400, ctypes.byref(flop), _lib.stream()))
+    b.record()
+    torch.cuda.synchronize()
+    mods[1].gemm_status()
+    pairs = torch.cuda.get_device_properties(0).multi_processor_count // 2
+    assert flop.value == pairs * 400 * 4 * 2.0 * 256 * 256 * 64
+    tflops = flop.value / (a.elapsed_time(b) * 1e-3) / 1e12
+    assert 1000 < tflops < 9500, tflops                      # between a bf16-class rate and the dense FP4 spec
+    assert L.ls_fp4_mma_peak(0, None, None) < 0

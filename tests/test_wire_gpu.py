@@ -328,3 +328,19 @@ def test_wire_object_raises_on_the_call_after_a_time_out(wire):
         w(x)
     w._h = None
     grp.close()
+
+
+def test_phase_methods_equal_the_call(wire):
+    # Wire.send / reduce / finish (what a training loop uses to send under backward) against Wire.__call__
+    n = 300_000
+    g = torch.randn(n, generator=torch.Generator().manual_seed(9)) * 1e-2
+    a, b = wire.Wire("mxfp4ef", n), wire.Wire("mxfp4ef", n)
+    for step in range(3):
+        x, y = (g * (1 + step)).cuda(), (g * (1 + step)).cuda()
+        a(x)
+        b.send(y)
+        b.reduce()
+        b.finish(y)
+        assert torch.equal(x, y) and torch.equal(a.res, b.res) and torch.equal(a.ores, b.ores)
+    a.status(), b.status()
+    a.close(), b.close()
