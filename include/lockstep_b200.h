@@ -48,6 +48,9 @@ const char *ls_last_error(void);
  * [rows, K] operand quantized in blocks of 32: 512 bytes per 128 rows x 128
  * columns, rows rounded up to 128.  K must be a multiple of 128. */
 int64_t ls_sf_bytes(int64_t rows, int64_t K);
+/* The same for blocks of `block` = 32 or 16 elements: a 512-byte tile holds 128
+ * rows x 4 scales, so blocks of 16 take twice the bytes.  -1 for a bad argument. */
+int64_t ls_sf_bytes_block(int64_t rows, int64_t K, int block);
 
 /* Fused MXFP4 quantizer along the last dimension.
  * Replaces fp4.py:57-72 (quantize_mxfp4), :43-54 (_round_to_e2m1) and,
@@ -59,8 +62,8 @@ int64_t ls_sf_bytes(int64_t rows, int64_t K);
  *   packed   [rows, K/2] two codes per byte, even index in the low nibble
  *   scale    [rows, K/block] fp32 power of two 2^E
  *   e8m0     [rows, K/block] biased exponent E+127 (0xFF for a NaN block)
- *   sf       e8m0 bytes in the tcgen05 scale-factor layout (ls_sf_bytes);
- *            needs block == 32 and K % 128 == 0 */
+ *   sf       e8m0 bytes in the tcgen05 scale-factor layout
+ *            (ls_sf_bytes_block(rows, K, block)); needs K % 128 == 0 */
 int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int block,
                       int rounding, uint8_t *codes, uint8_t *packed, float *scale,
                       uint8_t *e8m0, uint8_t *sf, void *stream);
@@ -134,6 +137,9 @@ int ls_dequantize_mxfp4(const uint8_t *q, int is_packed, const float *scale,
  * two in [2^-127, 2^127]. */
 int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint8_t *sf, int32_t *bad,
                     void *stream);
+/* The same for scales [rows, K/block], block = 32 or 16. */
+int ls_scales_to_sf_block(const float *scale, int64_t rows, int64_t K, int block, uint8_t *sf,
+                          int32_t *bad, void *stream);
 
 /* Packed MXFP4 GEMM  C[M,N] = A[M,K] * W[N,K]^T  with fp32 accumulation.
  * Replaces mxfp4_gemm.py:161-174 (mxfp4_gemm_packed) and the kernel behind it
@@ -158,6 +164,19 @@ int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa,
 int ls_mxfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
                        const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
                        void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
+
+/* ls_mxfp4_gemm and ls_mxfp4_gemm_dual for operands quantized in blocks of 16
+ * (fp4.py:57, quantize_mxfp4(x, 16)): scale-factor buffers of
+ * ls_sf_bytes_block(rows, K, 16) bytes, everything else as above.  lockstep's own
+ * GEMM takes 32 values per scale only (mxfp4_gemm.py:136), so this form has no
+ * counterpart there; the tensor core takes it natively
+ * (tcgen05.mma.kind::mxf4nvf4.block_scale.block16 with UE8M0 scales). */
+int ls_mxfp4_gemm_block16(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa,
+                          const uint8_t *sfb, void *c, int out_dtype, int64_t M, int64_t N, int64_t K,
+                          void *stream);
+int ls_mxfp4_gemm_dual_block16(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
+                               const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
+                               void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 
 /* GEMM whose epilogue also emits MXFP4 of act(C) for a following MXFP4 GEMM
  * (scale blocks of 32 along N), so that C is not re-read by a quantize pass.

@@ -19,6 +19,7 @@ _SIGS = {
     "ls_version": (c_int, []),
     "ls_last_error": (ctypes.c_char_p, []),
     "ls_sf_bytes": (c_i64, [c_i64, c_i64]),
+    "ls_sf_bytes_block": (c_i64, [c_i64, c_i64, c_int]),
     "ls_quantize_mxfp4": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "ls_quantize_mxfp4_t": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp]),
     "ls_quantize_mxfp4_t_act": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp]),
@@ -31,6 +32,8 @@ _SIGS = {
     "ls_dequantize_mxfp4": (c_int, [c_vp, c_int, c_vp, c_vp, c_i64, c_i64, c_int, c_vp, c_int, c_vp]),
     "ls_mxfp4_gemm": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_mxfp4_gemm_dual": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
+    "ls_mxfp4_gemm_block16": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "ls_mxfp4_gemm_dual_block16": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_mxfp4_gemm_quant": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
     "ls_gemm_status": (c_int, [c_vp]),
     "ls_gemm_set_variant": (c_int, [c_int]),
@@ -62,6 +65,7 @@ _SIGS = {
     "ls_wire_reset": (c_int, [c_vp]),
     "ls_wire_debug_slots": (c_int, [c_vp, c_int, c_vp, ctypes.POINTER(c_i64), c_vp]),
     "ls_scales_to_sf": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
+    "ls_scales_to_sf_block": (c_int, [c_vp, c_i64, c_i64, c_int, c_vp, c_vp, c_vp]),
     "ls_scales_to_sf_t": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp, c_vp]),
     "ls_e4m3_to_packed": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),
     "ls_e4m3_to_packed_t": (c_int, [c_vp, c_i64, c_i64, c_vp, c_vp]),

@@ -33,23 +33,27 @@ constexpr int kGemmThreads = 192;      // single-CTA kernel: producer, MMA issue
 constexpr int kPairThreads = 320;      // CTA-pair kernel: producer, MMA issuer, 8 epilogue warps
 constexpr int kTmemCols = 512;
 
-template <int BN>
+// VS = elements per scale (32: MXFP4 as lockstep quantizes by default; 16: the block-16 form of
+// quantize_mxfp4(x, 16), UE8M0 scales on kind::mxf4nvf4).  A scale tile holds 128 rows x 4
+// scales, i.e. 4 * VS elements of K, so a block-16 stage carries twice the scale tiles.
+template <int BN, int VS = 32>
 struct Cfg {
+    static constexpr int SFT = 32 / VS;                    // scale tiles per 128 elements of K: 1 or 2
     // Narrow tiles (64 columns) are for short-M products, which are weight streams: the
     // number of SMs that load and the bytes each keeps in flight matter, the tile shape does
     // not.  Their stages are small, so there are more of them.
     static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : 8;
     static constexpr int A_BYTES = BM * BKB;
     static constexpr int B_BYTES = BN * BKB;
-    static constexpr int SFA_BYTES = 1024;                 // 128 rows x 8 k-blocks
+    static constexpr int SFA_BYTES = 1024 * SFT;           // 128 rows x 8 (16) scales
     static constexpr int SFB_TILES = BN >= 128 ? BN / 128 : 1;   // 128-row scale tiles of W that a tile touches
-    static constexpr int SFB_BYTES = SFB_TILES * 1024;
+    static constexpr int SFB_BYTES = SFB_TILES * 1024 * SFT;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
     static constexpr int OVL = BN == 256 ? 32 : 0;        // columns shared by the two accumulators
     static constexpr int ACC1 = BN - OVL;                 // first column of the second accumulator
-    static constexpr int SFA_COL = 2 * BN - OVL;          // 8 columns
-    static constexpr int SFB_COL = SFA_COL + 8;           // 8 columns per 128 rows of W
-    static_assert(SFB_COL + SFB_TILES * 8 <= kTmemCols, "tensor memory overflow");
+    static constexpr int SFA_COL = 2 * BN - OVL;          // 8 (16) columns
+    static constexpr int SFB_COL = SFA_COL + 8 * SFT;     // 8 (16) columns per 128 rows of W
+    static_assert(SFB_COL + SFB_TILES * 8 * SFT <= kTmemCols, "tensor memory overflow");
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
     static_assert(SMEM <= 227 * 1024, "shared memory overflow");
 };
@@ -261,12 +265,34 @@ __device__ __forceinline__ void issue_stage(uint32_t acc, uint64_t adesc, uint64
     }
 }
 
-template <int BN>
+// The same for block-16 scales: every K = 64 MMA has a scale tile of its own (4 scales per row).
+template <int ATOMS, int SFB_ATOMS>
+__device__ __forceinline__ void issue_stage16(uint32_t acc, uint64_t adesc, uint64_t bdesc, uint64_t sfa_desc,
+                                              uint64_t sfb_desc, uint32_t sfa_t, uint32_t sfb_t, uint32_t idesc,
+                                              bool first_of_tile, uint32_t sfb_sub)
+{
+    constexpr int T = 2 * ATOMS;                            // scale tiles = MMAs in this stage
+    constexpr int SFB_COLS = 4 * SFB_ATOMS;                 // columns per scale tile index
+#pragma unroll
+    for (int j = 0; j < T; j++) {
+        ptx::tmem_cp_sf<1>(sfa_t + 4 * j, sfa_desc + 32 * j);
+#pragma unroll
+        for (int r = 0; r < SFB_ATOMS; r++)
+            ptx::tmem_cp_sf<1>(sfb_t + SFB_COLS * j + 4 * r, sfb_desc + 128 * r + 32 * j);
+    }
+#pragma unroll
+    for (int kb = 0; kb < T; kb++)
+        ptx::mma_mxf4_block16(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + sfb_sub + SFB_COLS * kb,
+                              (kb == 0 && first_of_tile) ? 0u : 1u);
+}
+
+template <int BN, int VS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                   const __grid_constant__ CUtensorMap tm_b, const GemmParams p)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, VS>;
+    constexpr int SFT = C::SFT;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
@@ -329,13 +355,13 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                 const int b = tt % p.nbatch, rest = tt / p.nbatch;
                 const int mt = rest % m_tiles, nt = rest / m_tiles;
                 const CUtensorMap *tma = b ? &tm_a1 : &tm_a0;
-                const uint8_t *sfa = (b ? p.sfa[1] : p.sfa[0]) + int64_t(mt) * k_atoms * 512;
+                const uint8_t *sfa = (b ? p.sfa[1] : p.sfa[0]) + int64_t(mt) * k_atoms * SFT * 512;
                 for (int kt = kt_begin(ks); kt < kt_end(ks); kt++, it++) {
                     const int s = it % C::STAGES;
                     const uint32_t ph = (it / C::STAGES) & 1;
                     if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag))) break;
                     const int atoms = min(2, k_atoms - 2 * kt);           // scale tiles in this stage
-                    const uint32_t sf_bytes = 512u * atoms;
+                    const uint32_t sf_bytes = 512u * SFT * atoms;
                     const uint32_t st = smem_base + s * C::STAGE_BYTES;
                     // scale tiles of W rows past N do not exist; their products are never stored
                     const int sfb_tile0 = nt * BN / 128;                  // first 128-row scale tile of this column tile
@@ -343,10 +369,10 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     ptx::mbar_expect_tx(full_bar(s), uint32_t(p.a_box_bytes) + C::B_BYTES + sf_bytes * (1 + b_atoms));
                     ptx::tma_load_2d(st, tma, kt * BKB, mt * BM, full_bar(s));
                     ptx::tma_load_2d(st + C::A_BYTES, &tm_b, kt * BKB, nt * BN, full_bar(s));
-                    ptx::bulk_load(st + C::A_BYTES + C::B_BYTES, sfa + int64_t(kt) * 1024, sf_bytes, full_bar(s));
+                    ptx::bulk_load(st + C::A_BYTES + C::B_BYTES, sfa + int64_t(kt) * 1024 * SFT, sf_bytes, full_bar(s));
                     for (int r = 0; r < b_atoms; r++)
-                        ptx::bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + r * 1024,
-                                       p.sfb + (int64_t(sfb_tile0 + r) * k_atoms + 2 * kt) * 512,
+                        ptx::bulk_load(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + r * 1024 * SFT,
+                                       p.sfb + (int64_t(sfb_tile0 + r) * k_atoms + 2 * kt) * SFT * 512,
                                        sf_bytes, full_bar(s));
                 }
             }
@@ -380,12 +406,21 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
                     ptx::tc_fence_after();
                     const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);       // stage offset in 16-byte units
-                    if (2 * kt + 2 <= k_atoms)
-                        issue_stage<1, 2, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
-                                                        tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
-                    else
-                        issue_stage<1, 1, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
-                                                        tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
+                    if constexpr (VS == 32) {
+                        if (2 * kt + 2 <= k_atoms)
+                            issue_stage<1, 2, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                            tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
+                        else
+                            issue_stage<1, 1, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                            tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
+                    } else {
+                        if (2 * kt + 2 <= k_atoms)
+                            issue_stage16<2, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                           tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, sfb_sub);
+                        else
+                            issue_stage16<1, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                                                           tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, sfb_sub);
+                    }
                     ptx::tc_commit(empty_bar(s));
                 }
                 if (ok) ptx::tc_commit(acc_full_bar);
@@ -800,18 +835,18 @@ int make_operand_map(CUtensorMap *m, const void *base, int64_t rows, int64_t kby
 
 std::atomic<int> g_gemm_pdl{1};       // 1: the GEMM kernels are launched with programmatic stream serialization
 
-template <int BN>
+template <int BN, int VS = 32>
 int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
            cudaStream_t st)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, VS>;
     static bool attr_set[64] = {};
     int dev = 0;
     if (int rc = current_device(&dev)) return rc;
     {
         std::lock_guard<std::mutex> lk(state_mutex());
         if (!attr_set[dev]) {
-            LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+            LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_kernel<BN, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
             attr_set[dev] = true;
         }
     }
@@ -827,7 +862,7 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = g_gemm_pdl.load(std::memory_order_relaxed) ? 1 : 0;
     cfg.attrs = at, cfg.numAttrs = 1;
-    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_kernel<BN>, ta0, ta1, tb, p));
+    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_kernel<BN, VS>, ta0, ta1, tb, p));
     return LS_OK;
 }
 
@@ -1104,9 +1139,68 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     return LS_OK;
 }
 
+// Operands quantized with blocks of 16 (fp4.py:57, quantize_mxfp4(x, 16)): the single-CTA
+// kernel with one scale tile per K = 64 MMA.  Tiles of 128 or 64 columns (tensor memory has no
+// room for two 256-column accumulators beside 48 scale columns); no K split, no CTA pairs.
+int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
+                 const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
+                 int64_t N, int64_t K, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (M < 0 || N < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a multiple of 128", (long long)K);
+    if (out_dtype != LS_F32 && out_dtype != LS_BF16) return fail(LS_EINVAL, "unsupported output dtype %d", out_dtype);
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return fail(LS_EINVAL, "dimension too large");
+    if (M == 0 || N == 0) return LS_OK;
+    if (K == 0) return fail(LS_EINVAL, "K must be positive");
+    if (!a0 || !w || !sfa0 || !sfb || !c0 || (nbatch == 2 && (!a1 || !sfa1 || !c1))) return fail(LS_EINVAL, "null pointer");
+    if (!aligned16(a0) || !aligned16(w) || !aligned16(sfa0) || !aligned16(sfb) || !aligned16(c0) ||
+        (nbatch == 2 && (!aligned16(a1) || !aligned16(sfa1) || !aligned16(c1))))
+        return fail(LS_EALIGN, "GEMM operands, scale buffers and outputs must be 16-byte aligned");
+    int *err = error_word();
+    if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
+    CUtensorMap ta0, ta1, tb;
+    int a_box_rows = 16;
+    while (a_box_rows < M && a_box_rows < BM) a_box_rows *= 2;
+    const int64_t tiles128 = ((M + BM - 1) / BM) * ((N + 127) / 128) * nbatch;
+    const int bn = tiles128 * 2 <= sm_count() ? 64 : 128;
+    if (int rc = make_operand_map(&ta0, a0, M, K / 2, a_box_rows)) return rc;
+    if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, a_box_rows)) return rc;
+    if (int rc = make_operand_map(&tb, w, N, K / 2, bn)) return rc;
+    GemmParams p{};
+    p.sfa[0] = sfa0;
+    p.sfa[1] = nbatch == 2 ? sfa1 : sfa0;
+    p.sfb = sfb;
+    p.c[0] = c0;
+    p.c[1] = nbatch == 2 ? c1 : c0;
+    p.M = int(M), p.N = int(N), p.K = int(K);
+    p.nbatch = nbatch;
+    p.out_bf16 = out_dtype == LS_BF16;
+    p.err = err;
+    p.splits = 1;
+    p.kt_per_split = int((K / 2 + BKB - 1) / BKB);
+    p.partial = nullptr;
+    p.store_c = true;
+    p.a_box_bytes = a_box_rows * BKB;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return bn == 64 ? launch<64, 16>(ta0, ta1, tb, p, st) : launch<128, 16>(ta0, ta1, tb, p, st);
+}
+
 }  // namespace ls
 
 using namespace ls;
+
+extern "C" int ls_mxfp4_gemm_block16(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                                     void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
+{
+    return gemm_block16(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream);
+}
+
+extern "C" int ls_mxfp4_gemm_dual_block16(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
+                                          const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
+                                          void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
+{
+    return gemm_block16(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream);
+}
 
 extern "C" int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
                              void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)

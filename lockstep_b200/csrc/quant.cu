@@ -606,6 +606,12 @@ extern "C" int64_t ls_sf_bytes(int64_t rows, int64_t K)
     return ((rows + 127) / 128) * (K / 128) * 512;
 }
 
+extern "C" int64_t ls_sf_bytes_block(int64_t rows, int64_t K, int block)
+{
+    if (rows < 0 || K < 0 || K % 128 != 0 || (block != 32 && block != 16)) return -1;
+    return ((rows + 127) / 128) * (K / (4 * block)) * 512;
+}
+
 extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64_t K, int block,
                                  int rounding, uint8_t *codes, uint8_t *packed, float *scale,
                                  uint8_t *e8m0, uint8_t *sf, void *stream)
@@ -618,8 +624,8 @@ extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64
     if (rounding != LS_ROUND_REF && rounding != LS_ROUND_RNE) return fail(LS_EINVAL, "bad rounding %d", rounding);
     if (rows * K == 0) return LS_OK;
     if (!codes && !packed && !scale && !e8m0 && !sf) return fail(LS_EINVAL, "no output requested");
-    if (sf && (block != 32 || K % 128 != 0))
-        return fail(LS_EINVAL, "scale-factor layout needs block 32 and K %% 128 == 0 (K=%lld)", (long long)K);
+    if (sf && K % 128 != 0)
+        return fail(LS_EINVAL, "scale-factor layout needs K %% 128 == 0 (K=%lld)", (long long)K);
     int64_t n = rows * K;
     if (n == 0) return LS_OK;
     if (!x) return fail(LS_EINVAL, "x is null");
@@ -630,7 +636,7 @@ extern "C" int ls_quantize_mxfp4(const void *x, int x_dtype, int64_t rows, int64
     if ((reinterpret_cast<uintptr_t>(scale) & 15) || (reinterpret_cast<uintptr_t>(e8m0) & 3) ||
         (reinterpret_cast<uintptr_t>(sf) & 3))
         return fail(LS_EALIGN, "scale must be 16-byte, e8m0 and sf 4-byte aligned");
-    QuantOut o{codes, packed, e8m0, sf, scale, uint32_t(K / block), uint32_t(K / 128), 0u, 0u, uint32_t(n / block)};
+    QuantOut o{codes, packed, e8m0, sf, scale, uint32_t(K / block), uint32_t(K / (4 * block)), 0u, 0u, uint32_t(n / block)};
     {   // multiply-shift division by kblocks (>= 4 whenever the scale-factor layout is requested)
         uint32_t d = o.kblocks, sh = 0;
         while ((1ull << sh) < d) sh++;
@@ -738,6 +744,21 @@ extern "C" int ls_scales_to_sf(const float *scale, int64_t rows, int64_t K, uint
     if (!scale || !sf) return fail(LS_EINVAL, "null pointer");
     scales_to_sf_kernel<<<grid_for(nblocks, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         scale, nblocks, uint32_t(K / 32), sf, bad);
+    LS_LAUNCH_CHECK("scales_to_sf");
+    return LS_OK;
+}
+
+extern "C" int ls_scales_to_sf_block(const float *scale, int64_t rows, int64_t K, int block, uint8_t *sf,
+                                     int32_t *bad, void *stream)
+{
+    if (int rc = check_device()) return rc;
+    if (block != 32 && block != 16) return fail(LS_EINVAL, "block must be 32 or 16, got %d", block);
+    if (rows < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K must be a multiple of 128");
+    int64_t nblocks = rows * (K / block);
+    if (nblocks == 0) return LS_OK;
+    if (!scale || !sf) return fail(LS_EINVAL, "null pointer");
+    scales_to_sf_kernel<<<grid_for(nblocks, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        scale, nblocks, uint32_t(K / block), sf, bad);
     LS_LAUNCH_CHECK("scales_to_sf");
     return LS_OK;
 }

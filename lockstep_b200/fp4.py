@@ -67,19 +67,21 @@ def quantize_mxfp4(x: torch.Tensor, block: int = 32, rounding: str = "ref"):
     return codes, scale
 
 
-def quantize_mxfp4_packed(x: torch.Tensor, rounding: str = "ref", want_scale: bool = False):
+def quantize_mxfp4_packed(x: torch.Tensor, rounding: str = "ref", want_scale: bool = False, block: int = 32):
     """(extension) One pass from bf16/fp32 to what the tensor-core GEMM reads:
     packed nibbles [..., K // 2] and E8M0 scale bytes in the tcgen05
     scale-factor layout (see sf_bytes).  Fuses quantize_mxfp4 + pack_fp4 +
     the scale re-layout.  K must be a multiple of 128.  With want_scale the
-    fp32 scales [..., K // 32] are returned as a third value."""
+    fp32 scales [..., K // block] are returned as a third value.  block = 16
+    gives the operands of mxfp4_gemm_packed(..., block=16)."""
     need_cuda(x)
-    x, lead, K, rows = _as_rows(x, 32)
+    assert block in (16, 32)
+    x, lead, K, rows = _as_rows(x, block)
     assert K % 128 == 0, "K must be a multiple of 128"
     packed = torch.empty((*lead, K // 2), dtype=torch.uint8, device=x.device)
-    sf = torch.empty(sf_bytes(rows, K), dtype=torch.uint8, device=x.device)
-    scale = torch.empty((*lead, K // 32), dtype=torch.float32, device=x.device) if want_scale else None
-    check(lib().ls_quantize_mxfp4(ptr(x), _lib.dtype_code(x.dtype), rows, K, 32, _ROUNDING[rounding],
+    sf = torch.empty(sf_bytes(rows, K, block), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((*lead, K // block), dtype=torch.float32, device=x.device) if want_scale else None
+    check(lib().ls_quantize_mxfp4(ptr(x), _lib.dtype_code(x.dtype), rows, K, block, _ROUNDING[rounding],
                                   None, ptr(packed), ptr(scale), None, ptr(sf), stream()))
     return (packed, sf, scale) if want_scale else (packed, sf)
 
@@ -157,21 +159,22 @@ def quantize_mxfp4_both(x: torch.Tensor, rounding: str = "ref", act=None):
     return packed, sf, packed_t, sf_t
 
 
-def sf_bytes(rows: int, K: int) -> int:
+def sf_bytes(rows: int, K: int, block: int = 32) -> int:
     """(extension) Size of the scale-factor buffer of a [rows, K] operand."""
-    return int(lib().ls_sf_bytes(rows, K))
+    return int(lib().ls_sf_bytes_block(rows, K, block))
 
 
-def scales_to_sf(scale: torch.Tensor) -> torch.Tensor:
-    """(extension) fp32 power-of-two scales [rows, K // 32] -> scale-factor
+def scales_to_sf(scale: torch.Tensor, block: int = 32) -> torch.Tensor:
+    """(extension) fp32 power-of-two scales [rows, K // block] -> scale-factor
     layout bytes.  Raises if a scale is not a power of two."""
     need_cuda(scale)
     scale = aligned(scale.float())
     rows, kb = scale.shape
-    assert kb % 4 == 0, "K must be a multiple of 128"
-    sf = torch.empty(sf_bytes(rows, kb * 32), dtype=torch.uint8, device=scale.device)
+    K = kb * block
+    assert K % 128 == 0, "K must be a multiple of 128"
+    sf = torch.empty(sf_bytes(rows, K, block), dtype=torch.uint8, device=scale.device)
     bad = torch.zeros(1, dtype=torch.int32, device=scale.device)
-    check(lib().ls_scales_to_sf(ptr(scale), rows, kb * 32, ptr(sf), ptr(bad), stream()))
+    check(lib().ls_scales_to_sf_block(ptr(scale), rows, K, block, ptr(sf), ptr(bad), stream()))
     return sf, bad
 
 

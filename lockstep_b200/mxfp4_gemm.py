@@ -21,30 +21,36 @@ from ._lib import aligned, check, lib, need_cuda, ptr, stream
 CFG = dict(BLOCK_M=128, BLOCK_N=256, BLOCK_K=256, num_stages=4, num_warps=6)
 
 
-def _sf(scale, rows, K):
-    """fp32 [rows, K//32] scales -> scale-factor bytes; uint8 buffers pass through."""
+def _sf(scale, rows, K, block=32):
+    """fp32 [rows, K//block] scales -> scale-factor bytes; uint8 buffers pass through."""
     if scale.dtype == torch.uint8:
-        assert scale.numel() == fp4.sf_bytes(rows, K), "scale-factor buffer has the wrong size"
+        assert scale.numel() == fp4.sf_bytes(rows, K, block), "scale-factor buffer has the wrong size"
         return aligned(scale)
-    assert scale.shape == (rows, K // 32), f"scale shape {tuple(scale.shape)} != {(rows, K // 32)}"
-    sf, _bad = fp4.scales_to_sf(scale)
+    assert scale.shape == (rows, K // block), f"scale shape {tuple(scale.shape)} != {(rows, K // block)}"
+    sf, _bad = fp4.scales_to_sf(scale, block)
     return sf
 
 
-def mxfp4_gemm_packed(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloat16):
+def mxfp4_gemm_packed(a_pk, bt_pk, a_scale, b_scale, out_dtype=torch.bfloat16, block=32):
     """a_pk [M, K//2] uint8, bt_pk [N, K//2] uint8 (both K-contiguous, even
     index in the low nibble), a_scale [M, K//32], b_scale [N, K//32].
-    Returns C = A @ B_T.T as [M, N] of out_dtype (bf16 or fp32)."""
+    Returns C = A @ B_T.T as [M, N] of out_dtype (bf16 or fp32).
+
+    (extension) block = 16 takes operands of fp4.quantize_mxfp4(x, 16): scales
+    [M, K//16] and [N, K//16].  The reference's GEMM has no such form
+    (mxfp4_gemm.py:136 fixes 32 values per scale); on tcgen05 it is the same
+    kernel on `kind::mxf4nvf4.block_scale.block16` with UE8M0 scales."""
     need_cuda(a_pk, bt_pk, a_scale, b_scale)
+    assert block in (16, 32)
     M, Kh = a_pk.shape
     N, Kh2 = bt_pk.shape
     K = Kh * 2
     assert Kh == Kh2 and K % 128 == 0, "K must be a multiple of 128 (max BLOCK_K)"
     a_pk, bt_pk = aligned(a_pk), aligned(bt_pk)
-    sfa, sfb = _sf(a_scale, M, K), _sf(b_scale, N, K)
+    sfa, sfb = _sf(a_scale, M, K, block), _sf(b_scale, N, K, block)
     c = torch.empty((M, N), device=a_pk.device, dtype=out_dtype)
-    check(lib().ls_mxfp4_gemm(ptr(a_pk), ptr(bt_pk), ptr(sfa), ptr(sfb), ptr(c), _lib.dtype_code(out_dtype),
-                              M, N, K, stream()))
+    fn = lib().ls_mxfp4_gemm if block == 32 else lib().ls_mxfp4_gemm_block16
+    check(fn(ptr(a_pk), ptr(bt_pk), ptr(sfa), ptr(sfb), ptr(c), _lib.dtype_code(out_dtype), M, N, K, stream()))
     return c
 
 
