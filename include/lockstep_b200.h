@@ -178,6 +178,29 @@ int ls_mxfp4_gemm_dual_block16(const uint8_t *a1_pk, const uint8_t *a2_pk, const
                                const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
                                void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 
+/* NVFP4: blocks of 16 E2M1 values under one E4M3 scale.  lockstep states the format in its
+ * study of block formats (rig_sm75/quant_sim.cuh:90-97 nv_scale_e2m1, :20-33 quant_e4m3,
+ * :57-69 quant_e2m1_code, applied per block as rig_q.cu:348-363) but has no kernel for it.
+ *   scale = E4M3(amax / 6) (half-even, saturating at 448; 2^-9 where that is 0; 1.0 for a block
+ *   with no positive maximum), code = E2M1 nearest to v / scale, ties to the smaller magnitude.
+ *   x         [rows, K] LS_F32 or LS_BF16, 16-byte aligned;  K % 128 == 0
+ *   packed    [rows, K/2]
+ *   scale_u8  [rows, K/16] E4M3 bytes, or NULL;  scale_f32 the same scales as fp32, or NULL
+ *   sf        the scale bytes in the scale-factor layout (ls_sf_bytes_block(rows, K, 16)), or NULL */
+int ls_quantize_nvfp4(const void *x, int x_dtype, int64_t rows, int64_t K, uint8_t *packed,
+                      uint8_t *scale_u8, float *scale_f32, uint8_t *sf, void *stream);
+/* value[code] * scale for NVFP4 operands: out [rows, K] LS_F32 or LS_BF16; K % 16 == 0. */
+int ls_dequantize_nvfp4(const uint8_t *packed, const uint8_t *scale_u8, int64_t rows, int64_t K,
+                        void *out, int out_dtype, void *stream);
+/* ls_mxfp4_gemm_block16 / ls_mxfp4_gemm_dual_block16 with E4M3 scale bytes (the `sf` output of
+ * ls_quantize_nvfp4): C = A W^T on tcgen05.mma.kind::mxf4nvf4.block_scale.block16, fp32
+ * accumulation.  No counterpart in lockstep. */
+int ls_nvfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                  void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
+int ls_nvfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
+                       const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1, void *c2,
+                       int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
+
 /* GEMM whose epilogue also emits MXFP4 of act(C) for a following MXFP4 GEMM
  * (scale blocks of 32 along N), so that C is not re-read by a quantize pass.
  * Covers the chain  _MXFP4Matmul -> F.gelu -> _MXFP4Matmul  of lockstep's

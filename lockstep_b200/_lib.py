@@ -34,6 +34,10 @@ _SIGS = {
     "ls_mxfp4_gemm_dual": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_mxfp4_gemm_block16": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_mxfp4_gemm_dual_block16": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
+    "ls_quantize_nvfp4": (c_int, [c_vp, c_int, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "ls_dequantize_nvfp4": (c_int, [c_vp, c_vp, c_i64, c_i64, c_vp, c_int, c_vp]),
+    "ls_nvfp4_gemm": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_i64, c_vp]),
+    "ls_nvfp4_gemm_dual": (c_int, [c_vp] * 8 + [c_int, c_i64, c_i64, c_i64, c_vp]),
     "ls_mxfp4_gemm_quant": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp]),
     "ls_gemm_status": (c_int, [c_vp]),
     "ls_gemm_set_variant": (c_int, [c_int]),

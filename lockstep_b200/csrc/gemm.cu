@@ -75,6 +75,7 @@ struct GemmParams {
     int act;                       // 0 none, 1 GELU (erf form)
     int store_c;                   // 0: C itself is not written (only its quantized form)
     int a_box_bytes;               // bytes one TMA load of an A tile delivers (single-CTA kernel: rows of the box x 128)
+    int sf_e4m3;                   // block-16 kernel only: the scale bytes are E4M3 (NVFP4), not UE8M0
 };
 
 // MXFP4 of one row's 32 consecutive outputs (exactly one scale block), as the next GEMM
@@ -383,7 +384,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::idesc_mxf4(BM, BN);
+            // bit 23 of the instruction descriptor: scale type (1 = UE8M0, 0 = UE4M3)
+            const uint32_t idesc = (VS == 16 && p.sf_e4m3) ? (ptx::idesc_mxf4(BM, BN) & ~(1u << 23)) : ptx::idesc_mxf4(BM, BN);
             const uint64_t adesc0 = ptx::desc_sw128(smem_base), bdesc0 = ptx::desc_sw128(smem_base + C::A_BYTES);
             const uint64_t sfadesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES);
             const uint64_t sfbdesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES + C::SFA_BYTES);
@@ -1144,7 +1146,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
 // room for two 256-column accumulators beside 48 scale columns); no K split, no CTA pairs.
 int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
                  const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
-                 int64_t N, int64_t K, void *stream)
+                 int64_t N, int64_t K, void *stream, bool e4m3_scales)
 {
     if (int rc = check_device()) return rc;
     if (M < 0 || N < 0 || K < 0 || K % 128 != 0) return fail(LS_EINVAL, "K=%lld must be a multiple of 128", (long long)K);
@@ -1181,6 +1183,7 @@ int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t
     p.partial = nullptr;
     p.store_c = true;
     p.a_box_bytes = a_box_rows * BKB;
+    p.sf_e4m3 = e4m3_scales;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return bn == 64 ? launch<64, 16>(ta0, ta1, tb, p, st) : launch<128, 16>(ta0, ta1, tb, p, st);
 }
@@ -1192,14 +1195,27 @@ using namespace ls;
 extern "C" int ls_mxfp4_gemm_block16(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
                                      void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
 {
-    return gemm_block16(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream);
+    return gemm_block16(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream, false);
 }
 
 extern "C" int ls_mxfp4_gemm_dual_block16(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
                                           const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
                                           void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
 {
-    return gemm_block16(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream);
+    return gemm_block16(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream, false);
+}
+
+extern "C" int ls_nvfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
+                             void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
+{
+    return gemm_block16(1, a_pk, nullptr, bt_pk, sfa, nullptr, sfb, c, nullptr, out_dtype, M, N, K, stream, true);
+}
+
+extern "C" int ls_nvfp4_gemm_dual(const uint8_t *a1_pk, const uint8_t *a2_pk, const uint8_t *bt_pk,
+                                  const uint8_t *sfa1, const uint8_t *sfa2, const uint8_t *sfb, void *c1,
+                                  void *c2, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream)
+{
+    return gemm_block16(2, a1_pk, a2_pk, bt_pk, sfa1, sfa2, sfb, c1, c2, out_dtype, M, N, K, stream, true);
 }
 
 extern "C" int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
