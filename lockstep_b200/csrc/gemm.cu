@@ -267,7 +267,7 @@ __device__ __forceinline__ void issue_stage(uint32_t acc, uint64_t adesc, uint64
 }
 
 // The same for block-16 scales: every K = 64 MMA has a scale tile of its own (4 scales per row).
-template <int ATOMS, int SFB_ATOMS>
+template <int CTAS, int ATOMS, int SFB_ATOMS>
 __device__ __forceinline__ void issue_stage16(uint32_t acc, uint64_t adesc, uint64_t bdesc, uint64_t sfa_desc,
                                               uint64_t sfb_desc, uint32_t sfa_t, uint32_t sfb_t, uint32_t idesc,
                                               bool first_of_tile, uint32_t sfb_sub)
@@ -276,14 +276,14 @@ __device__ __forceinline__ void issue_stage16(uint32_t acc, uint64_t adesc, uint
     constexpr int SFB_COLS = 4 * SFB_ATOMS;                 // columns per scale tile index
 #pragma unroll
     for (int j = 0; j < T; j++) {
-        ptx::tmem_cp_sf<1>(sfa_t + 4 * j, sfa_desc + 32 * j);
+        ptx::tmem_cp_sf<CTAS>(sfa_t + 4 * j, sfa_desc + 32 * j);
 #pragma unroll
         for (int r = 0; r < SFB_ATOMS; r++)
-            ptx::tmem_cp_sf<1>(sfb_t + SFB_COLS * j + 4 * r, sfb_desc + 128 * r + 32 * j);
+            ptx::tmem_cp_sf<CTAS>(sfb_t + SFB_COLS * j + 4 * r, sfb_desc + 128 * r + 32 * j);
     }
 #pragma unroll
     for (int kb = 0; kb < T; kb++)
-        ptx::mma_mxf4_block16(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + sfb_sub + SFB_COLS * kb,
+        ptx::mma_mxf4_block16<CTAS>(acc, adesc + 2 * kb, bdesc + 2 * kb, idesc, sfa_t + 4 * kb, sfb_t + sfb_sub + SFB_COLS * kb,
                               (kb == 0 && first_of_tile) ? 0u : 1u);
 }
 
@@ -417,10 +417,10 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_consta
                                                             tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, false, false, sfb_sub);
                     } else {
                         if (2 * kt + 2 <= k_atoms)
-                            issue_stage16<2, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                            issue_stage16<1, 2, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
                                                            tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, sfb_sub);
                         else
-                            issue_stage16<1, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
+                            issue_stage16<1, 1, C::SFB_TILES>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16,
                                                            tmem_base + C::SFA_COL, tmem_base + C::SFB_COL, idesc, kt == kt0, sfb_sub);
                     }
                     ptx::tc_commit(empty_bar(s));
@@ -534,21 +534,26 @@ splitk_reduce_kernel(const float *__restrict__ partial, void *__restrict__ out, 
 // load of either CTA completes on CTA 0's barrier).  Warp 1 lane of CTA 0: the
 // MMA issuer for the pair (warp 1 of CTA 1 only takes part in the tensor-memory
 // allocation).  Warps 2-9: epilogue, two warps per quarter of the rows.
+template <int VS>
 struct PairCfg {
+    static constexpr int SFT = 32 / VS;                    // scale tiles per 128 elements of K
     static constexpr int BN = 256;                         // tile columns (128 rows of W per CTA)
-    static constexpr int STAGES = 6;
+    static constexpr int STAGES = VS == 32 ? 6 : 5;
     static constexpr int A_BYTES = BM * BKB;               // 16 KB
     static constexpr int B_BYTES = 128 * BKB;              // this CTA's half of the W tile
-    static constexpr int SFA_BYTES = 1024;
-    static constexpr int SFB_BYTES = 2048;                 // scales of all 256 W rows, in both CTAs
+    static constexpr int SFA_BYTES = 1024 * SFT;
+    static constexpr int SFB_BYTES = 2048 * SFT;           // scales of all 256 W rows, in both CTAs
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
     // Tensor memory: accumulators [0,256) and [224,480) share 32 columns; scale columns
     // at 480 (8 for A, 16 for W).  A second set of scale columns (tried with a 64-column
-    // overlap) did not speed the kernel up.
-    static constexpr int OVL = 32;
-    static constexpr int ACC1 = BN - OVL;                  // 224
-    static constexpr int SF_COL = 2 * BN - OVL;            // 480
+    // overlap) did not speed the kernel up.  Scales per 16 elements take 48 columns: the
+    // accumulators then share 64 columns, [0,256) and [192,448).
+    static constexpr int OVL = VS == 32 ? 32 : 64;
+    static constexpr int ACC1 = BN - OVL;                  // 224 (192)
+    static constexpr int SF_COL = 2 * BN - OVL;            // 480 (448)
+    static_assert(SF_COL + 24 * SFT <= kTmemCols, "tensor memory overflow");
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(SMEM <= 227 * 1024, "shared memory overflow");
 };
 
 __device__ __forceinline__ void cluster_sync()
@@ -562,13 +567,15 @@ __device__ __forceinline__ uint32_t cluster_ctarank()
     return r;
 }
 
+template <int VS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfa0,
                        const __grid_constant__ CUtensorMap tm_sfa1, const __grid_constant__ CUtensorMap tm_sfb,
                        const GemmParams p)
 {
-    using C = PairCfg;
+    using C = PairCfg<VS>;
+    constexpr int SFT = C::SFT;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + C::STAGES * C::STAGE_BYTES;
@@ -647,11 +654,11 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                     if (cta == 0) ptx::mbar_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);
                     ptx::tma_load_2d_pair(st, tma, kt * BKB, mt * BM, bar);
                     ptx::tma_load_2d_pair(st + C::A_BYTES, &tm_b, kt * BKB, nt * C::BN + int(cta) * 128, bar);
-                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES, tsfa, 0, mt * k_atoms + 2 * kt, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES, tsfa, 0, (mt * k_atoms + 2 * kt) * SFT, bar);
                     ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES, &tm_sfb, 0,
-                                          (2 * nt) * k_atoms + 2 * kt, bar);
-                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + 1024, &tm_sfb, 0,
-                                          (2 * nt + 1) * k_atoms + 2 * kt, bar);
+                                          ((2 * nt) * k_atoms + 2 * kt) * SFT, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + 1024 * SFT, &tm_sfb, 0,
+                                          ((2 * nt + 1) * k_atoms + 2 * kt) * SFT, bar);
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
             }
@@ -663,7 +670,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
     } else if (warp == 1 && cta == 0) {
         // ------------------------------------------------------------ MMA issuer (CTA 0, for the pair)
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::idesc_mxf4(256, C::BN);
+            const uint32_t idesc = (VS == 16 && p.sf_e4m3) ? (ptx::idesc_mxf4(256, C::BN) & ~(1u << 23)) : ptx::idesc_mxf4(256, C::BN);
             const uint64_t adesc0 = ptx::desc_sw128(smem_base), bdesc0 = ptx::desc_sw128(smem_base + C::A_BYTES);
             const uint64_t sfadesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES);
             const uint64_t sfbdesc0 = ptx::desc_sf(smem_base + C::A_BYTES + C::B_BYTES + C::SFA_BYTES);
@@ -679,13 +686,22 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
                     ptx::tc_fence_after();
                     const uint32_t st16 = uint32_t(s) * (C::STAGE_BYTES >> 4);
-                    const uint32_t sfa_t = tmem_base + C::SF_COL, sfb_t = sfa_t + 8;
-                    if (2 * kt + 2 <= k_atoms)
-                        issue_stage<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                             sfb_t, idesc, kt == kt0, false, false);
-                    else
-                        issue_stage<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                             sfb_t, idesc, kt == kt0, false, false);
+                    const uint32_t sfa_t = tmem_base + C::SF_COL, sfb_t = sfa_t + 8 * SFT;
+                    if constexpr (VS == 32) {
+                        if (2 * kt + 2 <= k_atoms)
+                            issue_stage<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
+                                                 sfb_t, idesc, kt == kt0, false, false);
+                        else
+                            issue_stage<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
+                                                 sfb_t, idesc, kt == kt0, false, false);
+                    } else {
+                        if (2 * kt + 2 <= k_atoms)
+                            issue_stage16<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
+                                                   sfb_t, idesc, kt == kt0, 0u);
+                        else
+                            issue_stage16<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
+                                                   sfb_t, idesc, kt == kt0, 0u);
+                    }
                     ptx::tc_commit_pair(empty_bar(s), 3);      // frees the stage in both CTAs
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
@@ -716,13 +732,14 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
             const int row = mt * BM + 32 * q + lane;
             constexpr int CH = C::BN / 32 / 2;              // chunks per warp
-            static_assert(C::OVL == 32 && CH == 4, "the drain order below assumes one shared chunk per tile");
-            // The 32 columns shared with the other accumulator are chunk 7 of accumulator 0
-            // and chunk 0 of accumulator 1.  The warps that own them read them first and
+            constexpr int SH = C::OVL / 32;                 // chunks shared with the other accumulator: 1 or 2
+            static_assert((SH == 1 || SH == 2) && CH == 4, "the drain order below reads the shared chunks as the first pair");
+            // The columns shared with the other accumulator are the last chunk(s) of accumulator 0
+            // and the first of accumulator 1.  The warps that own them read them first and
             // then release the next tile; the other warps release it at once: being here,
             // they have finished every load of the tiles before this one.
             const bool owner = (lt & 1) ? half == 0 : half == 1;
-            const int start = (owner && !(lt & 1)) ? CH - 1 : 0;
+            const int start = (owner && !(lt & 1)) ? CH - SH : 0;
             auto chunk = [&](int i) { return CH * half + ((start + i) & (CH - 1)); };
             auto release_next_tile = [&]() {
                 ptx::tc_fence_before();
@@ -741,6 +758,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             for (int i = 0; i < CH; i += 2) {
                 ptx::tmem_ld_wait(ra);
                 ptx::tmem_ld32(acc + 32 * chunk(i + 1), rb);
+                if (SH == 2 && i == 0 && owner) ptx::tmem_ld_wait(rb);
                 if (i == 0 && owner) release_next_tile();   // shared columns drained
                 emit(chunk(i), ra);
                 ptx::tmem_ld_wait(rb);
@@ -870,9 +888,9 @@ int launch(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb
 
 // Scale-factor buffer as [tiles, 128] 32-bit words (512 bytes per 128-row x 4-block tile);
 // one box = two consecutive k-tiles of one row tile.
-int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K)
+int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K, int sft)
 {
-    const MapKey key{base, rows, K, 2, 1};
+    const MapKey key{base, rows, K, 2 * sft, 1};
     MapSlot *slot = map_slot(key);
     if (slot->used && slot->key == key) {
         *m = slot->map;
@@ -880,9 +898,9 @@ int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K)
     }
     EncodeFn fn = encode_fn();
     if (!fn) return fail(LS_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    cuuint64_t dims[2] = {128, cuuint64_t(((rows + 127) / 128) * (K / 128))};
+    cuuint64_t dims[2] = {128, cuuint64_t(((rows + 127) / 128) * (K / 128) * sft)};
     cuuint64_t strides[1] = {512};
-    cuuint32_t box[2] = {128, 2};
+    cuuint32_t box[2] = {128, cuuint32_t(2 * sft)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -892,20 +910,21 @@ int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K)
     return LS_OK;
 }
 
+template <int VS = 32>
 int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
                 cudaStream_t st)
 {
+    using C = PairCfg<VS>;
     CUtensorMap tsa0, tsa1, tsb;
-    if (int rc = make_sf_map(&tsa0, p.sfa[0], p.M, p.K)) return rc;
-    if (int rc = make_sf_map(&tsa1, p.sfa[1], p.M, p.K)) return rc;
-    if (int rc = make_sf_map(&tsb, p.sfb, p.N, p.K)) return rc;
-    using C = PairCfg;
+    if (int rc = make_sf_map(&tsa0, p.sfa[0], p.M, p.K, C::SFT)) return rc;
+    if (int rc = make_sf_map(&tsa1, p.sfa[1], p.M, p.K, C::SFT)) return rc;
+    if (int rc = make_sf_map(&tsb, p.sfb, p.N, p.K, C::SFT)) return rc;
     static int resident_pairs[64] = {};
     int dev = 0;
     if (int rc = current_device(&dev)) return rc;
     std::unique_lock<std::mutex> lk(state_mutex());
     if (!resident_pairs[dev]) {
-        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_pair_kernel<VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         // The kernel is persistent: the grid must not exceed the CTA pairs that can be
         // resident at once (fewer than SMs / 2 when a TPC has a single SM enabled).
         cudaLaunchConfig_t cfg = {};
@@ -917,7 +936,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
         at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
         cfg.attrs = at, cfg.numAttrs = 1;
         int n = 0;
-        LS_CUDA(cudaOccupancyMaxActiveClusters(&n, mxfp4_gemm_pair_kernel, &cfg));
+        LS_CUDA(cudaOccupancyMaxActiveClusters(&n, mxfp4_gemm_pair_kernel<VS>, &cfg));
         if (n < 1) return fail(LS_ECUDA, "no CTA pair of the GEMM kernel fits on this device");
         resident_pairs[dev] = n;
     }
@@ -935,7 +954,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = g_gemm_pdl.load(std::memory_order_relaxed) ? 1 : 0;
     cfg.attrs = at, cfg.numAttrs = 1;
-    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_pair_kernel, ta0, ta1, tb, tsa0, tsa1, tsb, p));
+    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_pair_kernel<VS>, ta0, ta1, tb, tsa0, tsa1, tsb, p));
     return LS_OK;
 }
 
@@ -1142,8 +1161,9 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
 }
 
 // Operands quantized with blocks of 16 (fp4.py:57, quantize_mxfp4(x, 16)): the single-CTA
-// kernel with one scale tile per K = 64 MMA.  Tiles of 128 or 64 columns (tensor memory has no
-// room for two 256-column accumulators beside 48 scale columns); no K split, no CTA pairs.
+// kernels with one scale tile per K = 64 MMA.  The single-CTA kernel takes tiles of 128 or 64
+// columns (two 256-column accumulators sharing 32 columns leave no room for 48 scale columns);
+// the CTA-pair kernel lets its accumulators share 64 columns.  No K split.
 int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *w, const uint8_t *sfa0,
                  const uint8_t *sfa1, const uint8_t *sfb, void *c0, void *c1, int out_dtype, int64_t M,
                  int64_t N, int64_t K, void *stream, bool e4m3_scales)
@@ -1161,13 +1181,18 @@ int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t
     int *err = error_word();
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     CUtensorMap ta0, ta1, tb;
-    int a_box_rows = 16;
-    while (a_box_rows < M && a_box_rows < BM) a_box_rows *= 2;
+    // as for blocks of 32: CTA pairs for two batches or more than one row tile, else one CTA per
+    // tile with a box of A no taller than A (ls_gemm_set_variant 2 / 1, 3, 5 force either)
+    const int variant = g_gemm_variant.load(std::memory_order_relaxed);
+    const bool pair = variant == 2 || (variant == 0 && (nbatch == 2 || M > BM));
+    int a_box_rows = BM;
+    if (!pair)
+        for (a_box_rows = 16; a_box_rows < M && a_box_rows < BM; a_box_rows *= 2) {}
     const int64_t tiles128 = ((M + BM - 1) / BM) * ((N + 127) / 128) * nbatch;
-    const int bn = tiles128 * 2 <= sm_count() ? 64 : 128;
+    const int bn = variant == 5 || (variant != 3 && tiles128 * 2 <= sm_count()) ? 64 : 128;
     if (int rc = make_operand_map(&ta0, a0, M, K / 2, a_box_rows)) return rc;
     if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, a_box_rows)) return rc;
-    if (int rc = make_operand_map(&tb, w, N, K / 2, bn)) return rc;
+    if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
     p.sfa[1] = nbatch == 2 ? sfa1 : sfa0;
@@ -1185,6 +1210,7 @@ int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t
     p.a_box_bytes = a_box_rows * BKB;
     p.sf_e4m3 = e4m3_scales;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (pair) return launch_pair<16>(ta0, ta1, tb, p, st);
     return bn == 64 ? launch<64, 16>(ta0, ta1, tb, p, st) : launch<128, 16>(ta0, ta1, tb, p, st);
 }
 

@@ -149,14 +149,21 @@ __device__ __forceinline__ void mma_mxf4(uint32_t d, uint64_t adesc, uint64_t bd
                      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 }
 
-// The same with one UE8M0 scale per 16 elements (four scales per row and MMA: a whole scale
-// column), on the kind that takes E2M1 operands with either scale granularity.
+// The same with one scale per 16 elements (four scales per row and MMA: a whole scale
+// column), on the kind that takes E2M1 operands with either scale granularity; the scale
+// type (UE8M0 or UE4M3) is a field of the instruction descriptor.
+template <int CTAS>
 __device__ __forceinline__ void mma_mxf4_block16(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                  uint32_t sfa, uint32_t sfb, uint32_t accumulate)
 {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
-                 ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+    if (CTAS == 1)
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                     "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+                     ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                     "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+                     ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 }
 
 // arrive on a barrier of this CTA once every tcgen05 op issued so far by this thread is done

@@ -144,3 +144,42 @@ def test_block16_is_at_least_as_close_to_the_unquantized_product(mods):
         errs[block] = ((c - exact).norm() / exact.norm()).item()
     mg.gemm_status()
     assert errs[16] < errs[32], errs
+
+
+@pytest.mark.parametrize("fmt", ["mx16", "nvfp4"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 640, 1152), (1000, 520, 2048)])
+def test_block16_kernels_agree(mods, fmt, M, N, K):
+    # the CTA-pair kernel (the default above 128 rows) and the single-CTA kernel with 128- and 64-column tiles
+    # issue the same MMAs in the same order over K: identical bits, and within tolerance of the oracle
+    fp4, mg = mods
+    from lockstep_b200 import nvfp4
+    from lockstep_b200._lib import lib
+    from oracle import nvfp4_ref
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+    if fmt == "mx16":
+        pa, sfa = fp4.quantize_mxfp4_packed(a, block=16)
+        pw, sfw = fp4.quantize_mxfp4_packed(w, block=16)
+        run = lambda: mg.mxfp4_gemm_packed(pa, pw, sfa, sfw, out_dtype=torch.float32, block=16)
+        ac, asc = ref_port.quantize(a.cpu(), block=16)
+        wc, wsc = ref_port.quantize(w.cpu(), block=16)
+        ref = torch.nn.functional.linear(ref_port.dequantize(ac, asc, 16), ref_port.dequantize(wc, wsc, 16))
+    else:
+        pa, _, sfa = nvfp4.quantize_nvfp4(a)
+        pw, _, sfw = nvfp4.quantize_nvfp4(w)
+        run = lambda: nvfp4.nvfp4_gemm_packed(pa, pw, sfa, sfw, out_dtype=torch.float32)
+        ac, asc = nvfp4_ref.quantize(a.float().cpu().numpy())
+        wc, wsc = nvfp4_ref.quantize(w.float().cpu().numpy())
+        ref = torch.nn.functional.linear(torch.from_numpy(nvfp4_ref.dequantize(ac, asc)),
+                                         torch.from_numpy(nvfp4_ref.dequantize(wc, wsc)))
+    outs = {}
+    try:
+        for variant in (2, 3, 5):
+            lib().ls_gemm_set_variant(variant)
+            outs[variant] = run()
+    finally:
+        lib().ls_gemm_set_variant(0)
+    mg.gemm_status()
+    _check(outs[2], ref, f"{fmt} pair kernel {M} x {N} x {K}")
+    assert torch.equal(outs[2], outs[3]) and torch.equal(outs[2], outs[5])
