@@ -492,7 +492,7 @@ def main():
     # scales; this torch build has no MXFP4 recipe) on 8192^3, the same FLOPs as one dual launch.
     import ctypes
     from lockstep_b200 import _lib
-    sus, ceil, trip = [], {}, {"mma_only": [], "cublaslt": []}
+    sus, ceil, trip = [], {}, {"mma_only": [], "cublaslt": [], "own_nvfp4": []}
     if not args.no_sustained:
         L = _lib.lib()
         flop = ctypes.c_double()
@@ -507,6 +507,13 @@ def main():
                 lib_args = (la, lb.t(), lsa, lsb)
             except Exception as e:                           # not offered by this build / device
                 ceil["cublaslt_nvfp4_error"] = repr(e)[:200]
+            # this library's NVFP4 GEMM on the shape and operand format of the cuBLASLt call
+            from lockstep_b200 import nvfp4
+            own = (torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev),
+                   torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev),
+                   torch.randint(0x30, 0x40, (fp4.sf_bytes(N, K, 16),), dtype=torch.uint8, device=dev),
+                   torch.randint(0x30, 0x40, (fp4.sf_bytes(N, K, 16),), dtype=torch.uint8, device=dev))
+            nvfp4.nvfp4_gemm_packed(*own)
             _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream()))
             torch.cuda.synchronize()
 
@@ -526,14 +533,17 @@ def main():
                 time_one(lambda: _lib.check(L.ls_fp4_mma_peak(600, ctypes.byref(flop), _lib.stream())), "mma_only")
                 if lib_args:
                     time_one(lambda: torch._scaled_mm(*lib_args, out_dtype=torch.bfloat16), "cublaslt")
+                time_one(lambda: nvfp4.nvfp4_gemm_packed(*own), "own_nvfp4")
         barrier()
         med = {k: sorted(a.elapsed_time(b) for a, b in v)[len(v) // 2] for k, v in trip.items() if v}
         if "mma_only" in med:
             ceil["mma_only_tflops"] = flop.value / med["mma_only"] / 1e9
             ceil["how"] = (f"inside the sustained region: after every 8th step one MMA-only launch ({len(trip['mma_only'])} in all) "
-                           "and one cuBLASLt NVFP4 8192^3 GEMM, each after an L2 flush; medians")
+                           "one cuBLASLt NVFP4 8192^3 GEMM and this library's NVFP4 GEMM of the same shape, each after an L2 flush; medians")
         if "cublaslt" in med:
             ceil["cublaslt_nvfp4_tflops"] = 2 * N * N * K / med["cublaslt"] / 1e9
+        if "own_nvfp4" in med:
+            ceil["own_nvfp4_tflops"] = 2 * N * N * K / med["own_nvfp4"] / 1e9
         del lib_args
     clocks = sampler.stop() if sampler else None
     mxfp4_gemm.gemm_status()

@@ -183,7 +183,7 @@ int ls_mxfp4_gemm_dual_block16(const uint8_t *a1_pk, const uint8_t *a2_pk, const
  * :57-69 quant_e2m1_code, applied per block as rig_q.cu:348-363) but has no kernel for it.
  *   scale = E4M3(amax / 6) (half-even, saturating at 448; 2^-9 where that is 0; 1.0 for a block
  *   with no positive maximum), code = E2M1 nearest to v / scale, ties to the smaller magnitude.
- *   x         [rows, K] LS_F32 or LS_BF16, 16-byte aligned;  K % 128 == 0
+ *   x         [rows, K] LS_F32 or LS_BF16, 32-byte aligned;  K % 128 == 0
  *   packed    [rows, K/2]
  *   scale_u8  [rows, K/16] E4M3 bytes, or NULL;  scale_f32 the same scales as fp32, or NULL
  *   sf        the scale bytes in the scale-factor layout (ls_sf_bytes_block(rows, K, 16)), or NULL */

@@ -105,7 +105,7 @@ def main():
             blk *= v / (np.abs(blk).max() * 1.01)
             blk[rng.integers(0, 16)] = v
     rows.append(t)
-    t = np.zeros((16, 128), np.float32)
+    t = np.zeros((18, 128), np.float32)
     t[1] = rng.standard_normal(128) * 1e-4
     t[2] = rng.standard_normal(128) * 1e-6
     t[3] = rng.standard_normal(128) * 1e5
@@ -119,6 +119,10 @@ def main():
     t[11, 17] = 1e-38
     t[12] = 448 * 6
     t[13] = rng.uniform(-6, 6, 128) * 448
+    t[14] = rng.standard_normal(128) * np.exp2(rng.uniform(20, 40, 128))       # quotients around and beyond 2^23:
+    t[15] = rng.standard_normal(128) * 1e30                                     # the candidate loop's distances collapse
+    t[16] = np.exp2(rng.integers(28, 36, 128)) * rng.choice([-1, 1, 1.5, -1.25], 128)
+    t[17, :16] = 3e38; t[17, 3] = -3.4e38
     rows.append(t)
     x = np.concatenate(rows).astype(np.float32)
     c, s, d = blocks(lib, x)

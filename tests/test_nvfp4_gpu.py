@@ -148,3 +148,20 @@ def test_nvfp4_is_closer_to_the_unquantized_product_than_mxfp4(mods):
     e_nv = ((nv.nvfp4_gemm_packed(pa, pw, sfa, sfw, out_dtype=torch.float32) - exact).norm() / exact.norm()).item()
     mg.gemm_status()
     assert e_nv < e_mx, (e_nv, e_mx)
+
+
+def test_quantizer_on_every_bf16_pattern(mods):
+    # all 65536 bf16 bit patterns (zeros, subnormals, infinities, NaNs included), in order (neighbours of like
+    # magnitude: realistic scales) and in blocks that mix a few binades; bf16 input and the same values as fp32
+    fp4, nv, _ = mods
+    bits = torch.arange(65536, dtype=torch.int32)
+    ordered = (bits << 16).view(torch.float32).reshape(32, 2048)
+    g = torch.Generator().manual_seed(1)
+    near = bits.reshape(-1, 256)[:, torch.randperm(256, generator=g)].reshape(-1)        # shuffled within +-2 binades
+    mixed = (near << 16).view(torch.float32).reshape(32, 2048)
+    for x in (ordered, mixed):
+        codes, want_scale = R.quantize(x.numpy())
+        for dt in (torch.bfloat16, torch.float32):
+            packed, scale, _ = nv.quantize_nvfp4(x.cuda().to(dt))
+            assert np.array_equal(scale.cpu().numpy().view(np.uint32), want_scale.view(np.uint32)), dt
+            assert np.array_equal(fp4.unpack_fp4(packed).cpu().numpy(), codes), dt
