@@ -220,41 +220,59 @@ def run_sweep(m_list=(1, 16, 128, 4096, 16384), nk_list=(4096, 8192, 16384)):
     return lines
 
 
-def run_shape(m, n, k, out_f32, steps):
-    """One shape of the single MXFP4 GEMM: `steps` launches replayed from a CUDA graph
+def run_shape(m, n, k, out_f32, steps, fmt="mxfp4"):
+    """One shape of the single FP4 GEMM: `steps` launches replayed from a CUDA graph
     (device time rather than launch overhead), timed with CUDA events after a 256 MiB
-    write that flushes L2."""
-    from lockstep_b200 import fp4, mxfp4_gemm
+    write that flushes L2.  fmt: "mxfp4" (blocks of 32), "mxfp4-b16" (blocks of 16, UE8M0
+    scales) or "nvfp4" (blocks of 16, E4M3 scales).  The quantizer of A (bf16 in) is timed too,
+    one launch at a time after the same flush."""
+    from lockstep_b200 import fp4, mxfp4_gemm, nvfp4
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
     w = (torch.randn(n, k, device=dev, generator=g) * 0.02).bfloat16()
     a = torch.randn(m, k, device=dev, generator=g).bfloat16()
-    w_pk, w_sf = fp4.quantize_mxfp4_packed(w)
-    a_pk, a_sf = fp4.quantize_mxfp4_packed(a)
     dt = torch.float32 if out_f32 else torch.bfloat16
+    if fmt == "nvfp4":
+        quant = lambda t: nvfp4.quantize_nvfp4(t)[::2]
+        gemm = lambda: nvfp4.nvfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf, dt)
+        scale_bytes = 1 / 16 + 4 / 16                             # scale-factor bytes + the fp32 scales
+    else:
+        block = 16 if fmt == "mxfp4-b16" else 32
+        quant = lambda t: fp4.quantize_mxfp4_packed(t, block=block)
+        gemm = lambda: mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf, dt, block=block)
+        scale_bytes = 1 / block
+    w_pk, w_sf = quant(w)
+    a_pk, a_sf = quant(a)
     for _ in range(3):
-        mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf, dt)
+        gemm()
     graph = torch.cuda.CUDAGraph()
     torch.cuda.synchronize()
     with torch.cuda.graph(graph):
         for _ in range(steps):
-            c = mxfp4_gemm.mxfp4_gemm_packed(a_pk, w_pk, a_sf, w_sf, dt)
+            c = gemm()
     graph.replay()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    best = float("inf")
+    best, qbest = float("inf"), float("inf")
     for _ in range(3):
         flush.fill_(1)
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         graph.replay()
         t1.record()
+        flush.fill_(1)
+        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        q0.record()
+        quant(a)
+        q1.record()
         torch.cuda.synchronize()
         best = min(best, t0.elapsed_time(t1) / steps)
+        qbest = min(qbest, q0.elapsed_time(q1))
     del graph, c
     mxfp4_gemm.gemm_status()
-    print(json.dumps({"shape": [m, n, k], "out": "f32" if out_f32 else "bf16", "steps": steps, "us": best * 1e3,
+    print(json.dumps({"shape": [m, n, k], "format": fmt, "out": "f32" if out_f32 else "bf16", "steps": steps, "us": best * 1e3,
                       "tflops": 2 * m * n * k / best / 1e9,
-                      "out_gbs": m * n * (4 if out_f32 else 2) / best / 1e6}), flush=True)
+                      "out_gbs": m * n * (4 if out_f32 else 2) / best / 1e6,
+                      "quantize_a_us": qbest * 1e3, "quantize_a_gbs": m * k * (2 + 0.5 + scale_bytes) / qbest / 1e6}), flush=True)
 
 
 def wire_leg(args, dev, rank, world, barrier, pk):
@@ -403,6 +421,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="shape sweep of the single GEMM instead of the benchmark step")
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="time one shape of the single GEMM instead")
     ap.add_argument("--out-f32", action="store_true", help="with --shape: fp32 output instead of bf16")
+    ap.add_argument("--format", default="mxfp4", choices=["mxfp4", "mxfp4-b16", "nvfp4"],
+                    help="with --shape: operand format (scale blocks of 32, of 16 with UE8M0 scales, of 16 with E4M3 scales)")
     args = ap.parse_args()
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
 
@@ -412,7 +432,7 @@ def main():
     if args.sweep or args.shape:
         if rank == 0:
             if args.shape:
-                run_shape(*args.shape, args.out_f32, min(args.steps, 50))
+                run_shape(*args.shape, args.out_f32, min(args.steps, 50), args.format)
             else:
                 for line in run_sweep():
                     print(json.dumps(line), flush=True)

@@ -55,6 +55,30 @@ def test_gemm_argument_errors(L):
     assert L.ls_gemm_set_splits(17) == EINVAL and L.ls_gemm_set_splits(0) == 0
 
 
+def test_block16_and_nvfp4_argument_errors(L):
+    a = torch.zeros(128 * 64, device="cuda", dtype=torch.uint8)
+    c = torch.zeros(128 * 128, device="cuda", dtype=torch.bfloat16)
+    x = torch.zeros(4, 128, device="cuda", dtype=torch.bfloat16)
+    for fn in (L.ls_mxfp4_gemm_block16, L.ls_nvfp4_gemm):
+        assert fn(_p(a), _p(a), _p(a), _p(a), _p(c), 1, 128, 128, 96, None) == EINVAL             # K % 128
+        assert fn(_p(a), _p(a), _p(a), _p(a), _p(c), 5, 128, 128, 128, None) == EINVAL            # output type
+        assert fn(_p(a), _p(a), None, _p(a), _p(c), 1, 128, 128, 128, None) == EINVAL             # null scales
+        assert fn(_p(a), _p(a, 4), _p(a), _p(a), _p(c), 1, 128, 128, 128, None) == EALIGN
+        assert fn(_p(a), _p(a), _p(a), _p(a), _p(c), 1, 128, 0, 128, None) == 0                   # N = 0
+    for fn in (L.ls_mxfp4_gemm_dual_block16, L.ls_nvfp4_gemm_dual):
+        assert fn(_p(a), None, _p(a), _p(a), _p(a), _p(a), _p(c), _p(c), 1, 128, 128, 128, None) == EINVAL
+    assert L.ls_sf_bytes_block(130, 256, 16) == 2 * 4 * 512 and L.ls_sf_bytes_block(130, 256, 32) == L.ls_sf_bytes(130, 256)
+    assert L.ls_sf_bytes_block(130, 256, 8) == -1 and L.ls_sf_bytes_block(130, 100, 16) == -1
+    assert L.ls_scales_to_sf_block(_p(c), 4, 128, 8, _p(a), None, None) == EINVAL                 # block
+    assert L.ls_quantize_nvfp4(_p(x), 1, 4, 64, _p(a), None, None, None, None) == EINVAL          # K % 128
+    assert L.ls_quantize_nvfp4(_p(x), 9, 4, 128, _p(a), None, None, None, None) == EINVAL         # dtype
+    assert L.ls_quantize_nvfp4(_p(x), 1, 4, 128, None, None, None, None, None) == EINVAL          # packed is required
+    assert L.ls_quantize_nvfp4(_p(x, 16), 1, 2, 128, _p(a), None, None, None, None) == EALIGN     # 32-byte loads
+    assert L.ls_quantize_nvfp4(_p(x), 1, 0, 128, None, None, None, None, None) == 0               # empty
+    assert L.ls_dequantize_nvfp4(_p(a), _p(a), 4, 24, _p(c), 1, None) == EINVAL                   # K % 16
+    assert L.ls_dequantize_nvfp4(_p(a), None, 4, 128, _p(c), 1, None) == EINVAL
+
+
 def test_wire_argument_errors(L):
     h = ctypes.c_void_p()
     assert L.ls_wire_create(0, 9, 9 * 256, ctypes.byref(h)) == EINVAL             # at most 8 ranks
