@@ -33,7 +33,15 @@ struct Nvfp4Out {
     uint8_t *sf;           // scale-factor layout, or NULL
     uint32_t kblocks;      // K / 16
     uint32_t nblocks;      // rows * kblocks
+    uint32_t div_mul, div_shift;   // row = block / kblocks by multiply-shift
 };
+
+// floor(b / kblocks) for any 32-bit b: t = hi(b * mul); q = (t + ((b - t) >> 1)) >> shift
+__device__ __forceinline__ uint32_t row_of(const Nvfp4Out &o, uint32_t b)
+{
+    const uint32_t t = __umulhi(b, o.div_mul);
+    return (t + ((b - t) >> 1)) >> o.div_shift;
+}
 
 __device__ __forceinline__ uint32_t e4m3_byte_sat(float a)      // a >= 0, not NaN
 {
@@ -248,7 +256,7 @@ nvfp4_quantize_kernel(const T *__restrict__ x, Nvfp4Out o)
     if (in_range && (threadIdx.x & 3) == 0) {
         if (o.scale_u8) *reinterpret_cast<uint32_t *>(o.scale_u8 + blk) = w;
         if (o.sf) {
-            const uint32_t row = blk / o.kblocks, kb = blk - row * o.kblocks;
+            const uint32_t row = row_of(o, blk), kb = blk - row * o.kblocks;
             *reinterpret_cast<uint32_t *>(o.sf + sf_offset(row, kb, o.kblocks / 4)) = w;
         }
     }
@@ -309,7 +317,13 @@ extern "C" int ls_quantize_nvfp4(const void *x, int x_dtype, int64_t rows, int64
         (reinterpret_cast<uintptr_t>(scale_u8) & 3) || (reinterpret_cast<uintptr_t>(scale_f32) & 3) ||
         (reinterpret_cast<uintptr_t>(sf) & 3))
         return fail(LS_EALIGN, "x must be 32-byte, packed 8-byte, scale buffers 4-byte aligned");
-    Nvfp4Out o{packed, scale_u8, scale_f32, sf, uint32_t(K / 16), uint32_t(n / 16)};
+    Nvfp4Out o{packed, scale_u8, scale_f32, sf, uint32_t(K / 16), uint32_t(n / 16), 0u, 0u};
+    {   // multiply-shift division by kblocks (>= 8 here)
+        uint32_t d = o.kblocks, sh = 0;
+        while ((1ull << sh) < d) sh++;
+        o.div_mul = uint32_t(((1ull << 32) * ((1ull << sh) - d)) / d + 1);
+        o.div_shift = sh - 1;
+    }
     const int grid = int((o.nblocks + kThreads * kBlocksPerThread - 1) / (kThreads * kBlocksPerThread));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (x_dtype == LS_BF16) nvfp4_quantize_kernel<<<grid, kThreads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), o);
