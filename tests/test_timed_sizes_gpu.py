@@ -12,6 +12,9 @@ here at full size:
   {4096, 8192, 16384} (1 % outliers x 50 in the activations) on sampled rows
   and sampled output columns that cover the first and last tiles and the
   128 / 256-column tile edges;
+* the GEMM on operands with scale blocks of 16 (UE8M0 scales, and E4M3 scales =
+  NVFP4) at 8192 x 8192 x 8192, the shape their timings are quoted on, on
+  sampled rows and columns against the oracles' dequantize + fp32 matmul;
 * one 64 Mi-element step sequence of the FP4 wire with error feedback at world
   size 1 (32-bit group indices near their top, the multi-CTA-per-SM grids,
   the tail logic of the decode kernel), bit for bit against the C oracle.
@@ -115,6 +118,45 @@ def test_shape_sweep_cell_vs_oracle(mods, M, NK):
     wc, wsc = ref_port.quantize(w[cols.cuda()].cpu())
     ref = ref_port.gemm_fake_quant(ac, asc, wc, wsc)
     _check(c[rows.cuda()][:, cols.cuda()], ref, f"sweep cell {M} x {NK} x {NK}")
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4-b16", "nvfp4"])
+def test_block16_formats_at_the_timed_size_vs_oracle(mods, fmt):
+    # 8192 x 8192 x 8192, the shape `bench.py --shape ... --format` and the benchmark's own NVFP4 comparison time:
+    # the CTA-pair kernel with 64 shared accumulator columns, every row-tile pair and column tile of it sampled
+    fp4, mg, _ = mods
+    from lockstep_b200 import nvfp4
+    from oracle import nvfp4_ref
+    M = N = K = 8192
+    g = torch.Generator(device="cuda").manual_seed(16)
+    a = torch.randn(M, K, device="cuda", generator=g)
+    a = torch.where(torch.rand(M, K, device="cuda", generator=g) < 0.01, a * 50, a).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+    cg = torch.Generator().manual_seed(7)
+    rows = _tile_rows(M, 0, cg)
+    rows = rows[torch.randperm(rows.numel(), generator=cg)[:96]].sort().values
+    rows = torch.cat([torch.tensor([0, 127, 128, 255, 256, M - 257, M - 256, M - 1]), rows]).unique()
+    edge = [0, 1, 31, 32, 127, 128, 191, 192, 223, 224, 255, 256, 257, 447, 448, 511, 512, N - 257, N - 256, N - 65, N - 64, N - 1]
+    cols = torch.tensor(sorted(set(edge + torch.randint(0, N, (234,), generator=cg).tolist())))
+    if fmt == "nvfp4":
+        pa, _, sfa = nvfp4.quantize_nvfp4(a)
+        pw, _, sfw = nvfp4.quantize_nvfp4(w)
+        c = nvfp4.nvfp4_gemm_packed(pa, pw, sfa, sfw)
+        ac, asc = nvfp4_ref.quantize(a[rows.cuda()].float().cpu().numpy())
+        wc, wsc = nvfp4_ref.quantize(w[cols.cuda()].float().cpu().numpy())
+        assert np.array_equal(fp4.unpack_fp4(pa[rows.cuda()]).cpu().numpy(), ac)
+        ref = torch.nn.functional.linear(torch.from_numpy(nvfp4_ref.dequantize(ac, asc)),
+                                         torch.from_numpy(nvfp4_ref.dequantize(wc, wsc))).to(torch.bfloat16)
+    else:
+        pa, sfa = fp4.quantize_mxfp4_packed(a, block=16)
+        pw, sfw = fp4.quantize_mxfp4_packed(w, block=16)
+        c = mg.mxfp4_gemm_packed(pa, pw, sfa, sfw, block=16)
+        ac, asc = ref_port.quantize(a[rows.cuda()].cpu(), block=16)
+        wc, wsc = ref_port.quantize(w[cols.cuda()].cpu(), block=16)
+        assert torch.equal(fp4.unpack_fp4(pa[rows.cuda()]).cpu(), ac)
+        ref = torch.nn.functional.linear(ref_port.dequantize(ac, asc, 16), ref_port.dequantize(wc, wsc, 16)).to(torch.bfloat16)
+    mg.gemm_status()
+    _check(c[rows.cuda()][:, cols.cuda()], ref, f"{fmt} 8192^3")
 
 
 def test_sweep_weights_released():
