@@ -119,6 +119,40 @@ class MXFP4Linear(nn.Linear):
 FP4Linear = MXFP4Linear
 
 
+class _NVFP4Matmul(torch.autograd.Function):
+    """x @ w.T with both operands in NVFP4 (blocks of 16 along K under E4M3 scales); straight-through backward as
+    fp4_linear.py:42-45."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from . import nvfp4
+        _need_kernel()
+        ctx.save_for_backward(x, w)
+        px, _, sx = nvfp4.quantize_nvfp4(x)
+        pw, _, sw = nvfp4.quantize_nvfp4(w)
+        return nvfp4.nvfp4_gemm_packed(px, pw, sx, sw, out_dtype=x.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        return (gy @ w.to(gy.dtype)).to(x.dtype), (gy.t() @ x.to(gy.dtype)).to(w.dtype)
+
+
+class NVFP4Linear(nn.Linear):
+    """(extension) MXFP4Linear's counterpart in the NVFP4 format that lockstep's format study defines
+    (rig_sm75/quant_sim.cuh:90-97) but has no layer for.  fan_in % 128 == 0; no bias."""
+
+    def __init__(self, fan_in, fan_out, bias=False):
+        assert not bias, "NVFP4Linear has no bias"
+        super().__init__(fan_in, fan_out, bias=False)
+
+    def forward(self, x):
+        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+        with torch.autocast("cuda", enabled=False):
+            y = _NVFP4Matmul.apply(x.reshape(-1, x.shape[-1]).to(dt), self.weight)
+        return y.view(*x.shape[:-1], -1)
+
+
 def _ln_backward(g_y, x, mean, rstd, gamma, beta):
     """LayerNorm's backward from the statistics the fused forward kept (torch's kernel)."""
     rows, D = x.shape

@@ -200,3 +200,30 @@ def test_norm_fused_modules_match_the_unfused_composition(mode):
     _close(fused_m.fc.weight.grad, fc.weight.grad, "norm + mlp dW fc", tol)
     _close(fused_m.out.weight.grad, out.weight.grad, "norm + mlp dW out", tol)
     _close(fused_m.norm.weight.grad, norm_m.weight.grad, "norm + mlp dgamma", tol)
+
+
+def test_nvfp4_linear_forward_and_straight_through_backward():
+    # forward: the oracle's NVFP4 quantization of x and w (lockstep's format rules), dequantized, fp32 matmul,
+    # cast; backward: the straight-through matmuls of fp4_linear.py:42-45 on the unquantized tensors
+    from lockstep_b200 import fp4_linear
+    from oracle import nvfp4_ref
+    g = torch.Generator().manual_seed(21)
+    lin = fp4_linear.NVFP4Linear(256, 160).cuda()
+    w = torch.randn(160, 256, generator=g) * 0.05
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    x = (torch.randn(4, 24, 256, generator=g) * torch.exp2(torch.randint(-3, 4, (4, 24, 1), generator=g).float())).bfloat16()
+    xg = x.cuda().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = lin(xg)
+    assert y.shape == (4, 24, 160) and y.dtype == torch.bfloat16
+    xc, xs = nvfp4_ref.quantize(x.float().reshape(-1, 256).numpy())
+    wc, ws = nvfp4_ref.quantize(w.numpy())                              # the layer quantizes its fp32 weight
+    ref = torch.nn.functional.linear(torch.from_numpy(nvfp4_ref.dequantize(xc, xs)),
+                                     torch.from_numpy(nvfp4_ref.dequantize(wc, ws))).bfloat16()
+    _close(y.reshape(-1, 160), ref, "NVFP4 forward")
+    gy = torch.randn(4, 24, 160, generator=g).bfloat16()
+    y.backward(gy.cuda())
+    gx_ref, gw_ref = ref_port.linear_backward_ste(gy.reshape(-1, 160), x.reshape(-1, 256), w)
+    _close(xg.grad.reshape(-1, 256), gx_ref, "NVFP4 dX", 1e-2)      # bf16 matmuls, different GEMM library
+    _close(lin.weight.grad, gw_ref, "NVFP4 dW", 1e-2)

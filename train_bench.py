@@ -27,6 +27,8 @@ def make_linear(kind):
     from lockstep_b200 import fp4_linear
     if kind == "dense":
         return lambda fan_in, fan_out: nn.Linear(fan_in, fan_out, bias=False)
+    if kind == "nvfp4":
+        return lambda fan_in, fan_out: fp4_linear.NVFP4Linear(fan_in, fan_out, bias=False)
     return lambda fan_in, fan_out: fp4_linear.MXFP4Linear(fan_in, fan_out, bias=False, backward=kind)
 
 
@@ -76,7 +78,7 @@ def make_parts(kind, fused):
     kind "mxfp4" the feed-forward half keeps its activation in MXFP4 between its two GEMMs."""
     from lockstep_b200 import fp4_linear
     linear = make_linear(kind)
-    if fused and kind != "dense":
+    if fused and kind not in ("dense", "nvfp4"):
         return (linear,
                 lambda width, out: fp4_linear.MXFP4NormLinear(width, out, backward=kind),
                 lambda width: fp4_linear.MXFP4MLP(width, 4 * width, backward=kind, norm=True))
@@ -240,7 +242,7 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
     sync after the backward pass against the bucketed sync that sends under it."""
     out = {}
     runs = (("dense", "dense", False), ("ste", "ste", True), ("ste_unfused", "ste", False), ("mxfp4", "mxfp4", True),
-            ("mxfp4_unfused", "mxfp4", False)) if world == 1 else (("mxfp4", "mxfp4", True),)
+            ("mxfp4_unfused", "mxfp4", False), ("nvfp4_ste_unfused", "nvfp4", False)) if world == 1 else (("mxfp4", "mxfp4", True),)
     for name, kind, fused in runs:
         torch.cuda.empty_cache()
         t = Trainer(kind, device=device, world=world, rank=rank, fused=fused)
