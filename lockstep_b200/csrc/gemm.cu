@@ -787,8 +787,21 @@ using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, vo
                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// cuTensorMapEncodeTiled is a driver entry point and wants a current context.  A host thread
+// that has only made calls that do not need one (cudaGetDevice) has none bound yet, and the
+// encode fails with CUDA_ERROR_INVALID_CONTEXT; cudaSetDevice binds the device's primary
+// context to the calling thread.  Once per thread.
+void bind_primary_context()
+{
+    static thread_local bool bound = false;
+    if (bound) return;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) bound = true;
+}
+
 EncodeFn encode_fn()
 {
+    bind_primary_context();
     static EncodeFn fn = [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
@@ -1134,7 +1147,13 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
         p.kt_per_split = (k_tiles + s - 1) / s;
         p.splits = (k_tiles + p.kt_per_split - 1) / p.kt_per_split;
     }
+    // The scratch of a device has one user at a time: the next user's stream waits for the event
+    // recorded after this one's summation.  Calls from several host threads must not interleave
+    // between that wait and that record, hence the lock over the (asynchronous) launches.
+    static std::mutex split_calls;
+    std::unique_lock<std::mutex> split_lk;
     if (p.splits > 1) {
+        split_lk = std::unique_lock<std::mutex>(split_calls);
         p.partial = splitk_acquire(size_t(p.splits) * nbatch * M * N * sizeof(float), static_cast<cudaStream_t>(stream));
         if (!p.partial) return fail(LS_ECUDA, "could not allocate split-K scratch");
     }

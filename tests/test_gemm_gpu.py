@@ -382,3 +382,47 @@ def test_mma_only_ceiling_kernel_runs_and_counts_its_flops(mods):
     tflops = flop.value / (a.elapsed_time(b) * 1e-3) / 1e12
     assert 1000 < tflops < 9500, tflops                      # between a bf16-class rate and the dense FP4 spec
     assert L.ls_fp4_mma_peak(0, None, None) < 0
+
+
+def test_split_k_on_two_streams_and_two_host_threads(mods):
+    # The split-K scratch is one buffer per device.  Products with forced K splits issued alternately on two
+    # streams, and from two host threads at once, give the bits of the same products issued one after another.
+    import threading
+    fp4, mg, _ = mods
+    from lockstep_b200._lib import lib
+    g = torch.Generator(device="cuda").manual_seed(31)
+    shapes = [(128, 512, 4096), (100, 300, 2304)]
+    ops = []
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+        ops.append((*fp4.quantize_mxfp4_packed(a), *fp4.quantize_mxfp4_packed(w)))
+    run = lambda o: mg.mxfp4_gemm_packed(o[0], o[2], o[1], o[3], out_dtype=torch.float32)
+    try:
+        lib().ls_gemm_set_variant(1)
+        lib().ls_gemm_set_splits(4)
+        want = [run(o) for o in ops]
+        torch.cuda.synchronize()
+        streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+        got = [[], []]
+        for it in range(40):                                   # one host thread, alternating streams
+            i = it & 1
+            with torch.cuda.stream(streams[i]):
+                got[i].append(run(ops[i]))
+        torch.cuda.synchronize()
+        assert all(torch.equal(c, want[i]) for i in (0, 1) for c in got[i])
+
+        def worker(i, out):
+            with torch.cuda.stream(streams[i]):
+                for _ in range(40):
+                    out.append(run(ops[i]))
+        outs = [[], []]
+        ts = [threading.Thread(target=worker, args=(i, outs[i])) for i in (0, 1)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        torch.cuda.synchronize()
+        assert all(len(outs[i]) == 40 and all(torch.equal(c, want[i]) for c in outs[i]) for i in (0, 1))
+    finally:
+        lib().ls_gemm_set_variant(0)
+        lib().ls_gemm_set_splits(0)
+    mg.gemm_status()
