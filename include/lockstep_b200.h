@@ -231,8 +231,10 @@ int ls_scales_to_sf_t(const float *scale, int64_t rows, int64_t K, uint8_t *sf, 
 
 /* Which GEMM kernel the two entry points above launch: 0 = by shape (default),
  * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles
- * (cta_group::2), 3 / 5 = one CTA per 128 x 128 / 128 x 64 tile.  Results are
- * identical; for measurements and tests. */
+ * (cta_group::2), 3 / 5 = one CTA per 128 x 128 / 128 x 64 tile, 6 = CTA pairs
+ * on 256 x 192 tiles (accumulators that share no tensor-memory columns).
+ * Results are identical; for measurements and tests.  The block-16 and NVFP4
+ * entry points follow it too (1 there means 128-column tiles). */
 int ls_gemm_set_variant(int variant);
 
 /* Measurement aid, no reference counterpart: launches a kernel that issues only

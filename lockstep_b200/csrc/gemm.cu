@@ -534,23 +534,26 @@ splitk_reduce_kernel(const float *__restrict__ partial, void *__restrict__ out, 
 // load of either CTA completes on CTA 0's barrier).  Warp 1 lane of CTA 0: the
 // MMA issuer for the pair (warp 1 of CTA 1 only takes part in the tensor-memory
 // allocation).  Warps 2-9: epilogue, two warps per quarter of the rows.
-template <int VS>
+template <int VS, int BNP = 256>
 struct PairCfg {
     static constexpr int SFT = 32 / VS;                    // scale tiles per 128 elements of K
-    static constexpr int BN = 256;                         // tile columns (128 rows of W per CTA)
-    static constexpr int STAGES = VS == 32 ? 6 : 5;
+    static constexpr int BN = BNP;                         // tile columns (BN / 2 rows of W per CTA): 256 or 192
+    static_assert(BN == 256 || BN == 192, "tile widths: 256 or 192");
     static constexpr int A_BYTES = BM * BKB;               // 16 KB
-    static constexpr int B_BYTES = 128 * BKB;              // this CTA's half of the W tile
+    static constexpr int B_BYTES = (BN / 2) * BKB;         // this CTA's half of the W tile
     static constexpr int SFA_BYTES = 1024 * SFT;
-    static constexpr int SFB_BYTES = 2048 * SFT;           // scales of all 256 W rows, in both CTAs
+    static constexpr int SFB_BYTES = 2048 * SFT;           // scales of the two 128-row scale tiles the W tile touches, in both CTAs
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    // Tensor memory: accumulators [0,256) and [224,480) share 32 columns; scale columns
-    // at 480 (8 for A, 16 for W).  A second set of scale columns (tried with a 64-column
+    static constexpr int STAGES = (227 * 1024 - 1024 - 256) / STAGE_BYTES;    // 6 (5 with scales per 16); 7 (6) at 192 columns
+    // Tensor memory, 256-column tiles: accumulators [0,256) and [224,480) share 32 columns; scale
+    // columns at 480 (8 for A, 16 for W).  A second set of scale columns (tried with a 64-column
     // overlap) did not speed the kernel up.  Scales per 16 elements take 48 columns: the
     // accumulators then share 64 columns, [0,256) and [192,448).
-    static constexpr int OVL = VS == 32 ? 32 : 64;
+    // 192-column tiles: [0,192) and [192,384) share nothing, and the MMAs of a tile can start
+    // while the tile before it is still being read out.
+    static constexpr int OVL = BN == 192 ? 0 : VS == 32 ? 32 : 64;
     static constexpr int ACC1 = BN - OVL;                  // 224 (192)
-    static constexpr int SF_COL = 2 * BN - OVL;            // 480 (448)
+    static constexpr int SF_COL = 2 * BN - OVL;            // 480 (448, 384)
     static_assert(SF_COL + 24 * SFT <= kTmemCols, "tensor memory overflow");
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
     static_assert(SMEM <= 227 * 1024, "shared memory overflow");
@@ -567,14 +570,14 @@ __device__ __forceinline__ uint32_t cluster_ctarank()
     return r;
 }
 
-template <int VS>
+template <int VS, int BNP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_sfa0,
                        const __grid_constant__ CUtensorMap tm_sfa1, const __grid_constant__ CUtensorMap tm_sfb,
                        const GemmParams p)
 {
-    using C = PairCfg<VS>;
+    using C = PairCfg<VS, BNP>;
     constexpr int SFT = C::SFT;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -582,11 +585,11 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (C::STAGES + s); };
     const uint32_t acc_full_bar = bar_base + 8u * (2 * C::STAGES);
-    const uint32_t acc_free_bar = acc_full_bar + 8u;                                    // used in CTA 0
-    const uint32_t tmem_slot = acc_free_bar + 8u;
+    const uint32_t acc_free_bar = acc_full_bar + 8u;                                    // used in CTA 0; a second one follows it
+    const uint32_t tmem_slot = acc_free_bar + 16u;
     uint8_t *gen_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
     volatile uint32_t *tmem_slot_p =
-        reinterpret_cast<volatile uint32_t *>(gen_base + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 2));
+        reinterpret_cast<volatile uint32_t *>(gen_base + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 3));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot_p + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -610,6 +613,7 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
         }
         ptx::mbar_init(acc_full_bar, 1);
         ptx::mbar_init(acc_free_bar, 16);                   // 8 epilogue warps of each CTA
+        ptx::mbar_init(acc_free_bar + 8u, 16);              // accumulators that share nothing: one barrier each
         *abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -653,12 +657,13 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                     const uint32_t bar = ptx::map_to_cta(full_bar(s), 0);
                     if (cta == 0) ptx::mbar_expect_tx(full_bar(s), 2 * C::STAGE_BYTES);
                     ptx::tma_load_2d_pair(st, tma, kt * BKB, mt * BM, bar);
-                    ptx::tma_load_2d_pair(st + C::A_BYTES, &tm_b, kt * BKB, nt * C::BN + int(cta) * 128, bar);
+                    ptx::tma_load_2d_pair(st + C::A_BYTES, &tm_b, kt * BKB, nt * C::BN + int(cta) * (C::BN / 2), bar);
                     ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES, tsfa, 0, (mt * k_atoms + 2 * kt) * SFT, bar);
+                    const int sfb_tile0 = nt * C::BN / 128;       // first of the two 128-row scale tiles of W under this tile
                     ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES, &tm_sfb, 0,
-                                          ((2 * nt) * k_atoms + 2 * kt) * SFT, bar);
+                                          (sfb_tile0 * k_atoms + 2 * kt) * SFT, bar);
                     ptx::tma_load_2d_pair(st + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + 1024 * SFT, &tm_sfb, 0,
-                                          ((2 * nt + 1) * k_atoms + 2 * kt) * SFT, bar);
+                                          ((sfb_tile0 + 1) * k_atoms + 2 * kt) * SFT, bar);
                     if (++s == C::STAGES) s = 0, ph ^= 1;
                 }
             }
@@ -678,10 +683,18 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             uint32_t ph = 0;
             bool ok = true;
             for (int t = pair; t < total && ok; t += npairs, lt++) {
-                if (lt > 0 && !(ok = ptx::mbar_wait(acc_free_bar, (lt - 1) & 1, abort_flag))) break;
+                if (C::OVL > 0) {
+                    // the tile before this one has been read out of the columns the two accumulators share
+                    if (lt > 0 && !(ok = ptx::mbar_wait(acc_free_bar, (lt - 1) & 1, abort_flag))) break;
+                } else {
+                    // this accumulator's previous tile (two tiles back) has been read out
+                    if (lt > 1 && !(ok = ptx::mbar_wait(acc_free_bar + 8u * (lt & 1), ((lt >> 1) - 1) & 1, abort_flag))) break;
+                }
                 ptx::tc_fence_after();
                 const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0);
                 const int kt0 = kt_begin(t), kt1 = kt_end(t);
+                // a 192-column tile starts at row 0 or 64 of its first scale tile of W: scale column 0 or 2
+                const uint32_t sfb_sub = uint32_t(((t / p.splits) / mp_tiles) * C::BN % 128) / 32u;
                 for (int kt = kt0; kt < kt1; kt++) {
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
                     ptx::tc_fence_after();
@@ -690,17 +703,17 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
                     if constexpr (VS == 32) {
                         if (2 * kt + 2 <= k_atoms)
                             issue_stage<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                                 sfb_t, idesc, kt == kt0, false, false);
+                                                 sfb_t, idesc, kt == kt0, false, false, sfb_sub);
                         else
                             issue_stage<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                                 sfb_t, idesc, kt == kt0, false, false);
+                                                 sfb_t, idesc, kt == kt0, false, false, sfb_sub);
                     } else {
                         if (2 * kt + 2 <= k_atoms)
                             issue_stage16<2, 2, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                                   sfb_t, idesc, kt == kt0, 0u);
+                                                   sfb_t, idesc, kt == kt0, sfb_sub);
                         else
                             issue_stage16<2, 1, 2>(acc, adesc0 + st16, bdesc0 + st16, sfadesc0 + st16, sfbdesc0 + st16, sfa_t,
-                                                   sfb_t, idesc, kt == kt0, 0u);
+                                                   sfb_t, idesc, kt == kt0, sfb_sub);
                     }
                     ptx::tc_commit_pair(empty_bar(s), 3);      // frees the stage in both CTAs
                     if (++s == C::STAGES) s = 0, ph ^= 1;
@@ -727,26 +740,34 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
             void *dst = splits > 1 ? static_cast<void *>(p.partial + int64_t(my_batch * splits + ks) * ep.M * ep.N)
                                    : (my_batch ? p.c[1] : p.c[0]);
             const bool dst_bf16 = splits > 1 ? false : ep.out_bf16;
-            if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
-            ptx::tc_fence_after();
-            const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
-            const int row = mt * BM + 32 * q + lane;
-            constexpr int CH = C::BN / 32 / 2;              // chunks per warp
-            constexpr int SH = C::OVL / 32;                 // chunks shared with the other accumulator: 1 or 2
-            static_assert((SH == 1 || SH == 2) && CH == 4, "the drain order below reads the shared chunks as the first pair");
-            // The columns shared with the other accumulator are the last chunk(s) of accumulator 0
-            // and the first of accumulator 1.  The warps that own them read them first and
-            // then release the next tile; the other warps release it at once: being here,
-            // they have finished every load of the tiles before this one.
-            const bool owner = (lt & 1) ? half == 0 : half == 1;
-            const int start = (owner && !(lt & 1)) ? CH - SH : 0;
-            auto chunk = [&](int i) { return CH * half + ((start + i) & (CH - 1)); };
+            constexpr int CH = C::BN / 32 / 2;              // chunks per warp: 4 or 3
+            constexpr int SH = C::OVL / 32;                 // chunks shared with the other accumulator: 0, 1 or 2
+            static_assert(SH == 0 || CH == 4, "the drain order below reads the shared chunks as the first pair of four");
             auto release_next_tile = [&]() {
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar, 0);
             };
-            if (!owner) release_next_tile();
+            // Accumulators that share nothing: a warp frees this tile's accumulator (one barrier per
+            // accumulator, so that a fast warp's arrival cannot be counted for the other one) as soon
+            // as its last load of the tile has landed in registers.
+            auto release_accumulator = [&]() {
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(acc_free_bar + 8u * (lt & 1), 0);
+            };
+            if (!(ok = ptx::mbar_wait(acc_full_bar, lt & 1, abort_flag))) break;
+            ptx::tc_fence_after();
+            const uint32_t acc = tmem_base + ((lt & 1) ? C::ACC1 : 0) + (uint32_t(32 * q) << 16);
+            const int row = mt * BM + 32 * q + lane;
+            // The columns shared with the other accumulator are the last chunk(s) of accumulator 0
+            // and the first of accumulator 1.  The warps that own them read them first and
+            // then release the next tile; the other warps release it at once: being here,
+            // they have finished every load of the tiles before this one.
+            const bool owner = SH > 0 && ((lt & 1) ? half == 0 : half == 1);
+            const int start = (owner && !(lt & 1)) ? CH - SH : 0;
+            auto chunk = [&](int i) { return CH * half + (SH > 0 ? ((start + i) & (CH - 1)) : i); };
+            if (SH > 0 && !owner) release_next_tile();
             auto emit = [&](int c, const uint32_t (&r)[32]) {
                 if (ep.store_c || splits > 1) store_chunk(ep, dst, dst_bf16, row - lane, lane, nt * C::BN + 32 * c, r);
                 if (ep.q_packed) quant_chunk(ep, row, nt * C::BN + 32 * c, r);
@@ -757,13 +778,17 @@ mxfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_c
 #pragma unroll 1                                    // code size: the body already holds two chunks
             for (int i = 0; i < CH; i += 2) {
                 ptx::tmem_ld_wait(ra);
-                ptx::tmem_ld32(acc + 32 * chunk(i + 1), rb);
+                if (i + 1 < CH) ptx::tmem_ld32(acc + 32 * chunk(i + 1), rb);
+                else if (SH == 0) release_accumulator();    // the last chunk is in registers
                 if (SH == 2 && i == 0 && owner) ptx::tmem_ld_wait(rb);
                 if (i == 0 && owner) release_next_tile();   // shared columns drained
                 emit(chunk(i), ra);
-                ptx::tmem_ld_wait(rb);
-                if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * chunk(i + 2), ra);
-                emit(chunk(i + 1), rb);
+                if (i + 1 < CH) {
+                    ptx::tmem_ld_wait(rb);
+                    if (i + 2 < CH) ptx::tmem_ld32(acc + 32 * chunk(i + 2), ra);
+                    else if (SH == 0) release_accumulator();
+                    emit(chunk(i + 1), rb);
+                }
             }
         }
     }
@@ -923,11 +948,11 @@ int make_sf_map(CUtensorMap *m, const void *base, int64_t rows, int64_t K, int s
     return LS_OK;
 }
 
-template <int VS = 32>
+template <int VS = 32, int BNP = 256>
 int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMap &tb, const GemmParams &p,
                 cudaStream_t st)
 {
-    using C = PairCfg<VS>;
+    using C = PairCfg<VS, BNP>;
     CUtensorMap tsa0, tsa1, tsb;
     if (int rc = make_sf_map(&tsa0, p.sfa[0], p.M, p.K, C::SFT)) return rc;
     if (int rc = make_sf_map(&tsa1, p.sfa[1], p.M, p.K, C::SFT)) return rc;
@@ -937,7 +962,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     if (int rc = current_device(&dev)) return rc;
     std::unique_lock<std::mutex> lk(state_mutex());
     if (!resident_pairs[dev]) {
-        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_pair_kernel<VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        LS_CUDA(cudaFuncSetAttribute(mxfp4_gemm_pair_kernel<VS, BNP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         // The kernel is persistent: the grid must not exceed the CTA pairs that can be
         // resident at once (fewer than SMs / 2 when a TPC has a single SM enabled).
         cudaLaunchConfig_t cfg = {};
@@ -949,7 +974,7 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
         at[0].val.clusterDim.x = 2, at[0].val.clusterDim.y = 1, at[0].val.clusterDim.z = 1;
         cfg.attrs = at, cfg.numAttrs = 1;
         int n = 0;
-        LS_CUDA(cudaOccupancyMaxActiveClusters(&n, mxfp4_gemm_pair_kernel<VS>, &cfg));
+        LS_CUDA(cudaOccupancyMaxActiveClusters(&n, mxfp4_gemm_pair_kernel<VS, BNP>, &cfg));
         if (n < 1) return fail(LS_ECUDA, "no CTA pair of the GEMM kernel fits on this device");
         resident_pairs[dev] = n;
     }
@@ -967,12 +992,12 @@ int launch_pair(const CUtensorMap &ta0, const CUtensorMap &ta1, const CUtensorMa
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = g_gemm_pdl.load(std::memory_order_relaxed) ? 1 : 0;
     cfg.attrs = at, cfg.numAttrs = 1;
-    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_pair_kernel<VS>, ta0, ta1, tb, tsa0, tsa1, tsb, p));
+    LS_CUDA(cudaLaunchKernelEx(&cfg, mxfp4_gemm_pair_kernel<VS, BNP>, ta0, ta1, tb, tsa0, tsa1, tsb, p));
     return LS_OK;
 }
 
 std::atomic<int> g_gemm_variant{0};   // 0 = choose by shape, 1 = single-CTA kernel (256-column tiles), 2 = CTA-pair kernel,
-                                      // 3 = single-CTA kernel with 128-column tiles
+                                      // 3 / 5 = single-CTA kernel with 128- / 64-column tiles, 6 = CTA-pair kernel with 192-column tiles
 std::atomic<int> g_gemm_splits{0};    // 0 = choose by shape, n = split K n ways where splitting is allowed
 
 // Per-device scratch for split-K partial sums, shared by every K-split GEMM of the device.
@@ -1072,7 +1097,8 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     if (!err) return fail(LS_ECUDA, "could not allocate the device error word");
     CUtensorMap ta0, ta1, tb;
     const int variant = g_gemm_variant.load(std::memory_order_relaxed), forced_splits = g_gemm_splits.load(std::memory_order_relaxed);
-    const bool pair = variant == 2 || (variant == 0 && (nbatch == 2 || M > BM));
+    const bool pair = variant == 2 || variant == 6 || (variant == 0 && (nbatch == 2 || M > BM));
+    const int pair_bn = variant == 6 ? 192 : 256;
     // A tile of the single-CTA kernel: the box has only as many rows (16, 32, 64 or 128) as
     // A has.  The other rows of the stage keep whatever shared memory held; an output row
     // depends on its own row of A only, and rows past M are never stored.  (A 128-row box
@@ -1099,7 +1125,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
             if (bn == 128 && tiles_of(128) * 2 <= sm_count()) bn = 64;
         }
     }
-    if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
+    if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? pair_bn / 2 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
     p.sfa[1] = nbatch == 2 ? sfa1 : sfa0;
@@ -1125,7 +1151,7 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
     // order.  Not on the allocation-free path (caller-supplied error word), which must
     // not touch an allocator, and not with the quantizing epilogue.
     const int k_tiles = p.kt_per_split;
-    const int tiles = pair ? int((nbatch == 2 ? (M + BM - 1) / BM : (M + 2 * BM - 1) / (2 * BM)) * ((N + bn - 1) / bn))
+    const int tiles = pair ? int((nbatch == 2 ? (M + BM - 1) / BM : (M + 2 * BM - 1) / (2 * BM)) * ((N + pair_bn - 1) / pair_bn))
                            : int(((M + BM - 1) / BM) * ((N + bn - 1) / bn)) * nbatch;
     const int slots = pair ? sm_count() / 2 : sm_count();       // work items that run at once
     int s = 1;
@@ -1158,7 +1184,8 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
         if (!p.partial) return fail(LS_ECUDA, "could not allocate split-K scratch");
     }
     if (pair) {
-        if (int rc = launch_pair(ta0, ta1, tb, p, static_cast<cudaStream_t>(stream))) return rc;
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (int rc = pair_bn == 192 ? launch_pair<32, 192>(ta0, ta1, tb, p, st) : launch_pair<32, 256>(ta0, ta1, tb, p, st)) return rc;
     } else {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         if (int rc = bn == 64 ? launch<64>(ta0, ta1, tb, p, st)
@@ -1203,7 +1230,8 @@ int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t
     // as for blocks of 32: CTA pairs for two batches or more than one row tile, else one CTA per
     // tile with a box of A no taller than A (ls_gemm_set_variant 2 / 1, 3, 5 force either)
     const int variant = g_gemm_variant.load(std::memory_order_relaxed);
-    const bool pair = variant == 2 || (variant == 0 && (nbatch == 2 || M > BM));
+    const bool pair = variant == 2 || variant == 6 || (variant == 0 && (nbatch == 2 || M > BM));
+    const int pair_bn = variant == 6 ? 192 : 256;
     int a_box_rows = BM;
     if (!pair)
         for (a_box_rows = 16; a_box_rows < M && a_box_rows < BM; a_box_rows *= 2) {}
@@ -1211,7 +1239,7 @@ int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t
     const int bn = variant == 5 || (variant != 3 && tiles128 * 2 <= sm_count()) ? 64 : 128;
     if (int rc = make_operand_map(&ta0, a0, M, K / 2, a_box_rows)) return rc;
     if (int rc = make_operand_map(&ta1, nbatch == 2 ? a1 : a0, M, K / 2, a_box_rows)) return rc;
-    if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? 128 : bn)) return rc;
+    if (int rc = make_operand_map(&tb, w, N, K / 2, pair ? pair_bn / 2 : bn)) return rc;
     GemmParams p{};
     p.sfa[0] = sfa0;
     p.sfa[1] = nbatch == 2 ? sfa1 : sfa0;
@@ -1229,7 +1257,7 @@ int gemm_block16(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t
     p.a_box_bytes = a_box_rows * BKB;
     p.sf_e4m3 = e4m3_scales;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (pair) return launch_pair<16>(ta0, ta1, tb, p, st);
+    if (pair) return pair_bn == 192 ? launch_pair<16, 192>(ta0, ta1, tb, p, st) : launch_pair<16, 256>(ta0, ta1, tb, p, st);
     return bn == 64 ? launch<64, 16>(ta0, ta1, tb, p, st) : launch<128, 16>(ta0, ta1, tb, p, st);
 }
 
@@ -1292,7 +1320,7 @@ extern "C" int ls_gemm_status(int *status_host)
 
 extern "C" int ls_gemm_set_variant(int variant)
 {
-    if (variant < 0 || variant > 5 || variant == 4) return fail(LS_EINVAL, "variant must be 0..3 or 5");
+    if (variant < 0 || variant > 6 || variant == 4) return fail(LS_EINVAL, "variant must be 0..3, 5 or 6");
     g_gemm_variant.store(variant, std::memory_order_relaxed);
     return LS_OK;
 }

@@ -51,7 +51,7 @@ def test_gemm_argument_errors(L):
     assert L.ls_mxfp4_gemm(_p(a, 4), _p(a), _p(a), _p(a), _p(c), 1, 128, 128, 128, None) == EALIGN
     assert L.ls_mxfp4_gemm(*args(128)[:6], 0, 128, 128, None) == 0                # M = 0
     assert L.ls_mxfp4_gemm_quant(_p(a), _p(a), _p(a), _p(a), _p(c), 1, 0, _p(a), _p(a), 128, 100, 128, None) == EINVAL   # N % 128
-    assert L.ls_gemm_set_variant(9) == EINVAL and L.ls_gemm_set_variant(3) == 0 and L.ls_gemm_set_variant(0) == 0
+    assert L.ls_gemm_set_variant(9) == EINVAL and L.ls_gemm_set_variant(4) == EINVAL and L.ls_gemm_set_variant(3) == 0 and L.ls_gemm_set_variant(0) == 0
     assert L.ls_gemm_set_splits(17) == EINVAL and L.ls_gemm_set_splits(0) == 0
 
 

@@ -149,7 +149,7 @@ def test_block16_is_at_least_as_close_to_the_unquantized_product(mods):
 @pytest.mark.parametrize("fmt", ["mx16", "nvfp4"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 640, 1152), (1000, 520, 2048)])
 def test_block16_kernels_agree(mods, fmt, M, N, K):
-    # the CTA-pair kernel (the default above 128 rows) and the single-CTA kernel with 128- and 64-column tiles
+    # the CTA-pair kernel (the default above 128 rows; 256- and 192-column tiles) and the single-CTA kernel with 128- and 64-column tiles
     # issue the same MMAs in the same order over K: identical bits, and within tolerance of the oracle
     fp4, mg = mods
     from lockstep_b200 import nvfp4
@@ -175,11 +175,11 @@ def test_block16_kernels_agree(mods, fmt, M, N, K):
                                          torch.from_numpy(nvfp4_ref.dequantize(wc, wsc)))
     outs = {}
     try:
-        for variant in (2, 3, 5):
+        for variant in (2, 6, 3, 5):
             lib().ls_gemm_set_variant(variant)
             outs[variant] = run()
     finally:
         lib().ls_gemm_set_variant(0)
     mg.gemm_status()
     _check(outs[2], ref, f"{fmt} pair kernel {M} x {N} x {K}")
-    assert torch.equal(outs[2], outs[3]) and torch.equal(outs[2], outs[5])
+    assert torch.equal(outs[2], outs[3]) and torch.equal(outs[2], outs[5]) and torch.equal(outs[2], outs[6])

@@ -137,7 +137,9 @@ def test_skinny_shapes(mods, M, N, K):
 @pytest.mark.parametrize("variant,M,N,K,splits", [(1, 128, 512, 2048, 3), (1, 100, 300, 1152, 16), (2, 512, 512, 2048, 2), (3, 40, 300, 1152, 2), (1, 700, 520, 1024, 1), (3, 300, 264, 512, 2),
                                                   (2, 300, 520, 4096, 5), (2, 1024, 1024, 16384, 0),
                                                   (5, 16, 4096, 512, 1), (5, 1, 1000, 1152, 1), (5, 100, 300, 1152, 2),
-                                                  (5, 128, 264, 640, 3), (5, 40, 8192, 256, 1), (5, 130, 200, 384, 1)])
+                                                  (5, 128, 264, 640, 3), (5, 40, 8192, 256, 1), (5, 130, 200, 384, 1),
+                                                  (6, 256, 384, 128, 1), (6, 512, 520, 2048, 1), (6, 300, 1000, 1152, 2),
+                                                  (6, 1024, 200, 640, 3), (6, 130, 8192, 256, 1), (6, 2048, 448, 4096, 0)])
 def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
     # power-of-two scales on an integer grid: every partial sum is exact, so a split
     # product must equal the unsplit one bit for bit, on both kernels and both batches
@@ -167,7 +169,7 @@ def test_forced_k_splits_exact_and_dual(mods, variant, M, N, K, splits):
         for got, ref in ((c, want[0]), (c1, want[0]), (c2, want[1]), (cb, want[1])):
             _check(got, ref.float().to(got.dtype), f"{M}x{N}x{K} splits {splits}")
     assert (guard == 777.0).all()
-    assert L.ls_gemm_set_splits(17) < 0 and L.ls_gemm_set_splits(-1) < 0 and L.ls_gemm_set_variant(4) < 0 and L.ls_gemm_set_variant(6) < 0
+    assert L.ls_gemm_set_splits(17) < 0 and L.ls_gemm_set_splits(-1) < 0 and L.ls_gemm_set_variant(4) < 0 and L.ls_gemm_set_variant(7) < 0
 
 
 @pytest.mark.parametrize("M,N,K,dt", [(256, 512, 384, torch.bfloat16), (130, 256, 256, torch.bfloat16),
