@@ -350,10 +350,26 @@ def wire_leg(args, dev, rank, world, barrier, pk):
     phases = [statistics.median(e[j].elapsed_time(e[j + 1]) for e in pev) for j in range(3)]
     mode = wobj.mode_name()
     wobj.close()
-    t = torch.tensor([wire_ms] + phases, device=dev, dtype=torch.float64)
+    # ---- the reference's own default on the same buffer: Wire("fp32") is NCCL's all-reduce and a division (wire.py:93-95)
+    nccl_ms = 0.0
+    if world > 1:
+        ref = grad.clone()
+        for _ in range(3):
+            dist.all_reduce(ref)
+            ref.div_(world)
+        barrier()
+        a.record()
+        for _ in range(wsteps):
+            dist.all_reduce(ref)
+            ref.div_(world)
+        b.record()
+        barrier()
+        nccl_ms = a.elapsed_time(b) / wsteps
+        del ref
+    t = torch.tensor([wire_ms] + phases + [nccl_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    wire_ms, send_ms, reduce_ms, finish_ms = t.tolist()
+    wire_ms, send_ms, reduce_ms, finish_ms, nccl_ms = t.tolist()
     comp = wn * 0.53125                                      # packed + exponent bytes of one buffer
     # per rank and step: send reads g, res and writes res, payload; reduce reads W payloads,
     # ores, writes ores and W payloads; finish reads the payload and writes g
@@ -370,6 +386,10 @@ def wire_leg(args, dev, rank, world, barrier, pk):
         "phases_ms": {"send": send_ms, "reduce_incl_wait": reduce_ms, "finish_incl_wait": finish_ms,
                       "how": f"three separate launches, median of {psteps} steps, barrier before each step, max over ranks"},
         "data": "Student-t(3) * 1e-3, seed 100 + rank"}
+    if world > 1:
+        out["nccl_fp32"] = {"ms": nccl_ms, "algbw_gbs": wn * 4 / (nccl_ms * 1e-3) / 1e9,
+                            "what": "torch.distributed.all_reduce (NCCL) of the same fp32 buffer + division by the world size: "
+                                    "the reference's Wire('fp32'), timed the same way"}
     if world == 1 and not args.no_cpu_baseline:
         cn = 8 << 20                                         # bounded sample of the 64 Mi buffer
         rng = np.random.default_rng(100)
