@@ -101,6 +101,18 @@ int ls_layernorm_quantize(const void *x, int x_dtype, const float *gamma, const 
                           int64_t rows, int64_t D, void *y_bf16, uint8_t *packed, uint8_t *sf, float *mean,
                           float *rstd, void *stream);
 
+/* Backward of that LayerNorm from the statistics ls_layernorm_quantize kept (what
+ * torch.native_layer_norm_backward computes; lockstep leaves it to torch, train.py:50,53):
+ *   gx [rows, D] in x's type = rstd (g - mean_D(g) - xhat mean_D(g xhat)),  g = gy gamma,
+ *   ggamma [D] = sum over rows of gy xhat,  gbeta [D] = sum over rows of gy  (fp32; either may be NULL)
+ *   gy [rows, D] LS_F32 or LS_BF16 (the incoming gradient as the GEMM left it: no cast pass);
+ *   gamma NULL means 1.  scratch: ls_layernorm_backward_scratch(rows, D) floats, 16-byte aligned;
+ *   the column sums are added in a fixed order (no atomics).  D % 256 == 0, D <= 8192. */
+int64_t ls_layernorm_backward_scratch(int64_t rows, int64_t D);
+int ls_layernorm_backward(const void *gy, int gy_dtype, const void *x, int x_dtype, const float *mean,
+                          const float *rstd, const float *gamma, int64_t rows, int64_t D, void *gx,
+                          float *ggamma, float *gbeta, float *scratch, void *stream);
+
 /* Both orientations of one tensor from one read of x [R, C]: what
  * ls_quantize_mxfp4 (packed + scale-factor bytes of x, blocks along C) and
  * ls_quantize_mxfp4_t (of x^T, blocks along R) would write.  For a linear layer

@@ -26,6 +26,8 @@ _SIGS = {
     "ls_quantize_mxfp4_both_act": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "ls_quantize_mxfp4_both": (c_int, [c_vp, c_int, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "ls_layernorm_quantize": (c_int, [c_vp, c_int, c_vp, c_vp, ctypes.c_float, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp]),
+    "ls_layernorm_backward_scratch": (c_i64, [c_i64, c_i64]),
+    "ls_layernorm_backward": (c_int, [c_vp, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp]),
     "ls_round_e2m1": (c_int, [c_vp, c_i64, c_int, c_vp, c_vp]),
     "ls_pack_fp4": (c_int, [c_vp, c_vp, c_i64, c_vp]),
     "ls_unpack_fp4": (c_int, [c_vp, c_vp, c_i64, c_vp]),

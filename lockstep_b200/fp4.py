@@ -125,6 +125,25 @@ def layernorm_quantize(x: torch.Tensor, weight, bias, eps: float = 1e-5):
     return y, packed, sf, mean, rstd
 
 
+def layernorm_backward(g_y: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor, weight, want_bias=True):
+    """(extension) Backward of layer_norm from the statistics layernorm_quantize kept: returns
+    (gx in x's dtype, gweight fp32 [D] or None, gbias fp32 [D] or None).  g_y fp32 or bf16 [rows, D]."""
+    need_cuda(g_y, x, mean, rstd)
+    rows, D = x.shape
+    assert g_y.shape == x.shape and D % 256 == 0 and D <= 8192
+    if g_y.dtype not in (torch.float32, torch.bfloat16):
+        g_y = g_y.float()
+    g_y, x = aligned(g_y), aligned(x)
+    w = None if weight is None else aligned(weight.float())
+    gx = torch.empty_like(x)
+    gw = torch.empty(D, dtype=torch.float32, device=x.device) if weight is not None else None
+    gb = torch.empty(D, dtype=torch.float32, device=x.device) if want_bias else None
+    scratch = torch.empty(int(lib().ls_layernorm_backward_scratch(rows, D)), dtype=torch.float32, device=x.device)
+    check(lib().ls_layernorm_backward(ptr(g_y), _lib.dtype_code(g_y.dtype), ptr(x), _lib.dtype_code(x.dtype), ptr(aligned(mean)),
+                                      ptr(aligned(rstd)), ptr(w), rows, D, ptr(gx), ptr(gw), ptr(gb), ptr(scratch), stream()))
+    return gx, gw, gb
+
+
 def quantize_mxfp4_packed_t_gelu(x: torch.Tensor, rounding: str = "ref"):
     """(extension) quantize_mxfp4_packed_t(gelu(x)) for bf16 x [R, C] without the elementwise
     pass: the activation is applied to the tile inside the kernel.  R % 128 == 0."""

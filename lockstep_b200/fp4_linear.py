@@ -154,8 +154,12 @@ class NVFP4Linear(nn.Linear):
 
 
 def _ln_backward(g_y, x, mean, rstd, gamma, beta):
-    """LayerNorm's backward from the statistics the fused forward kept (torch's kernel)."""
+    """LayerNorm's backward from the statistics the fused forward kept: this library's kernel (it
+    reads the incoming gradient in the type the GEMM left it in), torch's for other shapes."""
     rows, D = x.shape
+    if D % 256 == 0 and D <= 8192 and x.dtype in (torch.float32, torch.bfloat16):
+        gx, gw, gb = fp4.layernorm_backward(g_y, x, mean, rstd, gamma, want_bias=beta is not None)
+        return gx, (None if gw is None else gw.to(gamma.dtype)), (None if gb is None else gb.to(beta.dtype))
     return torch.ops.aten.native_layer_norm_backward(g_y.to(x.dtype), x, [D], mean.view(rows, 1), rstd.view(rows, 1),
                                                      gamma, beta, [True, gamma is not None, beta is not None])
 

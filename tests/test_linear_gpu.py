@@ -227,3 +227,33 @@ def test_nvfp4_linear_forward_and_straight_through_backward():
     gx_ref, gw_ref = ref_port.linear_backward_ste(gy.reshape(-1, 160), x.reshape(-1, 256), w)
     _close(xg.grad.reshape(-1, 256), gx_ref, "NVFP4 dX", 1e-2)      # bf16 matmuls, different GEMM library
     _close(lin.weight.grad, gw_ref, "NVFP4 dW", 1e-2)
+
+
+@pytest.mark.parametrize("rows,D,xdt,gdt", [(1000, 1024, torch.float32, torch.bfloat16), (16384, 1024, torch.float32, torch.bfloat16),
+                                            (300, 256, torch.bfloat16, torch.bfloat16), (37, 4096, torch.float32, torch.float32),
+                                            (5000, 2048, torch.bfloat16, torch.float32)])
+def test_layernorm_backward_kernel_against_torch(rows, D, xdt, gdt):
+    # the statistics come from the fused forward kernel; the expected values from torch's own backward in fp64
+    from lockstep_b200 import fp4
+    g = torch.Generator(device="cuda").manual_seed(rows + D)
+    x = (torch.randn(rows, D, device="cuda", generator=g) * 2 + 0.5).to(xdt)
+    gy = torch.randn(rows, D, device="cuda", generator=g).to(gdt)
+    gamma = torch.randn(D, device="cuda", generator=g)
+    beta = torch.randn(D, device="cuda", generator=g)
+    _, _, _, mean, rstd = fp4.layernorm_quantize(x, gamma, beta, 1e-5)
+    gx, gw, gb = fp4.layernorm_backward(gy, x, mean, rstd, gamma)
+    xd = x.double().requires_grad_(True)
+    gd, bd = gamma.double().requires_grad_(True), beta.double().requires_grad_(True)
+    torch.nn.functional.layer_norm(xd, (D,), gd, bd, 1e-5).backward(gy.double())
+    assert gx.dtype == xdt and gw.dtype == torch.float32
+    tol = 2e-6 if xdt == torch.float32 else 4e-3                # bf16 gx: one rounding of the result
+    _close(gx, xd.grad, "gx", tol)
+    _close(gw, gd.grad, "ggamma", 2e-6)
+    _close(gb, bd.grad, "gbeta", 2e-6)
+    again = fp4.layernorm_backward(gy, x, mean, rstd, gamma)
+    assert all(torch.equal(a, b) for a, b in zip(again, (gx, gw, gb)))         # fixed summation order
+    gx2, gw2, gb2 = fp4.layernorm_backward(gy, x, mean, rstd, None, want_bias=False)
+    assert gw2 is None and gb2 is None
+    xd2 = x.double().requires_grad_(True)
+    torch.nn.functional.layer_norm(xd2, (D,), None, None, 1e-5).backward(gy.double())
+    _close(gx2, xd2.grad, "gx without gamma", tol)
