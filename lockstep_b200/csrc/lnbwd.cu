@@ -5,7 +5,7 @@
 //   ggamma = sum_rows gy xhat,   gbeta = sum_rows gy
 // One CTA of D / 8 threads per row, as the forward kernel: a thread owns 8 consecutive
 // features and keeps their 16 column sums in registers over all rows of its CTA; the CTAs'
-// partial sums go to a scratch array that a second kernel adds in a fixed order (no atomics:
+// partial sums go to a scratch array that two small kernels add in a fixed order (no atomics:
 // the result does not depend on scheduling).  HBM-bound: x and gy in, gx out, once each.
 #include "common.cuh"
 
@@ -98,16 +98,19 @@ layernorm_backward_kernel(const TX *__restrict__ x, const TG *__restrict__ gy, c
     *reinterpret_cast<float4 *>(pb + 4) = make_float4(acc_b[4], acc_b[5], acc_b[6], acc_b[7]);
 }
 
-// part [2][nparts][D] -> ggamma [D], gbeta [D].  A CTA owns 32 columns; its 8 warps take the
-// partial rows w, w + 8, ... in ascending order and their eight sums are added in warp order.
+// part [2][nparts][D] -> ggamma [D], gbeta [D] in two steps, each adding in a fixed order.
+// Step 1: CTA (x, y) owns 32 columns and the partial rows p with p % kSplits == y; its 8 warps
+// take every 8th of those in ascending order and their eight sums are added in warp order.
+// Step 2: one thread per column adds the kSplits results in ascending order.
+constexpr int kSplits = 16;
+
 __global__ void __launch_bounds__(256)
-layernorm_backward_sum_kernel(const float *__restrict__ part, int nparts, int D, float *__restrict__ ggamma,
-                              float *__restrict__ gbeta)
+layernorm_backward_sum1_kernel(const float *__restrict__ part, int nparts, int D, float *__restrict__ part2)
 {
     __shared__ float sm[2][8][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c = blockIdx.x * 32 + lane;
     float sg = 0.0f, sb = 0.0f;
-    for (int p = warp; p < nparts; p += 8) {
+    for (int p = blockIdx.y + kSplits * warp; p < nparts; p += kSplits * 8) {
         sg += part[int64_t(p) * D + c];
         sb += part[(int64_t(nparts) + p) * D + c];
     }
@@ -116,9 +119,20 @@ layernorm_backward_sum_kernel(const float *__restrict__ part, int nparts, int D,
     if (warp == 0) {
         float tg = 0.0f, tb = 0.0f;
         for (int w = 0; w < 8; w++) tg += sm[0][w][lane], tb += sm[1][w][lane];
-        if (ggamma) ggamma[c] = tg;
-        if (gbeta) gbeta[c] = tb;
+        part2[int64_t(blockIdx.y) * D + c] = tg;
+        part2[int64_t(kSplits + blockIdx.y) * D + c] = tb;
     }
+}
+
+__global__ void __launch_bounds__(256)
+layernorm_backward_sum2_kernel(const float *__restrict__ part2, int D, float *__restrict__ ggamma, float *__restrict__ gbeta)
+{
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= D) return;
+    float tg = 0.0f, tb = 0.0f;
+    for (int s = 0; s < kSplits; s++) tg += part2[int64_t(s) * D + c], tb += part2[int64_t(kSplits + s) * D + c];
+    if (ggamma) ggamma[c] = tg;
+    if (gbeta) gbeta[c] = tb;
 }
 
 int parts_for(int64_t rows, int64_t D)
@@ -136,7 +150,7 @@ using namespace ls;
 extern "C" int64_t ls_layernorm_backward_scratch(int64_t rows, int64_t D)
 {
     if (rows < 0 || D <= 0 || D % 256 != 0 || D > 8192) return -1;
-    return int64_t(2) * parts_for(rows, D) * D;
+    return int64_t(2) * (parts_for(rows, D) + kSplits) * D;
 }
 
 extern "C" int ls_layernorm_backward(const void *gy, int gy_dtype, const void *x, int x_dtype, const float *mean,
@@ -161,7 +175,9 @@ extern "C" int ls_layernorm_backward(const void *gy, int gy_dtype, const void *x
 #undef LS_LNB
     LS_LAUNCH_CHECK("layernorm_backward");
     if (ggamma || gbeta) {
-        layernorm_backward_sum_kernel<<<int(D / 32), 256, 0, st>>>(scratch, parts, int(D), ggamma, gbeta);
+        float *part2 = scratch + int64_t(2) * parts * D;
+        layernorm_backward_sum1_kernel<<<dim3(unsigned(D / 32), kSplits), 256, 0, st>>>(scratch, parts, int(D), part2);
+        layernorm_backward_sum2_kernel<<<int((D + 255) / 256), 256, 0, st>>>(part2, int(D), ggamma, gbeta);
         LS_LAUNCH_CHECK("layernorm_backward_sum");
     }
     return LS_OK;
