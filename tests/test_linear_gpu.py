@@ -142,7 +142,9 @@ def test_transposed_quantizer_with_gelu_equals_two_passes():
 def test_layernorm_quantize_kernel_against_two_passes():
     from lockstep_b200 import fp4
     g = torch.Generator(device="cuda").manual_seed(12)
-    for dt, rows, D in ((torch.float32, 300, 1024), (torch.bfloat16, 129, 256), (torch.float32, 64, 4096)):
+    for dt, rows, D in ((torch.float32, 300, 1024), (torch.bfloat16, 129, 256), (torch.float32, 64, 4096), (torch.bfloat16, 77, 512),
+                        (torch.float32, 1000, 768), (torch.bfloat16, 200, 1536), (torch.float32, 33, 2048), (torch.float32, 50, 1280),
+                        (torch.bfloat16, 5000, 1024)):
         x = (torch.randn(rows, D, device="cuda", generator=g) * 3 + 0.5).to(dt)
         gamma = torch.randn(D, device="cuda", generator=g) * 0.2 + 1
         beta = torch.randn(D, device="cuda", generator=g) * 0.1
