@@ -166,7 +166,9 @@ int ls_scales_to_sf_block(const float *scale, int64_t rows, int64_t K, int block
  * ls_gemm_set_splits) puts its partial sums in one scratch buffer per device;
  * the library orders such calls on different streams with an event (the later
  * call waits for the earlier one's summation), so they are safe but do not
- * overlap.  Encoded TMA descriptors are cached per host thread. */
+ * overlap.  On a stream that is being captured into a CUDA graph the product is
+ * never split (the capture cannot wait for a user outside it).  Encoded TMA
+ * descriptors are cached per host thread. */
 int ls_mxfp4_gemm(const uint8_t *a_pk, const uint8_t *bt_pk, const uint8_t *sfa, const uint8_t *sfb,
                   void *c, int out_dtype, int64_t M, int64_t N, int64_t K, void *stream);
 

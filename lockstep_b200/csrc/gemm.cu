@@ -1155,7 +1155,11 @@ int gemm_fused(int nbatch, const uint8_t *a0, const uint8_t *a1, const uint8_t *
                            : int(((M + BM - 1) / BM) * ((N + bn - 1) / bn)) * nbatch;
     const int slots = pair ? sm_count() / 2 : sm_count();       // work items that run at once
     int s = 1;
-    if (!caller_err && !fused) {
+    // A stream that is being captured into a CUDA graph cannot wait for the scratch's last user
+    // outside the capture, and a replay may run beside other users: no K split inside a capture.
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capture) != cudaSuccess) capture = cudaStreamCaptureStatusNone;
+    if (!caller_err && !fused && capture == cudaStreamCaptureStatusNone) {
         if (forced_splits > 0) {
             s = forced_splits;
         } else if (pair) {

@@ -428,3 +428,31 @@ def test_split_k_on_two_streams_and_two_host_threads(mods):
         lib().ls_gemm_set_variant(0)
         lib().ls_gemm_set_splits(0)
     mg.gemm_status()
+
+
+def test_split_eligible_product_inside_a_cuda_graph(mods):
+    # 1024 x 1024 x 16384 is a shape the library splits along K on its own.  Captured into a CUDA graph (after an
+    # eager call on another stream has used the split-K scratch) it runs unsplit: the replay gives the bits of
+    # the unsplit eager product, and the capture is not invalidated.
+    fp4, mg, _ = mods
+    from lockstep_b200._lib import lib
+    g = torch.Generator(device="cuda").manual_seed(77)
+    a = torch.randn(1024, 16384, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(1024, 16384, device="cuda", generator=g) * 0.02).bfloat16()
+    pa, sa = fp4.quantize_mxfp4_packed(a)
+    pw, sw = fp4.quantize_mxfp4_packed(w)
+    split = mg.mxfp4_gemm_packed(pa, pw, sa, sw, out_dtype=torch.float32)          # eager, split by the library
+    try:
+        lib().ls_gemm_set_splits(1)
+        unsplit = mg.mxfp4_gemm_packed(pa, pw, sa, sw, out_dtype=torch.float32)
+    finally:
+        lib().ls_gemm_set_splits(0)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        c = mg.mxfp4_gemm_packed(pa, pw, sa, sw, out_dtype=torch.float32)
+    graph.replay()
+    torch.cuda.synchronize()
+    mg.gemm_status()
+    assert torch.equal(c, unsplit)
+    _check(c, split, "graph replay against the split product")
