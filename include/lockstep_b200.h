@@ -311,7 +311,10 @@ int ls_wire_map_local(void *handle, void *const *handles_host);
  * interleave ranks in one process, or that want to start the send early, use
  * them).  ls_wire_allreduce runs the step either as those three launches or as
  * ONE cooperative launch that pipelines sub-ranges of the shards through the
- * three phases (see ls_wire_set_mode); results and wire bytes are the same. */
+ * three phases (see ls_wire_set_mode); results and wire bytes are the same.
+ * A step cannot be captured into a CUDA graph (its epoch advances on the host and
+ * travels as a kernel argument): on a capturing stream these calls, and the
+ * integer wire's, return LS_ESTATE and launch nothing. */
 int ls_wire_send(void *handle, const float *g, int64_t numel, float *res, void *stream);
 int ls_wire_reduce(void *handle, float *ores, int reverse, void *stream);
 int ls_wire_finish(void *handle, float *g, int64_t numel, void *stream);

@@ -769,6 +769,17 @@ int check_call(Wire *w, const float *g, int64_t numel)
     return LS_OK;
 }
 
+// A step's epoch is a kernel argument that the host advances on every call: a CUDA graph would
+// replay one epoch for ever and its waits would pass on stale flags.  Calls on a stream under
+// capture are refused.
+int refuse_capture(void *stream)
+{
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+        return fail(LS_ESTATE, "a wire step cannot be captured into a CUDA graph (its epoch advances on the host)");
+    return LS_OK;
+}
+
 }  // namespace
 }  // namespace ls
 
@@ -961,6 +972,7 @@ extern "C" int ls_wire_send(void *h, const float *g, int64_t numel, float *res, 
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
+    if (int rc = refuse_capture(stream)) return rc;
     w->epoch++;
     const Sub sub = whole_shard(w);
     wire_send_kernel<<<grid_for(int64_t(w->g.world) * sub.count, 5), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -973,6 +985,7 @@ extern "C" int ls_wire_reduce(void *h, float *ores, int reverse, void *stream)
 {
     Wire *w = as_wire(h);
     if (!w || !w->mapped || w->g.bits) return fail(LS_ESTATE, "wire not ready");
+    if (int rc = refuse_capture(stream)) return rc;
     const Sub sub = whole_shard(w);
     wire_reduce_kernel<<<grid_for(sub.count, 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         ores, w->g, w->peers, w->epoch, reverse, sub);
@@ -984,6 +997,7 @@ extern "C" int ls_wire_finish(void *h, float *g, int64_t numel, void *stream)
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
+    if (int rc = refuse_capture(stream)) return rc;
     const Sub sub = whole_shard(w);
     // four groups per thread and step
     wire_finish_kernel<<<grid_for((int64_t(w->g.world) * sub.count + 3) / 4, 8), kThreads, 0,
@@ -1016,6 +1030,7 @@ extern "C" int ls_wire_allreduce(void *h, float *g, int64_t numel, float *res, f
 {
     Wire *w = as_wire(h);
     if (int rc = check_call(w, g, numel)) return rc;
+    if (int rc = refuse_capture(stream)) return rc;
     if (ls_wire_mode(h) == 1) {
         if (int rc = ls_wire_send(h, g, numel, res, stream)) return rc;
         if (int rc = ls_wire_reduce(h, ores, reverse, stream)) return rc;
@@ -1040,6 +1055,7 @@ extern "C" int ls_wire_allreduce_group(void *const *handles, float *const *gs, i
     if (!handles || !gs) return fail(LS_EINVAL, "null argument");
     Wire *w0 = as_wire(handles[0]);
     if (int rc = check_call(w0, gs[0], numel)) return rc;
+    if (int rc = refuse_capture(stream)) return rc;
     const int world = w0->g.world;
     const int capacity = fused_capacity(w0);
     if (!capacity) return fail(LS_ECUDA, "could not size the cooperative wire kernel");
@@ -1061,6 +1077,7 @@ extern "C" int ls_wire_int_phase(void *h, int phase, float *g, int64_t numel, fl
 {
     Wire *w = as_wire(h);
     if (!w || !w->mapped || !w->g.bits) return fail(LS_ESTATE, "not a ready integer wire");
+    if (int rc = refuse_capture(stream)) return rc;
     if ((phase == 0 || phase == 1 || phase == 3) && (!g || numel <= 0 || numel > w->g.padded))
         return fail(LS_EINVAL, "numel %lld does not fit the wire", (long long)numel);
     cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -344,3 +344,24 @@ def test_phase_methods_equal_the_call(wire):
         assert torch.equal(x, y) and torch.equal(a.res, b.res) and torch.equal(a.ores, b.ores)
     a.status(), b.status()
     a.close(), b.close()
+
+
+@pytest.mark.parametrize("method", ["mxfp4ef", "int8ef"])
+def test_a_wire_step_refuses_cuda_graph_capture(wire, method):
+    # a step's epoch advances on the host and travels as a kernel argument: a replayed graph would wait on
+    # flags of an old epoch.  The call is refused on a capturing stream, nothing is launched, and the wire
+    # works as before afterwards.
+    n = 100_000
+    w = wire.Wire(method, n)
+    g = (torch.randn(n, generator=torch.Generator().manual_seed(3)) * 1e-2).cuda()
+    first = w(g.clone()).clone()
+    graph = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="CUDA graph"):
+        with torch.cuda.graph(graph):
+            w(g.clone())
+    torch.cuda.synchronize()
+    w2 = wire.Wire(method, n)
+    assert torch.equal(w2(g.clone()), first)                   # an untouched wire gives the first step's result
+    w(g.clone())                                                # and the one that refused still runs
+    w.status(), w2.status()
+    w.close(), w2.close()
