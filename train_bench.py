@@ -44,8 +44,10 @@ class CausalSelfAttention(nn.Module):
 
     def forward(self, x):
         batch, steps, width = x.shape
-        qkv = self.qkv(x).view(batch, steps, 3, self.heads, width // self.heads)
-        q, k, v = qkv.permute(2, 0, 3, 1, 4)                      # each [batch, heads, steps, head_dim]
+        # three views of the projection's output, each [batch, heads, steps, head_dim]; no copy here, and one
+        # concatenation of the three gradients in backward (train.py:47-48 splits the same way)
+        q, k, v = (part.view(batch, steps, self.heads, width // self.heads).transpose(1, 2)
+                   for part in self.qkv(x).split(width, dim=2))
         mixed = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return self.proj(mixed.transpose(1, 2).reshape(batch, steps, width))
 
