@@ -11,6 +11,10 @@ The four projections of every block come from `make_linear`:
   "dense"   nn.Linear (cuBLAS bf16 under autocast)             -- the comparison point
   "ste"     MXFP4Linear, straight-through bf16 backward        -- lockstep's fp4_linear.py
   "mxfp4"   MXFP4Linear with MXFP4 dgrad / wgrad as well
+  "nvfp4"   NVFP4Linear (blocks of 16 under E4M3 scales), straight-through backward
+
+    python train_bench.py --kind mxfp4            # tokens/s
+    python train_bench.py --kind mxfp4 --kernels  # device time per kernel of one step
 
 Gradient sync follows train.py:100-105,124-138: all gradients live in one flat fp32
 buffer that a `wire.Wire` averages in place after the backward pass.
@@ -269,3 +273,42 @@ def report(device, steps=5, warmup=2, world=1, rank=0):
         res["mxfp4_vs_dense"] = out["mxfp4"]["tokens_per_s"] / out["dense"]["tokens_per_s"]
         res["ste_vs_dense"] = out["ste"]["tokens_per_s"] / out["dense"]["tokens_per_s"]
     return res
+
+
+def kernel_table(kind="mxfp4", fused=True, steps=3, top=24, device=None):
+    """Device time per kernel of one training step (torch profiler, CUDA activity only): a list of
+    (microseconds per step, launches per step, kernel name) sorted by time, and the total."""
+    from torch.profiler import ProfilerActivity, profile
+    device = device or torch.device("cuda", 0)
+    t = Trainer(kind, device=device, fused=fused)
+    for _ in range(3):
+        t.step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            t.step()
+        torch.cuda.synchronize()
+    t.close()
+    rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+    total = sum(e.device_time_total for e in rows) / steps
+    return [(e.device_time_total / steps, e.count // steps, e.key) for e in rows[:top]], total
+
+
+if __name__ == "__main__":
+    import argparse
+    ap = argparse.ArgumentParser(description="tokens/s of the 12-layer configuration, or the kernel list of one step")
+    ap.add_argument("--kind", default="mxfp4", choices=["dense", "ste", "mxfp4", "nvfp4"])
+    ap.add_argument("--unfused", action="store_true", help="separate LayerNorm, GELU and quantizer passes")
+    ap.add_argument("--kernels", action="store_true", help="print device time per kernel of one step instead")
+    ap.add_argument("--steps", type=int, default=5)
+    a = ap.parse_args()
+    if a.kernels:
+        rows, total = kernel_table(a.kind, not a.unfused)
+        print(f"{total:10.1f} us of device time per step ({a.kind}, {'unfused' if a.unfused else 'fused'})")
+        for us, n, name in rows:
+            print(f"{us:10.1f} us  x{n:4d}  {name[:120]}")
+    else:
+        t = Trainer(a.kind, device=torch.device("cuda", 0), fused=not a.unfused)
+        sec, loss = t.time(a.steps, 2)
+        t.close()
+        print(f"{a.kind}: {t.tokens_per_step / sec:.0f} tokens/s, {sec * 1e3:.2f} ms per step, loss {loss:.4f}")
