@@ -354,9 +354,10 @@ int ls_wire_int_allreduce(void *handle, float *g, int64_t numel, float *res, flo
 int ls_wire_set_mode(void *handle, int mode, int subs, int stagger);
 int ls_wire_mode(void *handle);
 
-/* How the groups of a phase are spread over the warps: 0 (default) = fixed
- * shares, 1 = chunks of 256 groups handed out from a counter in the arena.
- * Results do not depend on it; for measurements. */
+/* How the groups of a phase are spread over the warps: 0 = fixed shares (the
+ * default up to seven ranks), 1 = chunks of 256 groups handed out from a counter
+ * in the arena (the default from eight ranks up, where it measured 9 % faster).
+ * Results do not depend on it. */
 int ls_wire_set_dynamic(void *handle, int on);
 
 /* How long (default 20 s) a kernel waits for a peer's flag before it gives up.

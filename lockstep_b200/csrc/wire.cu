@@ -815,7 +815,9 @@ static int wire_create(int rank, int world, int64_t padded, int bits, void **out
     w->g.ag_off = w->g.rs_off + w->g.slot_bytes * world;
     w->g.timeout_ns = kDefaultTimeoutNs;
     w->g.bits = bits;
-    w->g.dynamic = 0;
+    // groups handed out in chunks from a counter instead of fixed shares per warp: nothing on
+    // one to four ranks (277 vs 281 us on four), 9 % on eight (292 vs 324 us)
+    w->g.dynamic = world >= 8 ? 1 : 0;
     w->g.mx_off = w->g.ag_off + w->g.slot_bytes * world;
     w->arena_bytes = size_t(w->g.mx_off + (bits ? int64_t(world) * (padded / kChunk) * 4 : 0));
     w->mapped = false;
@@ -903,15 +905,16 @@ Sub whole_shard(const Wire *w) { return Sub{0, 0u, uint32_t(w->g.shard / 8)}; }
 int subs_of(const Wire *w, int want)
 {
     const int64_t units = w->g.shard / 256;
-    // default: two sub-ranges, one on two ranks and from eight ranks up.  Every part boundary
-    // drains the CTA (barrier, fence, flag), so more sub-ranges cost more than their overlap
-    // wins.  Measured, 64 Mi elements with error feedback, 1 / 2 / 4 sub-ranges: one rank 321 /
-    // 306 / 345 us, two ranks 268 / 288 / 341 us, four ranks 281 / 294 / 358 us and 266 us for
-    // two sub-ranges with the CTAs taking a step's three items in rotated orders (the default
-    // from three ranks up), eight ranks 315 / 327 / 442 us (312 / 318 / 440 with rotated
-    // orders).  Letting the warps of a CTA pass the boundaries on their own (no barrier) was
-    // slower still: the early warps' polling competes with the others' memory traffic.
-    int s = want > 0 ? want : ((w->g.world == 2 || w->g.world >= 8) ? 1 : 2);
+    // default: two sub-ranges, one on two ranks.  Every part boundary drains the CTA (barrier,
+    // fence, flag), so more sub-ranges cost more than their overlap wins.  Measured, 64 Mi
+    // elements with error feedback, 1 / 2 / 4 sub-ranges: one rank 321 / 306 / 345 us, two
+    // ranks 268 / 288 / 341 us, four ranks 281 / 294 / 358 us and 266 us for two sub-ranges
+    // with the CTAs taking a step's three items in rotated orders (the default from three
+    // ranks up), eight ranks 315 / 327 / 442 us (312 / 318 / 440 with rotated orders; with the
+    // groups handed out from a counter, the default there, 304 / 292 / 398 and 292 for three).
+    // Letting the warps of a CTA pass the boundaries on their own (no barrier) was slower
+    // still: the early warps' polling competes with the others' memory traffic.
+    int s = want > 0 ? want : (w->g.world == 2 ? 1 : 2);
     if (s > kMaxSub) s = kMaxSub;
     while (s > 1 && units % s != 0) s--;
     return s;

@@ -150,6 +150,12 @@ class Wire:
         h = self._handle(device or torch.device("cuda", torch.cuda.current_device()))
         check(lib().ls_wire_set_mode(h, {"auto": 0, "launches": 1, "fused": 2}[mode], subs, int(bool(stagger))))
 
+    def set_dynamic(self, on, device=None):
+        """How a phase's groups are spread over the warps: handed out in chunks from a counter
+        (True; the default from eight ranks up) or as fixed shares (False).  Results do not depend on it."""
+        h = self._handle(device or torch.device("cuda", torch.cuda.current_device()))
+        check(lib().ls_wire_set_dynamic(h, int(bool(on))))
+
     def mode_name(self):
         if self._h is None or not self.fp4:
             return "launches"
@@ -268,6 +274,11 @@ class LocalWireGroup:
         dev = torch.device("cuda")
         self.res = [torch.zeros(self.kpadded, device=dev) for _ in range(world)] if ef else [None] * world
         self.ores = [torch.zeros(self.kpadded // world, device=dev) for _ in range(world)] if ef else [None] * world
+
+    def set_dynamic(self, on):
+        """Groups handed out from a counter (True) or fixed shares per warp (False); see Wire.set_dynamic."""
+        for h in self.handles:
+            check(lib().ls_wire_set_dynamic(h, int(bool(on))))
 
     def step(self, gs, reverse=False):
         """One step with the phases as separate launches, rank after rank."""

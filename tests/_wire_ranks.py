@@ -29,10 +29,14 @@ def student_t(n, seed):
 def main():
     rank, world, dev = wire.init()
     n = int(sys.argv[1]) if len(sys.argv) > 1 else 1_000_003
-    for method, mode, subs, stagger in (("mxfp4", "launches", 0, False), ("mxfp4ef", "launches", 0, False),
-                                        ("mxfp4ef", "fused", 0, False), ("mxfp4ef", "fused", 8, True), ("mxfp4", "fused", 2, False)):
+    # the last entry of a tuple: groups handed out from a counter (True), fixed shares (False), the default (None)
+    for method, mode, subs, stagger, dynamic in (("mxfp4", "launches", 0, False, None), ("mxfp4ef", "launches", 0, False, True),
+                                                 ("mxfp4ef", "fused", 0, False, None), ("mxfp4ef", "fused", 8, True, False),
+                                                 ("mxfp4", "fused", 2, False, None), ("mxfp4ef", "fused", 2, True, True)):
         w = wire.Wire(method, n, world, rank)
         w.set_mode(mode, subs, stagger, device=dev)
+        if dynamic is not None:
+            w.set_dynamic(dynamic, device=dev)
         ef = method == "mxfp4ef"
         res_c = [np.zeros(w._kpadded, np.float32) for _ in range(world)] if ef else None
         ores_c = [np.zeros(w._kpadded // world, np.float32) for _ in range(world)] if ef else None

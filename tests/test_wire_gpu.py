@@ -99,17 +99,22 @@ def test_wire_object_one_rank(wire):
         w.close()
 
 
-@pytest.mark.parametrize("world,n,subs,stagger", [(1, 70_001, 0, False), (2, 300_000, 4, False), (3, 70_001, 2, True),
-                                                  (4, 1 << 20, 8, True), (8, 100_003, 0, False), (8, 3_000_000, 4, True)])
-def test_cooperative_launch_bytes_and_residuals_vs_oracle(wire, world, n, subs, stagger):
+@pytest.mark.parametrize("world,n,subs,stagger,dynamic", [(1, 70_001, 0, False, None), (2, 300_000, 4, False, None), (3, 70_001, 2, True, None),
+                                                          (4, 1 << 20, 8, True, None), (8, 100_003, 0, False, None), (8, 3_000_000, 4, True, None),
+                                                          (1, 1 << 20, 2, False, True), (2, 300_000, 3, True, True), (4, 3_000_000, 0, False, True),
+                                                          (8, 3_000_000, 2, True, False)])
+def test_cooperative_launch_bytes_and_residuals_vs_oracle(wire, world, n, subs, stagger, dynamic):
     # The pipelined kernel (send(t), reduce(t-1), finish(t-2) over sub-ranges, one flag per
     # sub-range) with every rank's CTAs inside ONE cooperative launch: the waits between ranks
     # are real.  Same bits as the oracle: g, both residuals and the bytes on the wire.
+    # dynamic: the groups of a phase handed out from a counter (the default from eight ranks up) or as fixed shares
     grp = wire.LocalWireGroup(world, n, ef=True)
+    if dynamic is not None:
+        grp.set_dynamic(dynamic)
     padded, shard = grp.kpadded, grp.kpadded // world
     res_c = [np.zeros(padded, np.float32) for _ in range(world)]
     ores_c = [np.zeros(shard, np.float32) for _ in range(world)]
-    for step in range(3):
+    for step in range(4 if dynamic else 3):
         grads = [_student_t(n, 100 * step + r).numpy() for r in range(world)]
         want, sent, owned = cref.wire_step(grads, res_c, ores_c, unit=256)
         gs = [torch.from_numpy(g.copy()).cuda() for g in grads]
@@ -148,6 +153,8 @@ def test_wire_modes_give_the_same_bits(wire, mode, subs):
     gen = torch.Generator().manual_seed(5)
     w = wire.Wire("mxfp4ef", n)
     w.set_mode(mode, subs, stagger=subs == 4)
+    if subs in (0, 3):
+        w.set_dynamic(True)                                    # groups handed out from a counter, in both ways to run a step
     assert w.mode_name() == ("three launches" if mode == "launches" else "one cooperative launch")
     res_c, ores_c = [np.zeros(w._kpadded, np.float32)], [np.zeros(w._kpadded, np.float32)]
     for _ in range(3):
