@@ -14,7 +14,8 @@
 // for an fp32 |v| the comparison with their real sum equals the comparison with that sum
 // rounded down: seven thresholds per block, seven comparisons per element.  Most blocks never
 // get there: a multiplication and the hardware converter give the same codes (see the kernel).
-// A thread owns one block: 32 or 64 bytes in, 8 bytes of codes and one scale byte out.
+// A thread owns one block at a time (two per launch, their loads issued together): 32 or 64
+// bytes in, 8 bytes of codes and one scale byte out.
 // Four neighbouring lanes hold the four scales of one word of the tensor-core scale-factor
 // layout, so the scale bytes leave as words.
 
